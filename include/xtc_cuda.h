@@ -1,0 +1,213 @@
+/*
+ * libxtc_cuda -- C ABI of the B200 (sm_100a) execution backend for XTC graphs.
+ *
+ * Every entry point has C linkage, takes plain pointers and sizes, returns an
+ * int status (XTC_CUDA_OK == 0) and records a message readable through
+ * xtc_cuda_last_error().  There is no CPU fallback: on a machine without a
+ * CUDA device the compute entry points return XTC_CUDA_ERR_RUNTIME.
+ *
+ * Each declaration cites the piece of the reference (xtc-tools/xtc, paths
+ * relative to that project) whose role it takes over.
+ */
+#ifndef XTC_CUDA_H_
+#define XTC_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XTC_CUDA_ABI_VERSION 1
+
+enum {
+  XTC_CUDA_OK = 0,
+  XTC_CUDA_ERR_INVALID = 1,        /* bad argument (shape, alignment, NULL, unknown step) */
+  XTC_CUDA_ERR_RUNTIME = 2,        /* a CUDA runtime/driver call failed                     */
+  XTC_CUDA_ERR_UNSUPPORTED = 3,    /* legal request the kernels do not cover                */
+  XTC_CUDA_ERR_DEVICE_TIMEOUT = 4, /* a bounded in-kernel wait gave up (see device_status)  */
+  XTC_CUDA_ERR_NOMEM = 5
+};
+
+/* ------------------------------------------------------------------------
+ * Device, memory, streams.
+ * Replaces src/xtc/runtimes/accelerator/gpu/GPUDevice.py:131-215 (mgpuMemAlloc,
+ * mgpuMemFree, mgpuMemcpy, mgpuStreamCreate, mgpuStreamSynchronize) and the
+ * aligned allocator src/xtc/csrcs/runtimes/host/alloc.c:9-38 (256-byte default
+ * alignment, src/xtc/csrcs/runtimes/host/cndarray.c:16).
+ * ---------------------------------------------------------------------- */
+int xtc_cuda_abi_version(void);
+int xtc_cuda_device_count(int* count);
+int xtc_cuda_set_device(int device);
+int xtc_cuda_get_device(int* device);
+int xtc_cuda_device_name(int device, char* buf, size_t buf_len);
+int xtc_cuda_malloc(void** ptr, size_t bytes);
+int xtc_cuda_free(void* ptr);
+int xtc_cuda_host_alloc(void** ptr, size_t bytes); /* pinned host memory */
+int xtc_cuda_host_free(void* ptr);
+int xtc_cuda_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+int xtc_cuda_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+int xtc_cuda_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+int xtc_cuda_memset(void* dst, int byte_value, size_t bytes, void* stream);
+int xtc_cuda_stream_create(void** stream);
+int xtc_cuda_stream_destroy(void* stream);
+int xtc_cuda_stream_synchronize(void* stream);
+int xtc_cuda_device_synchronize(void);
+/* Reads and clears the per-device status word that kernels set when one of
+ * their bounded waits gives up (0 = none).  Error reporting in the reference is
+ * the (results, code, message) tuple of src/xtc/utils/evaluation.py:129-145. */
+int xtc_cuda_device_status(int* status);
+const char* xtc_cuda_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Kernels.  All pointers are device pointers; tensors are float32, dense,
+ * C-contiguous unless a leading dimension says otherwise.
+ * ---------------------------------------------------------------------- */
+
+enum {
+  XTC_CUDA_GEMM_A_TRANSPOSED = 1, /* A is stored [K, M] row-major (a fused O.transpose) */
+  XTC_CUDA_GEMM_B_TRANSPOSED = 2, /* B is stored [N, K] row-major (layout=[1,0])        */
+  XTC_CUDA_FUSE_RELU = 4          /* out = max(out, relu_threshold) in the epilogue     */
+};
+
+enum {
+  XTC_CUDA_PRECISION_TF32 = 0,   /* one TF32 tensor-core product, fp32 accumulate        */
+  XTC_CUDA_PRECISION_3XTF32 = 1, /* hi/lo split, three products: ~fp32 accuracy          */
+  XTC_CUDA_PRECISION_FP32_SIMT = 2 /* CUDA-core fp32 FMA (no tensor cores)               */
+};
+
+/* Kernel parameters a schedule maps onto (0 = let the library choose).  These
+ * are what the Scheduler's tile / unroll / parallelize directives turn into:
+ * the reference records the same directives in
+ * src/xtc/backends/mlir/MlirNodeScheduler.py:84-170. */
+typedef struct xtc_cuda_gemm_config {
+  int32_t tile_m;    /* CTA tile rows     : 128                                   */
+  int32_t tile_n;    /* CTA tile columns  : 64, 128 or 256                        */
+  int32_t tile_k;    /* K per pipeline stage: 32 or 64                            */
+  int32_t stages;    /* shared-memory ring depth (0 = as many as fit)             */
+  int32_t precision; /* XTC_CUDA_PRECISION_*                                      */
+  int32_t epilogue;  /* 0 = default; 1 = direct global stores; 2 = TMA stores     */
+  int32_t reserved[2];
+} xtc_cuda_gemm_config;
+
+/* C[M,N] = A[M,K] * B[K,N]  (+ optional relu).  Replaces the loop nest the
+ * reference generates for O.matmul: linalg.fill(0) + linalg.matmul,
+ * src/xtc/backends/mlir/MlirOps.py:189-270; semantics
+ * src/xtc/graphs/xtc/operators.py:159-221 (np.dot) and, for the fused relu,
+ * operators.py:224-249.  `workspace` is scratch for the 3xTF32 operand split
+ * (size from xtc_cuda_gemm_workspace_bytes); it may be NULL for TF32. */
+int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldb, int64_t ldc, int flags, float relu_threshold,
+                      const xtc_cuda_gemm_config* cfg, void* workspace, size_t workspace_bytes,
+                      void* stream);
+int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int flags,
+                                  const xtc_cuda_gemm_config* cfg, size_t* bytes);
+
+/* Y[B,OH,OW,F] = conv2d(pad(X[B,H,W,C]), Wt[R,S,C,F]) (+ optional relu), NHWC x
+ * HWIO, stride (stride_h, stride_w).  pad_* is a zero padding of H and W fused
+ * into the operand fetch (the reference needs a separate O.pad node for it).
+ * Replaces the 7-D linalg.generic of src/xtc/backends/mlir/MlirOps.py:331-420;
+ * semantics src/xtc/graphs/xtc/operators.py:252-347 and, for the fused pad,
+ * operators.py:350-433 with constant_value == 0. */
+int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* Y, int64_t B, int64_t H,
+                             int64_t W, int64_t C, int64_t R, int64_t S, int64_t F, int stride_h,
+                             int stride_w, int pad_top, int pad_bottom, int pad_left,
+                             int pad_right, int flags, float relu_threshold,
+                             const xtc_cuda_gemm_config* cfg, void* workspace,
+                             size_t workspace_bytes, void* stream);
+int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, int64_t C, int64_t R,
+                                    int64_t S, int64_t F, int stride_h, int stride_w, int pad_top,
+                                    int pad_bottom, int pad_left, int pad_right,
+                                    const xtc_cuda_gemm_config* cfg, size_t* bytes);
+
+#define XTC_CUDA_MAX_DIMS 6
+
+/* Y = transpose(X, axes) for ndim <= XTC_CUDA_MAX_DIMS; bit-exact.  Replaces
+ * src/xtc/graphs/xtc/operators.py:757-787 (np.transpose); the only compiled
+ * lowering in the reference is TVM's, src/xtc/backends/tvm/TVMOps.py:688-778. */
+int xtc_cuda_transpose_f32(const float* X, float* Y, int ndim, const int64_t* shape,
+                           const int32_t* axes, void* stream);
+
+/* Y = pad(X) with per-axis (lo, hi) widths and a constant; negative widths crop
+ * (O.unpad).  Bit-exact.  Replaces linalg.fill + linalg.copy into a subview,
+ * src/xtc/backends/mlir/MlirOps.py:718-735 (pad), :778-887 (pad2d / unpad);
+ * semantics src/xtc/graphs/xtc/operators.py:413-433 (np.pad, mode="constant"). */
+int xtc_cuda_pad_f32(const float* X, float* Y, int ndim, const int64_t* shape, const int64_t* lo,
+                     const int64_t* hi, float value, void* stream);
+
+/* Y = max(X, threshold) elementwise.  Replaces src/xtc/backends/mlir/MlirOps.py:
+ * 459-557; semantics src/xtc/graphs/xtc/operators.py:224-249. */
+int xtc_cuda_relu_f32(const float* X, float* Y, int64_t n, float threshold, void* stream);
+
+/* hi = round_to_tf32(X), lo = X - hi: the operand split of the 3xTF32 mode. */
+int xtc_cuda_split_tf32(const float* X, float* hi, float* lo, int64_t n, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Plans: a lowered graph = a list of steps over numbered buffer slots.
+ * Slots [0, n_inputs) are the graph inputs, [n_inputs, n_inputs + n_outputs)
+ * the graph outputs, in the order of the reference's payload signature
+ * `void <graph.name>(void* in0.., void* out0..)` produced by
+ * src/xtc/backends/mlir/MlirGraphBackend.py:144-148; the remaining slots are
+ * intermediates the plan owns (the reference puts them in memref.alloca,
+ * MlirGraphBackend.py:96-103).
+ * ---------------------------------------------------------------------- */
+enum {
+  XTC_CUDA_STEP_GEMM = 1,
+  XTC_CUDA_STEP_CONV2D = 2,
+  XTC_CUDA_STEP_TRANSPOSE = 3,
+  XTC_CUDA_STEP_PAD = 4,
+  XTC_CUDA_STEP_RELU = 5,
+  XTC_CUDA_STEP_COPY = 6
+};
+
+typedef struct xtc_cuda_step {
+  int32_t kind;
+  int32_t in0, in1, out; /* buffer slots; in1 = -1 when unused */
+  int32_t flags;         /* XTC_CUDA_GEMM_* | XTC_CUDA_FUSE_RELU */
+  int32_t ndim;          /* transpose / pad: rank of the input                      */
+  float relu_threshold;
+  float pad_value;
+  /* GEMM: {M, N, K, lda, ldb, ldc}; CONV2D: {B, H, W, C, R, S}; TRANSPOSE / PAD:
+   * input shape; RELU / COPY: {numel}. */
+  int64_t dims[XTC_CUDA_MAX_DIMS];
+  /* CONV2D: {F, stride_h, stride_w}; TRANSPOSE: axes; PAD: lo widths. */
+  int64_t aux0[XTC_CUDA_MAX_DIMS];
+  /* CONV2D: {pad_top, pad_bottom, pad_left, pad_right}; PAD: hi widths. */
+  int64_t aux1[XTC_CUDA_MAX_DIMS];
+  xtc_cuda_gemm_config cfg;
+} xtc_cuda_step;
+
+typedef struct xtc_cuda_plan xtc_cuda_plan;
+
+/* slot_bytes[n_slots] gives every slot's size.  The plan allocates the
+ * intermediates and any kernel workspace on the current device.  Plays the role
+ * of Compiler.compile -> Module, src/xtc/backends/mlir/MlirCompiler.py:67-110. */
+int xtc_cuda_plan_create(xtc_cuda_plan** plan, const xtc_cuda_step* steps, int n_steps,
+                         int n_inputs, int n_outputs, int n_slots, const size_t* slot_bytes);
+int xtc_cuda_plan_destroy(xtc_cuda_plan* plan);
+/* io[n_inputs + n_outputs]: device pointers.  Asynchronous on `stream`. */
+int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* stream);
+/* io: HOST pointers.  Copies inputs to the device, runs, copies outputs back,
+ * synchronises: the call the per-module payload makes, equivalent to calling
+ * the reference payload with host memory (src/xtc/utils/cfunc.py:89-110). */
+int xtc_cuda_plan_run_host(xtc_cuda_plan* plan, void* const* io);
+/* CUDA-event twin of evaluate_perf, src/xtc/csrcs/runtimes/host/
+ * evaluate_perf.c:63-125: one untimed warm-up call when number > 0, then
+ * `repeat` measurements of `number` back-to-back runs, doubling the count until
+ * a measurement lasts min_repeat_ms; results[r] = seconds per run. */
+int xtc_cuda_evaluate(xtc_cuda_plan* plan, void* const* io, int repeat, int number,
+                      int min_repeat_ms, double* results);
+/* Device time of the kernels launched by the most recent xtc_cuda_evaluate
+ * measurement, per step, in seconds per run (n_steps doubles). */
+int xtc_cuda_plan_step_count(const xtc_cuda_plan* plan, int* n_steps);
+
+/* Peak fused-multiply-add rate of the tensor pipe for "float32" (TF32 inputs),
+ * in FMA/s: same unit as evaluate_flops, src/xtc/csrcs/runtimes/host/
+ * evaluate_flops.c:461-495, so ops_count / peak keeps its meaning. */
+int xtc_cuda_peak_fma(const char* dtype, double* fma_per_second);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XTC_CUDA_H_ */

@@ -1,0 +1,233 @@
+// NHWC x HWIO convolution as an implicit GEMM on the TF32 tensor cores:
+//   M = B*OH*OW output pixels, N = F output channels, K = R*S*C.
+// The A operand is never materialised: the producer warp of the GEMM kernel
+// fetches [128 pixels x 32 channels] slabs with im2col-mode TMA, one filter
+// tap (r, s) at a time.  Zero padding of H and W is folded into the fetch (the
+// tensor map's bounding box starts at -pad and out-of-bounds reads return 0),
+// relu into the epilogue.  Shapes TMA cannot address (C or F not a multiple of
+// 4) run on a direct CUDA-core kernel.
+#include "gemm_tf32.cuh"
+
+namespace xtc {
+
+struct ConvArgs {
+  const float *X, *Wt;
+  float* Y;
+  int64_t B, H, W, C, R, S, F;
+  int sh, sw, pt, pb, pl, pr;
+  int64_t OH, OW;
+  bool relu;
+  float thr;
+  int stages;
+  cudaStream_t stream;
+};
+
+__global__ void __launch_bounds__(256)
+conv2d_direct_kernel(const float* __restrict__ X, const float* __restrict__ Wt,
+                     float* __restrict__ Y, int64_t total, int H, int W, int C, int R, int S,
+                     int F, int OH, int OW, int sh, int sw, int pt, int pl, int relu, float thr) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int f = static_cast<int>(i % F);
+    int64_t pix = i / F;
+    const int ow = static_cast<int>(pix % OW); pix /= OW;
+    const int oh = static_cast<int>(pix % OH);
+    const int64_t b = pix / OH;
+    float acc = 0.f;
+    for (int r = 0; r < R; ++r) {
+      const int ih = oh * sh - pt + r;
+      if (ih < 0 || ih >= H) continue;
+      for (int s = 0; s < S; ++s) {
+        const int iw = ow * sw - pl + s;
+        if (iw < 0 || iw >= W) continue;
+        const float* xp = X + ((b * H + ih) * W + iw) * C;
+        const float* wp = Wt + (static_cast<int64_t>(r) * S + s) * C * F + f;
+        for (int c = 0; c < C; ++c) acc = fmaf(xp[c], wp[static_cast<int64_t>(c) * F], acc);
+      }
+    }
+    if (relu) acc = fmaxf(acc, thr);
+    Y[i] = acc;
+  }
+}
+
+namespace {
+
+int make_tmap_im2col(CUtensorMap* map, const ConvArgs& a, uint32_t pixels) {
+  encode_im2col_fn enc = get_encode_im2col();
+  if (!enc) {
+    set_error("cuTensorMapEncodeIm2col is not available from this driver");
+    return XTC_CUDA_ERR_RUNTIME;
+  }
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W),
+                        static_cast<cuuint64_t>(a.H), static_cast<cuuint64_t>(a.B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(a.C) * 4, static_cast<cuuint64_t>(a.W * a.C) * 4,
+                           static_cast<cuuint64_t>(a.H * a.W * a.C) * 4};
+  // Base pixels (the input pixel under filter tap (0,0)) range over
+  // [-pad, extent + pad - (filter - 1)) in each of W and H.
+  int lower[2] = {-a.pl, -a.pt};
+  int upper[2] = {a.pr - static_cast<int>(a.S - 1), a.pb - static_cast<int>(a.R - 1)};
+  cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(a.sw), static_cast<cuuint32_t>(a.sh), 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.X), dims, strides,
+                   lower, upper, 32, pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeIm2col failed (%d)", static_cast<int>(r));
+    return XTC_CUDA_ERR_INVALID;
+  }
+  return XTC_CUDA_OK;
+}
+
+template <int BN, int KSPANS, bool TMA_STORE>
+int launch_conv_tc(const ConvArgs& a) {
+  using L = SmemLayout<BN, KSPANS, false>;
+  constexpr int BK = L::BK;
+  const int max_stages = L::max_stages(TMA_STORE);
+  int stages = a.stages <= 0 ? max_stages : a.stages;
+  if (stages > max_stages) stages = max_stages;
+  if (stages < 2) stages = 2;
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+
+  const int64_t M = a.B * a.OH * a.OW, N = a.F, K = a.R * a.S * a.C;
+  CUtensorMap tmA, tmB, tmZ, tmC;
+  memset(&tmZ, 0, sizeof(tmZ));
+  memset(&tmC, 0, sizeof(tmC));
+  int rc;
+  if ((rc = make_tmap_im2col(&tmA, a, BM))) return rc;
+  if ((rc = make_tmap_2d(&tmB, a.Wt, K, N, N, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)))
+    return rc;
+  if (TMA_STORE &&
+      (rc = make_tmap_2d(&tmC, a.Y, M, N, N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = a.Y;
+  p.ldc = N;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.tiles_m = static_cast<int>((M + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((N + BN - 1) / BN);
+  p.conv_cblocks = static_cast<int>((a.C + BK - 1) / BK);
+  p.k_blocks = static_cast<int>(a.R * a.S) * p.conv_cblocks;
+  p.relu = a.relu;
+  p.relu_threshold = a.thr;
+  p.status = device_status_word(dev);
+  XTC_REQUIRE(p.status != nullptr, "conv2d: device status word unavailable");
+  p.conv_ohow = static_cast<int>(a.OH * a.OW);
+  p.conv_ow = static_cast<int>(a.OW);
+  p.conv_c = static_cast<int>(a.C);
+  p.conv_s = static_cast<int>(a.S);
+  p.conv_stride_h = a.sh;
+  p.conv_stride_w = a.sw;
+  p.conv_pad_top = a.pt;
+  p.conv_pad_left = a.pl;
+
+  auto kernel = gemm_tf32_kernel<BN, KSPANS, A_IM2COL, true, false, TMA_STORE>;
+  const int smem = L::total(stages, TMA_STORE);
+  static thread_local int configured_dev = -1;
+  static thread_local int configured_smem = 0;
+  if (configured_dev != dev || configured_smem < smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured_dev = dev;
+    configured_smem = smem;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
+  kernel<<<grid, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmZ, tmZ, tmC, p, stages);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+template <bool TMA_STORE>
+int dispatch_conv(const ConvArgs& a, int tile_n, int tile_k) {
+  const int ks = tile_k == 64 ? 2 : 1;
+  switch (tile_n) {
+    case 64: return ks == 1 ? launch_conv_tc<64, 1, TMA_STORE>(a) : launch_conv_tc<64, 2, TMA_STORE>(a);
+    case 128: return ks == 1 ? launch_conv_tc<128, 1, TMA_STORE>(a) : launch_conv_tc<128, 2, TMA_STORE>(a);
+    case 256: return ks == 1 ? launch_conv_tc<256, 1, TMA_STORE>(a) : launch_conv_tc<256, 2, TMA_STORE>(a);
+  }
+  set_error("conv2d: unsupported tile_n=%d", tile_n);
+  return XTC_CUDA_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+}  // namespace xtc
+
+using namespace xtc;
+
+extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t,
+                                               int64_t, int64_t, int, int, int, int, int, int,
+                                               const xtc_cuda_gemm_config*, size_t* bytes) {
+  XTC_REQUIRE(bytes != nullptr, "conv2d_workspace_bytes: bytes is NULL");
+  *bytes = 0;
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* Y, int64_t B,
+                                        int64_t H, int64_t W, int64_t C, int64_t R, int64_t S,
+                                        int64_t F, int stride_h, int stride_w, int pad_top,
+                                        int pad_bottom, int pad_left, int pad_right, int flags,
+                                        float relu_threshold, const xtc_cuda_gemm_config* cfg,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  XTC_REQUIRE(X && Wt && Y, "conv2d: NULL operand");
+  XTC_REQUIRE(B > 0 && H > 0 && W > 0 && C > 0 && R > 0 && S > 0 && F > 0, "conv2d: empty extent");
+  XTC_REQUIRE(stride_h > 0 && stride_w > 0, "conv2d: stride must be positive");
+  XTC_REQUIRE(pad_top >= 0 && pad_bottom >= 0 && pad_left >= 0 && pad_right >= 0,
+              "conv2d: negative padding");
+  ConvArgs a;
+  a.X = X; a.Wt = Wt; a.Y = Y;
+  a.B = B; a.H = H; a.W = W; a.C = C; a.R = R; a.S = S; a.F = F;
+  a.sh = stride_h; a.sw = stride_w;
+  a.pt = pad_top; a.pb = pad_bottom; a.pl = pad_left; a.pr = pad_right;
+  XTC_REQUIRE(H + pad_top + pad_bottom >= R && W + pad_left + pad_right >= S,
+              "conv2d: filter larger than the padded input");
+  a.OH = (H + pad_top + pad_bottom - R) / stride_h + 1;
+  a.OW = (W + pad_left + pad_right - S) / stride_w + 1;
+  a.relu = flags & XTC_CUDA_FUSE_RELU;
+  a.thr = relu_threshold;
+  xtc_cuda_gemm_config c;
+  memset(&c, 0, sizeof(c));
+  if (cfg) c = *cfg;
+  a.stages = c.stages;
+  a.stream = static_cast<cudaStream_t>(stream);
+  const int64_t M = B * a.OH * a.OW;
+  XTC_REQUIRE(M < (1ll << 31) && R * S * C < (1ll << 31), "conv2d: problem too large");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+
+  auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  // The tensor-core path needs TMA-addressable operands, a unit or small
+  // traversal stride, corner offsets within the im2col descriptor's range, and
+  // the tiles of the bounding box to line up with the output pixel grid.
+  const bool exact_h = (H + pad_top + pad_bottom - R) % stride_h == 0;
+  const bool exact_w = (W + pad_left + pad_right - S) % stride_w == 0;
+  const bool tc_ok = c.precision == XTC_CUDA_PRECISION_TF32 && C % 4 == 0 && F % 4 == 0 &&
+                     a16(X) && a16(Wt) && stride_h <= 8 && stride_w <= 8 && pad_top <= 127 &&
+                     pad_left <= 127 && S <= 128 && R <= 128 && exact_h && exact_w &&
+                     W <= 65535 && H <= 65535;
+  if (!tc_ok) {
+    XTC_REQUIRE(c.precision != XTC_CUDA_PRECISION_3XTF32,
+                "conv2d: the 3xTF32 mode is not available for convolutions");
+    const int64_t total = M * F;
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count(dev)) * 16;
+    if (blocks > cap) blocks = cap;
+    conv2d_direct_kernel<<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
+        X, Wt, Y, total, (int)H, (int)W, (int)C, (int)R, (int)S, (int)F, (int)a.OH, (int)a.OW,
+        stride_h, stride_w, pad_top, pad_left, a.relu, a.thr);
+    XTC_CUDA_CHECK(cudaGetLastError());
+    return XTC_CUDA_OK;
+  }
+  XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM, "conv2d: tile_m=%d unsupported (only %d)", c.tile_m, BM);
+  int tile_n = c.tile_n;
+  if (tile_n == 0) tile_n = F <= 64 ? 64 : (F <= 128 ? 128 : 256);
+  int tile_k = c.tile_k ? c.tile_k : (C % 64 == 0 ? 64 : 32);
+  const bool tma_store = c.epilogue == 2 && a16(Y);
+  return tma_store ? dispatch_conv<true>(a, tile_n, tile_k) : dispatch_conv<false>(a, tile_n, tile_k);
+}

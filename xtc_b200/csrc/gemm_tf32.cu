@@ -1,0 +1,299 @@
+// Host launchers of the TF32 GEMM kernel and the CUDA-core fallback GEMM.
+#include "gemm_tf32.cuh"
+
+namespace xtc {
+
+// ---------------------------------------------------------------------------
+// CUDA-core fp32 GEMM for shapes the TMA path cannot address (leading
+// dimensions that are not a multiple of 4 elements) and for the FP32_SIMT
+// precision mode.  64x64 tile, 16-deep, 4x4 micro-tile per thread.
+// ---------------------------------------------------------------------------
+template <bool A_T, bool B_T>
+__global__ void __launch_bounds__(256)
+gemm_f32_simt_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                     float* __restrict__ C, int M, int N, int K, int64_t lda, int64_t ldb,
+                     int64_t ldc, int relu, float thr) {
+  __shared__ float sA[16][64 + 4];
+  __shared__ float sB[16][64 + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      int mm, kk;
+      if (!A_T) { kk = i & 15; mm = i >> 4; } else { mm = i & 63; kk = i >> 6; }
+      int gm = m0 + mm, gk = k0 + kk;
+      float v = 0.f;
+      if (gm < M && gk < K) v = A_T ? A[static_cast<int64_t>(gk) * lda + gm]
+                                    : A[static_cast<int64_t>(gm) * lda + gk];
+      sA[kk][mm] = v;
+    }
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      int nn, kk;
+      if (!B_T) { nn = i & 63; kk = i >> 6; } else { kk = i & 15; nn = i >> 4; }
+      int gn = n0 + nn, gk = k0 + kk;
+      float v = 0.f;
+      if (gn < N && gk < K) v = B_T ? B[static_cast<int64_t>(gn) * ldb + gk]
+                                    : B[static_cast<int64_t>(gk) * ldb + gn];
+      sB[kk][nn] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = sA[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = sB[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int gn = n0 + tx * 4 + j;
+      if (gn < N) {
+        float v = acc[i][j];
+        if (relu) v = fmaxf(v, thr);
+        C[static_cast<int64_t>(gm) * ldc + gn] = v;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host launcher
+// ---------------------------------------------------------------------------
+namespace {
+
+struct LaunchArgs {
+  const float *A, *B, *Alo, *Blo;
+  float* C;
+  int64_t M, N, K, lda, ldb, ldc;
+  bool a_t, b_t, relu;
+  float thr;
+  int stages;
+  cudaStream_t stream;
+};
+
+template <int BN, int KSPANS, int A_MODE, bool B_MN, bool SPLIT3, bool TMA_STORE>
+int launch_tc(const LaunchArgs& a) {
+  using L = SmemLayout<BN, KSPANS, SPLIT3>;
+  constexpr int BK = L::BK;
+  constexpr bool A_MN = A_MODE == A_MNMAJOR;
+  const int max_stages = L::max_stages(TMA_STORE);
+  XTC_REQUIRE(max_stages >= 2, "gemm: tile %dx%dx%d does not fit shared memory", BM, BN, BK);
+  int stages = a.stages <= 0 ? max_stages : a.stages;
+  if (stages > max_stages) stages = max_stages;
+  if (stages < 2) stages = 2;
+
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+
+  CUtensorMap tmA, tmB, tmAlo, tmBlo, tmC;
+  memset(&tmAlo, 0, sizeof(tmAlo));
+  memset(&tmBlo, 0, sizeof(tmBlo));
+  memset(&tmC, 0, sizeof(tmC));
+  int rc;
+  auto mapA = [&](CUtensorMap* m, const float* p) {
+    return A_MN ? make_tmap_2d(m, p, a.K, a.M, a.lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+                : make_tmap_2d(m, p, a.M, a.K, a.lda, 32, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  auto mapB = [&](CUtensorMap* m, const float* p) {
+    return B_MN ? make_tmap_2d(m, p, a.K, a.N, a.ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+                : make_tmap_2d(m, p, a.N, a.K, a.ldb, 32, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  if ((rc = mapA(&tmA, a.A))) return rc;
+  if ((rc = mapB(&tmB, a.B))) return rc;
+  if (SPLIT3) {
+    if ((rc = mapA(&tmAlo, a.Alo))) return rc;
+    if ((rc = mapB(&tmBlo, a.Blo))) return rc;
+  }
+  if (TMA_STORE) {
+    if ((rc = make_tmap_2d(&tmC, a.C, a.M, a.N, a.ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B)))
+      return rc;
+  }
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = a.C;
+  p.ldc = a.ldc;
+  p.M = static_cast<int>(a.M);
+  p.N = static_cast<int>(a.N);
+  p.K = static_cast<int>(a.K);
+  p.tiles_m = static_cast<int>((a.M + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((a.N + BN - 1) / BN);
+  p.k_blocks = static_cast<int>((a.K + BK - 1) / BK);
+  p.relu = a.relu;
+  p.relu_threshold = a.thr;
+  p.status = device_status_word(dev);
+  XTC_REQUIRE(p.status != nullptr, "gemm: device status word unavailable");
+
+  auto kernel = gemm_tf32_kernel<BN, KSPANS, A_MODE, B_MN, SPLIT3, TMA_STORE>;
+  const int smem = L::total(stages, TMA_STORE);
+  static thread_local int configured_dev = -1;
+  static thread_local int configured_smem = 0;
+  if (configured_dev != dev || configured_smem < smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured_dev = dev;
+    configured_smem = smem;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
+  kernel<<<grid, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmAlo, tmBlo, tmC, p, stages);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+template <int BN, int KSPANS, bool SPLIT3, bool TMA_STORE>
+int dispatch_major(const LaunchArgs& a) {
+  // a_t: A stored [K,M] -> MN-major A.  b_t: B stored [N,K] -> K-major B.
+  if (!a.a_t && !a.b_t) return launch_tc<BN, KSPANS, A_KMAJOR, true, SPLIT3, TMA_STORE>(a);
+  if (a.a_t && !a.b_t) return launch_tc<BN, KSPANS, A_MNMAJOR, true, SPLIT3, TMA_STORE>(a);
+  if (!a.a_t && a.b_t) return launch_tc<BN, KSPANS, A_KMAJOR, false, SPLIT3, TMA_STORE>(a);
+  return launch_tc<BN, KSPANS, A_MNMAJOR, false, SPLIT3, TMA_STORE>(a);
+}
+
+template <bool SPLIT3, bool TMA_STORE>
+int dispatch_tile(const LaunchArgs& a, int tile_n, int tile_k) {
+  const int ks = tile_k == 64 ? 2 : 1;
+  if (SPLIT3 && ks == 2 && tile_n == 256) {
+    // 2 x (128+256) x 64 x 4 bytes per stage leaves a single stage: not a pipeline
+    set_error("gemm: tile 128x256x64 is not available in 3xTF32 mode");
+    return XTC_CUDA_ERR_UNSUPPORTED;
+  }
+  switch (tile_n) {
+    case 64:
+      return ks == 1 ? dispatch_major<64, 1, SPLIT3, TMA_STORE>(a)
+                     : dispatch_major<64, 2, SPLIT3, TMA_STORE>(a);
+    case 128:
+      return ks == 1 ? dispatch_major<128, 1, SPLIT3, TMA_STORE>(a)
+                     : dispatch_major<128, 2, SPLIT3, TMA_STORE>(a);
+    case 256:
+      if (ks == 1) return dispatch_major<256, 1, SPLIT3, TMA_STORE>(a);
+      if constexpr (!SPLIT3) return dispatch_major<256, 2, SPLIT3, TMA_STORE>(a);
+  }
+  set_error("gemm: unsupported tile_n=%d tile_k=%d (tile_n in {64,128,256}, tile_k in {32,64})",
+            tile_n, tile_k);
+  return XTC_CUDA_ERR_UNSUPPORTED;
+}
+
+int launch_simt(const LaunchArgs& a) {
+  dim3 grid(static_cast<unsigned>((a.N + 63) / 64), static_cast<unsigned>((a.M + 63) / 64));
+  const int M = static_cast<int>(a.M), N = static_cast<int>(a.N), K = static_cast<int>(a.K);
+  if (!a.a_t && !a.b_t)
+    gemm_f32_simt_kernel<false, false><<<grid, 256, 0, a.stream>>>(a.A, a.B, a.C, M, N, K, a.lda, a.ldb, a.ldc, a.relu, a.thr);
+  else if (a.a_t && !a.b_t)
+    gemm_f32_simt_kernel<true, false><<<grid, 256, 0, a.stream>>>(a.A, a.B, a.C, M, N, K, a.lda, a.ldb, a.ldc, a.relu, a.thr);
+  else if (!a.a_t && a.b_t)
+    gemm_f32_simt_kernel<false, true><<<grid, 256, 0, a.stream>>>(a.A, a.B, a.C, M, N, K, a.lda, a.ldb, a.ldc, a.relu, a.thr);
+  else
+    gemm_f32_simt_kernel<true, true><<<grid, 256, 0, a.stream>>>(a.A, a.B, a.C, M, N, K, a.lda, a.ldb, a.ldc, a.relu, a.thr);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+bool tma_addressable(const void* p, int64_t ld) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld % 4) == 0;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+}  // namespace
+
+// Default CTA tile for a problem: the widest N tile that still yields at least
+// one tile per SM, else the narrower ones (more tiles for small problems).
+static int default_tile_n(int64_t M, int64_t N, int sms) {
+  const int64_t tm = (M + BM - 1) / BM;
+  for (int bn : {256, 128, 64}) {
+    if (N >= bn && tm * ((N + bn - 1) / bn) >= sms) return bn;
+  }
+  if (N <= 64) return 64;
+  if (N <= 128) return 128;
+  return tm * ((N + 127) / 128) >= sms / 2 ? 128 : 64;
+}
+
+}  // namespace xtc
+
+using namespace xtc;
+
+extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int flags,
+                                             const xtc_cuda_gemm_config* cfg, size_t* bytes) {
+  XTC_REQUIRE(bytes != nullptr, "gemm_workspace_bytes: bytes is NULL");
+  (void)flags;
+  *bytes = 0;
+  if (cfg && cfg->precision == XTC_CUDA_PRECISION_3XTF32) {
+    // hi and lo parts of both operands, each a dense copy
+    *bytes = 2 * align256(static_cast<size_t>(M) * K * 4) + 2 * align256(static_cast<size_t>(K) * N * 4);
+  }
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N,
+                                 int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int flags,
+                                 float relu_threshold, const xtc_cuda_gemm_config* cfg,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  XTC_REQUIRE(A && B && C, "gemm: NULL operand");
+  XTC_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %lldx%lldx%lld", (long long)M,
+              (long long)N, (long long)K);
+  XTC_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm: dimension too large");
+  const bool a_t = flags & XTC_CUDA_GEMM_A_TRANSPOSED;
+  const bool b_t = flags & XTC_CUDA_GEMM_B_TRANSPOSED;
+  XTC_REQUIRE(lda >= (a_t ? M : K), "gemm: lda=%lld too small", (long long)lda);
+  XTC_REQUIRE(ldb >= (b_t ? K : N), "gemm: ldb=%lld too small", (long long)ldb);
+  XTC_REQUIRE(ldc >= N, "gemm: ldc=%lld too small", (long long)ldc);
+
+  xtc_cuda_gemm_config c;
+  memset(&c, 0, sizeof(c));
+  if (cfg) c = *cfg;
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+
+  LaunchArgs a;
+  a.A = A; a.B = B; a.Alo = nullptr; a.Blo = nullptr; a.C = C;
+  a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldb = ldb; a.ldc = ldc;
+  a.a_t = a_t; a.b_t = b_t;
+  a.relu = flags & XTC_CUDA_FUSE_RELU;
+  a.thr = relu_threshold;
+  a.stages = c.stages;
+  a.stream = static_cast<cudaStream_t>(stream);
+
+  const bool tma_ok = tma_addressable(A, lda) && tma_addressable(B, ldb);
+  if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
+
+  XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM, "gemm: tile_m=%d unsupported (only %d)", c.tile_m, BM);
+  const int tile_n = c.tile_n ? c.tile_n : default_tile_n(M, N, sm_count(dev));
+  const int tile_k = c.tile_k ? c.tile_k : 32;
+  const bool tma_store = (c.epilogue == 2) && tma_addressable(C, ldc);
+
+  if (c.precision == XTC_CUDA_PRECISION_3XTF32) {
+    size_t need = 0;
+    xtc_cuda_gemm_workspace_bytes(M, N, K, flags, &c, &need);
+    XTC_REQUIRE(workspace != nullptr && workspace_bytes >= need,
+                "gemm: 3xTF32 needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+    XTC_REQUIRE(lda == (a_t ? M : K) && ldb == (b_t ? K : N),
+                "gemm: 3xTF32 requires dense operands");
+    uint8_t* w = static_cast<uint8_t*>(workspace);
+    float* Ahi = reinterpret_cast<float*>(w);
+    float* Alo = reinterpret_cast<float*>(w + align256(static_cast<size_t>(M) * K * 4));
+    float* Bhi = reinterpret_cast<float*>(w + 2 * align256(static_cast<size_t>(M) * K * 4));
+    float* Blo = reinterpret_cast<float*>(w + 2 * align256(static_cast<size_t>(M) * K * 4) +
+                                          align256(static_cast<size_t>(K) * N * 4));
+    int rc;
+    if ((rc = xtc_cuda_split_tf32(A, Ahi, Alo, M * K, stream))) return rc;
+    if ((rc = xtc_cuda_split_tf32(B, Bhi, Blo, K * N, stream))) return rc;
+    a.A = Ahi; a.Alo = Alo; a.B = Bhi; a.Blo = Blo;
+    return tma_store ? dispatch_tile<true, true>(a, tile_n, tile_k)
+                     : dispatch_tile<true, false>(a, tile_n, tile_k);
+  }
+  XTC_REQUIRE(c.precision == XTC_CUDA_PRECISION_TF32, "gemm: unknown precision %d", c.precision);
+  return tma_store ? dispatch_tile<false, true>(a, tile_n, tile_k)
+                   : dispatch_tile<false, false>(a, tile_n, tile_k);
+}

@@ -1,0 +1,365 @@
+// TF32 tensor-core GEMM for sm_100a: C[M,N] = A[M,K] * B[K,N] (+ relu).
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer   (global -> swizzled shared-memory ring)
+//   warp 1      MMA issuer     (tcgen05.mma kind::tf32, accumulators in TMEM)
+//   warps 2..5  epilogue       (tcgen05.ld -> relu -> global / TMA store)
+// The accumulator is double buffered in TMEM so the epilogue of one output
+// tile overlaps the main loop of the next.
+//
+// Operand layouts in shared memory
+//   K-major operand (A stored [M,K], or B stored [N,K]): 128-byte rows of 32
+//     floats along K, SWIZZLE_128B, 8-row groups 1024 bytes apart.
+//   MN-major operand (B stored [K,N], or A stored [K,M]): 128-byte rows of 32
+//     floats along M/N, one row per k, SWIZZLE_128B with 32-byte atoms (the
+//     only swizzle the tensor core accepts for transposed 32-bit operands),
+//     4-row groups 512 bytes apart, 32-column groups BK*128 bytes apart.
+#pragma once
+#include "common.cuh"
+
+namespace xtc {
+
+using namespace dev;
+
+static constexpr int BM = 128;         // UMMA M (cta_group::1)
+static constexpr int NUM_THREADS = 192;
+static constexpr int EPI_WARPS = 4;
+
+// How the A operand reaches shared memory.
+enum : int {
+  A_KMAJOR = 0,  // A stored [M,K] row-major: 2-D tiled TMA, K-major UMMA operand
+  A_MNMAJOR = 1, // A stored [K,M] row-major (a fused transpose): MN-major UMMA operand
+  A_IM2COL = 2   // A is the implicit im2col matrix of an NHWC tensor: im2col-mode TMA
+};
+
+struct GemmParams {
+  float* C;
+  int64_t ldc;
+  int M, N, K;
+  int tiles_m, tiles_n, k_blocks;
+  int relu;
+  float relu_threshold;
+  int* status;
+  // implicit-GEMM convolution (A_IM2COL): row m = (image, oh, ow), k = (r, s, c)
+  int conv_ohow, conv_ow, conv_c, conv_cblocks, conv_s;
+  int conv_stride_h, conv_stride_w, conv_pad_top, conv_pad_left;
+};
+
+template <int BN, int KSPANS, bool SPLIT3>
+struct SmemLayout {
+  static constexpr int BK = 32 * KSPANS;
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int OPERANDS = SPLIT3 ? 2 : 1;
+  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * OPERANDS;
+  // Per epilogue warp, two 32x32 fp32 staging tiles for TMA stores.
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * 32 * 32 * 4;
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int max_stages(bool tma_store) {
+    int avail = 232448 - 1024 /*alignment slack*/ - BAR_BYTES - (tma_store ? EPI_BYTES : 0);
+    int s = avail / STAGE_BYTES;
+    return s > 8 ? 8 : s;
+  }
+  static constexpr int total(int stages, bool tma_store) {
+    return 1024 + BAR_BYTES + (tma_store ? EPI_BYTES : 0) + stages * STAGE_BYTES;
+  }
+};
+
+// tile index -> (m, n) tile coordinates.  Tiles are walked in panels of
+// GROUP_N tile columns, rows fastest, so that CTAs running at the same time
+// share a few B panels and stream A once per panel.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int GROUP_N = 4;
+  int per_group = tiles_m * GROUP_N;
+  int g = tile / per_group;
+  int first_n = g * GROUP_N;
+  int gn = min(GROUP_N, tiles_n - first_n);
+  int r = tile - g * per_group;
+  tm = r / gn;
+  tn = first_n + (r - tm * gn);
+}
+
+template <int BN, int KSPANS, int A_MODE, bool B_MN, bool SPLIT3, bool TMA_STORE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmAlo,
+                 const __grid_constant__ CUtensorMap tmBlo,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p, const int stages) {
+  using L = SmemLayout<BN, KSPANS, SPLIT3>;
+  constexpr int BK = L::BK;
+  constexpr bool A_MN = A_MODE == A_MNMAJOR;
+  static_assert(!(A_MODE == A_IM2COL && SPLIT3), "the 3xTF32 split is not wired for im2col loads");
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* ring = smem;  // stages * STAGE_BYTES, 1024-aligned
+  uint8_t* epi = ring + static_cast<size_t>(stages) * L::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + (TMA_STORE ? L::EPI_BYTES : 0));
+  uint64_t* full = bars;             // [stages]
+  uint64_t* empty = bars + 8;        // [stages]
+  uint64_t* acc_full = bars + 16;    // [2]
+  uint64_t* acc_empty = bars + 18;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    if (SPLIT3) {
+      prefetch_tmap(&tmAlo);
+      prefetch_tmap(&tmBlo);
+    }
+    if (TMA_STORE) prefetch_tmap(&tmC);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], EPI_WARPS);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        int img = 0, ih0 = 0, iw0 = 0;  // input pixel under the filter origin of row m0
+        if (A_MODE == A_IM2COL) {
+          img = m0 / p.conv_ohow;
+          const int rem = m0 - img * p.conv_ohow;
+          const int oh = rem / p.conv_ow;
+          ih0 = oh * p.conv_stride_h - p.conv_pad_top;
+          iw0 = (rem - oh * p.conv_ow) * p.conv_stride_w - p.conv_pad_left;
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
+            failed = true;
+            break;
+          }
+          uint8_t* sA = ring + static_cast<size_t>(stage) * L::STAGE_BYTES;
+          uint8_t* sB = sA + L::A_BYTES;
+          mbar_arrive_expect_tx(&full[stage], L::STAGE_BYTES);
+          int k0 = kb * BK;
+          int fr = 0, fs = 0, c0 = 0;  // filter tap and first channel of this K block
+          if (A_MODE == A_IM2COL) {
+            const int rs = kb / p.conv_cblocks;
+            c0 = (kb - rs * p.conv_cblocks) * BK;
+            fr = rs / p.conv_s;
+            fs = rs - fr * p.conv_s;
+            k0 = rs * p.conv_c + c0;
+          }
+#pragma unroll
+          for (int op = 0; op < L::OPERANDS; ++op) {
+            const CUtensorMap* ta = op == 0 ? &tmA : &tmAlo;
+            const CUtensorMap* tb = op == 0 ? &tmB : &tmBlo;
+            uint8_t* dA = sA + op * (L::A_BYTES + L::B_BYTES);
+            uint8_t* dB = sB + op * (L::A_BYTES + L::B_BYTES);
+            if (A_MODE == A_IM2COL) {
+#pragma unroll
+              for (int s = 0; s < KSPANS; ++s)
+                tma_load_im2col_4d(dA + s * (BM * 128), ta, &full[stage], c0 + s * 32, iw0, ih0,
+                                   img, static_cast<uint16_t>(fs), static_cast<uint16_t>(fr));
+            } else if (A_MODE == A_KMAJOR) {
+#pragma unroll
+              for (int s = 0; s < KSPANS; ++s)
+                tma_load_2d(dA + s * (BM * 128), ta, &full[stage], k0 + s * 32, m0);
+            } else {
+#pragma unroll
+              for (int g = 0; g < BM / 32; ++g)
+                tma_load_2d(dA + g * (BK * 128), ta, &full[stage], m0 + g * 32, k0);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int g = 0; g < BN / 32; ++g)
+                tma_load_2d(dB + g * (BK * 128), tb, &full[stage], n0 + g * 32, k0);
+            } else {
+#pragma unroll
+              for (int s = 0; s < KSPANS; ++s)
+                tma_load_2d(dB + s * (BN * 128), tb, &full[stage], k0 + s * 32, n0);
+            }
+          }
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_DRAIN);
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            uint32_t aoff, boff;
+            if (!A_MN) aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+            else aoff = kk * 1024;
+            if (B_MN) boff = kk * 1024;
+            else boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
+            const uint32_t acc_in = (kb | kk) != 0;
+            if (!SPLIT3) {
+              uint64_t ad = A_MN ? umma_smem_desc(sA + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                                 : umma_smem_desc(sA + aoff, 16, 1024, UMMA_SWIZZLE_128B);
+              uint64_t bd = B_MN ? umma_smem_desc(sB + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                                 : umma_smem_desc(sB + boff, 16, 1024, UMMA_SWIZZLE_128B);
+              umma_tf32(d_tmem, ad, bd, idesc, acc_in);
+            } else {
+              const uint32_t lo = L::A_BYTES + L::B_BYTES;
+              uint64_t ah = A_MN ? umma_smem_desc(sA + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                                 : umma_smem_desc(sA + aoff, 16, 1024, UMMA_SWIZZLE_128B);
+              uint64_t bh = B_MN ? umma_smem_desc(sB + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                                 : umma_smem_desc(sB + boff, 16, 1024, UMMA_SWIZZLE_128B);
+              uint64_t al = A_MN ? umma_smem_desc(sA + lo + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                                 : umma_smem_desc(sA + lo + aoff, 16, 1024, UMMA_SWIZZLE_128B);
+              uint64_t bl = B_MN ? umma_smem_desc(sB + lo + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                                 : umma_smem_desc(sB + lo + boff, 16, 1024, UMMA_SWIZZLE_128B);
+              // small cross terms first, the dominant hi*hi product last
+              umma_tf32(d_tmem, al, bh, idesc, acc_in);
+              umma_tf32(d_tmem, ah, bl, idesc, 1);
+              umma_tf32(d_tmem, ah, bh, idesc, 1);
+            }
+          }
+          tc_commit(&empty[stage]);  // stage reusable once these MMAs retire
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!failed) tc_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int epi_id = warp - 2;
+    float* stage_buf = reinterpret_cast<float*>(epi + epi_id * (2 * 32 * 32 * 4));
+    int local = 0;
+    int buf = 0;
+    const bool vec_ok = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase)) {
+        if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (p.relu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), p.relu_threshold));
+        }
+        const int col0 = n0 + c * 32;
+        if (TMA_STORE) {
+          // Stage the 32x32 block in shared memory with the 128-byte swizzle
+          // the store's tensor map expects, then one lane issues the store.
+          float* sb = stage_buf + buf * (32 * 32);
+          tma_store_wait_read<1>();  // the buffer used two stores ago is free
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int chunk = j ^ (lane & 7);
+            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            *reinterpret_cast<float4*>(sb + lane * 32 + chunk * 4) = v;
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M) {
+            tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
+          }
+          if (lane == 0) tma_store_commit();
+          buf ^= 1;
+        } else if (row < p.M) {
+          float* dst = p.C + static_cast<int64_t>(row) * p.ldc + col0;
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              reinterpret_cast<float4*>(dst)[j] = v;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) dst[i] = __uint_as_float(r[i]);
+          }
+        }
+      }
+      // all TMEM reads of this warp are complete (wait::ld above): release the buffer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+    if (TMA_STORE) tma_store_wait_all<0>();
+  }
+
+  if (failed) {
+    // Unwind path of a bounded wait that gave up: give copies that may still be
+    // in flight towards this CTA's shared memory time to land before exiting.
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace xtc

@@ -1,0 +1,403 @@
+// Bandwidth-bound kernels: transpose, constant pad / crop, relu and the
+// hi/lo operand split of the 3xTF32 mode.  All are single pass (each input
+// element read once, each output element written once) with 128-bit accesses
+// wherever alignment allows, and bit-exact data movement.
+#include "common.cuh"
+
+namespace xtc {
+
+// ---------------------------------------------------------------------------
+// relu / split: grid-stride, float4
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+relu_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n, float thr) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t n4 = n >> 2;
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  float4* y4 = reinterpret_cast<float4*>(y);
+  for (int64_t i = tid; i < n4; i += stride) {
+    float4 v = __ldcs(x4 + i);
+    v.x = fmaxf(v.x, thr); v.y = fmaxf(v.y, thr); v.z = fmaxf(v.z, thr); v.w = fmaxf(v.w, thr);
+    __stcs(y4 + i, v);
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += stride) y[i] = fmaxf(x[i], thr);
+}
+
+__global__ void __launch_bounds__(256)
+relu_f32_scalar_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n, float thr) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = fmaxf(x[i], thr);
+}
+
+__device__ __forceinline__ float round_tf32(float v) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+  return __uint_as_float(u);
+}
+
+__global__ void __launch_bounds__(256)
+split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
+                  int64_t n) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t n4 = n >> 2;
+  for (int64_t i = tid; i < n4; i += stride) {
+    float4 v = __ldcs(reinterpret_cast<const float4*>(x) + i);
+    float4 h, l;
+    h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
+    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+    reinterpret_cast<float4*>(hi)[i] = h;
+    reinterpret_cast<float4*>(lo)[i] = l;
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += stride) {
+    float h = round_tf32(x[i]);
+    hi[i] = h;
+    lo[i] = x[i] - h;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// transpose
+// ---------------------------------------------------------------------------
+struct TransposeDims {
+  int ndim;               // rank after merging axes
+  int64_t in_shape[XTC_CUDA_MAX_DIMS];
+  int64_t in_stride[XTC_CUDA_MAX_DIMS];   // input strides (elements), indexed by input axis
+  int64_t out_shape[XTC_CUDA_MAX_DIMS];   // out_shape[d] = in_shape[axes[d]]
+  int64_t out_in_stride[XTC_CUDA_MAX_DIMS];  // input stride of the axis that output dim d walks
+  int axes[XTC_CUDA_MAX_DIMS];
+};
+
+// Batched 2-D tile transpose.  The input's innermost axis (length C, stride 1)
+// lands at output dim `oc`; the output's innermost dim walks input axis `ar`
+// (length R, input stride rs).  A 64x64 tile is read with 128-bit loads along C,
+// transposed through padded shared memory, and written with 128-bit stores
+// along R.  Remaining dims form the batch.
+struct Tile2DParams {
+  int64_t R, C;             // tile-plane extents (R: output-contiguous, C: input-contiguous)
+  int64_t in_r_stride;      // input stride of R axis
+  int64_t out_c_stride;     // output stride of C axis
+  int nbatch_dims;
+  int64_t batch_shape[XTC_CUDA_MAX_DIMS];
+  int64_t batch_in_stride[XTC_CUDA_MAX_DIMS];
+  int64_t batch_out_stride[XTC_CUDA_MAX_DIMS];
+  int64_t tiles_r, tiles_c;
+  int vec_in, vec_out;      // 128-bit access legal on the input / output side
+};
+
+template <int TILE>
+__global__ void __launch_bounds__(256)
+transpose_tile_kernel(const float* __restrict__ x, float* __restrict__ y, Tile2DParams p) {
+  __shared__ float tile[TILE][TILE + 1];
+  int64_t b = blockIdx.x;
+  const int64_t tc = b % p.tiles_c; b /= p.tiles_c;
+  const int64_t tr = b % p.tiles_r; b /= p.tiles_r;
+  int64_t in_off = 0, out_off = 0;
+  for (int d = p.nbatch_dims - 1; d >= 0; --d) {
+    const int64_t i = b % p.batch_shape[d];
+    b /= p.batch_shape[d];
+    in_off += i * p.batch_in_stride[d];
+    out_off += i * p.batch_out_stride[d];
+  }
+  const int64_t r0 = tr * TILE, c0 = tc * TILE;
+  const float* src = x + in_off + r0 * p.in_r_stride + c0;
+  float* dst = y + out_off + c0 * p.out_c_stride + r0;
+  const int64_t nr = (p.R - r0) < TILE ? (p.R - r0) : TILE, nc = (p.C - c0) < TILE ? (p.C - c0) : TILE;
+  constexpr int V = TILE / 4;  // float4 per tile row
+
+  if (p.vec_in && nc == TILE) {
+    for (int i = threadIdx.x; i < TILE * V; i += 256) {
+      const int r = i / V, c4 = i % V;
+      if (r < nr) {
+        float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * p.in_r_stride) + c4);
+        tile[r][c4 * 4 + 0] = v.x; tile[r][c4 * 4 + 1] = v.y;
+        tile[r][c4 * 4 + 2] = v.z; tile[r][c4 * 4 + 3] = v.w;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < TILE * TILE; i += 256) {
+      const int r = i / TILE, c = i % TILE;
+      if (r < nr && c < nc) tile[r][c] = src[r * p.in_r_stride + c];
+    }
+  }
+  __syncthreads();
+  if (p.vec_out && nr == TILE) {
+    for (int i = threadIdx.x; i < TILE * V; i += 256) {
+      const int c = i / V, r4 = i % V;
+      if (c < nc) {
+        float4 v = make_float4(tile[r4 * 4 + 0][c], tile[r4 * 4 + 1][c], tile[r4 * 4 + 2][c],
+                               tile[r4 * 4 + 3][c]);
+        __stcs(reinterpret_cast<float4*>(dst + c * p.out_c_stride) + r4, v);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < TILE * TILE; i += 256) {
+      const int c = i / TILE, r = i % TILE;
+      if (r < nr && c < nc) dst[c * p.out_c_stride + r] = tile[r][c];
+    }
+  }
+}
+
+// Permutation that keeps the innermost axis: rows of `inner` contiguous floats
+// are copied whole; `vec` floats (4 or 1) per thread.
+struct RowCopyParams {
+  int ndim;  // outer dims (output order)
+  int64_t out_shape[XTC_CUDA_MAX_DIMS];
+  int64_t in_stride[XTC_CUDA_MAX_DIMS];
+  int64_t inner;   // innermost extent in units of `vec` floats
+  int64_t total;   // total units
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+permute_rows_kernel(const T* __restrict__ x, T* __restrict__ y, RowCopyParams p, int64_t in_unit) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.total;
+       i += stride) {
+    int64_t rem = i / p.inner;
+    const int64_t col = i - rem * p.inner;
+    int64_t off = 0;
+    for (int d = p.ndim - 1; d >= 0; --d) {
+      const int64_t q = rem / p.out_shape[d];
+      off += (rem - q * p.out_shape[d]) * p.in_stride[d];
+      rem = q;
+    }
+    y[i] = x[off / in_unit + col];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// pad / crop: output indexed, one pass
+// ---------------------------------------------------------------------------
+struct PadParams {
+  int ndim;
+  int64_t out_shape[XTC_CUDA_MAX_DIMS];   // innermost in units of VEC floats
+  int64_t in_shape[XTC_CUDA_MAX_DIMS];
+  int64_t in_stride[XTC_CUDA_MAX_DIMS];   // in units of VEC floats
+  int64_t lo[XTC_CUDA_MAX_DIMS];
+  int64_t total;
+  float value;
+};
+
+template <typename T>
+__device__ __forceinline__ T splat(float v);
+template <> __device__ __forceinline__ float splat<float>(float v) { return v; }
+template <> __device__ __forceinline__ float4 splat<float4>(float v) { return make_float4(v, v, v, v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+pad_kernel(const T* __restrict__ x, T* __restrict__ y, PadParams p) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const T fill = splat<T>(p.value);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.total;
+       i += stride) {
+    int64_t rem = i, off = 0;
+    bool inside = true;
+    for (int d = p.ndim - 1; d >= 0; --d) {
+      const int64_t q = rem / p.out_shape[d];
+      const int64_t c = (rem - q * p.out_shape[d]) - p.lo[d];
+      rem = q;
+      inside = inside && c >= 0 && c < p.in_shape[d];
+      off += c * p.in_stride[d];
+    }
+    y[i] = inside ? x[off] : fill;
+  }
+}
+
+namespace {
+int grid_for(int64_t work_items, int dev) {
+  int64_t blocks = (work_items + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count(dev)) * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+}  // namespace
+
+}  // namespace xtc
+
+using namespace xtc;
+
+extern "C" int xtc_cuda_relu_f32(const float* X, float* Y, int64_t n, float threshold,
+                                 void* stream) {
+  XTC_REQUIRE(n >= 0, "relu: negative size");
+  if (n == 0) return XTC_CUDA_OK;
+  XTC_REQUIRE(X && Y, "relu: NULL operand");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (aligned16(X) && aligned16(Y))
+    relu_f32_kernel<<<grid_for((n + 3) / 4, dev), 256, 0, s>>>(X, Y, n, threshold);
+  else
+    relu_f32_scalar_kernel<<<grid_for(n, dev), 256, 0, s>>>(X, Y, n, threshold);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_split_tf32(const float* X, float* hi, float* lo, int64_t n, void* stream) {
+  XTC_REQUIRE(n >= 0, "split_tf32: negative size");
+  if (n == 0) return XTC_CUDA_OK;
+  XTC_REQUIRE(X && hi && lo, "split_tf32: NULL operand");
+  XTC_REQUIRE(aligned16(X) && aligned16(hi) && aligned16(lo), "split_tf32: operands must be 16-byte aligned");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  split_tf32_kernel<<<grid_for((n + 3) / 4, dev), 256, 0, static_cast<cudaStream_t>(stream)>>>(X, hi, lo, n);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_transpose_f32(const float* X, float* Y, int ndim, const int64_t* shape,
+                                      const int32_t* axes, void* stream) {
+  XTC_REQUIRE(ndim >= 1 && ndim <= XTC_CUDA_MAX_DIMS, "transpose: rank %d not in [1,%d]", ndim,
+              XTC_CUDA_MAX_DIMS);
+  XTC_REQUIRE(shape && axes, "transpose: NULL shape/axes");
+  bool seen[XTC_CUDA_MAX_DIMS] = {};
+  int64_t total = 1;
+  for (int d = 0; d < ndim; ++d) {
+    XTC_REQUIRE(axes[d] >= 0 && axes[d] < ndim && !seen[axes[d]], "transpose: axes is not a permutation");
+    seen[axes[d]] = true;
+    XTC_REQUIRE(shape[d] >= 0, "transpose: negative extent");
+    total *= shape[d];
+  }
+  if (total == 0) return XTC_CUDA_OK;
+  XTC_REQUIRE(X && Y, "transpose: NULL operand");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  // Drop unit axes, then merge input axes that stay adjacent and in order in the output.
+  int64_t in_stride_full[XTC_CUDA_MAX_DIMS];
+  {
+    int64_t st = 1;
+    for (int d = ndim - 1; d >= 0; --d) { in_stride_full[d] = st; st *= shape[d]; }
+  }
+  int n = 0;
+  int64_t oshape[XTC_CUDA_MAX_DIMS], ostride[XTC_CUDA_MAX_DIMS];  // output dims: extent, input stride
+  for (int d = 0; d < ndim; ++d) {
+    const int a = axes[d];
+    if (shape[a] == 1) continue;
+    if (n > 0 && ostride[n - 1] == in_stride_full[a] * shape[a]) {
+      // previous output dim walks the input axis just outside `a`: merge
+      oshape[n - 1] *= shape[a];
+      ostride[n - 1] = in_stride_full[a];
+    } else {
+      oshape[n] = shape[a];
+      ostride[n] = in_stride_full[a];
+      ++n;
+    }
+  }
+  if (n <= 1) {  // identity permutation: plain copy
+    XTC_CUDA_CHECK(cudaMemcpyAsync(Y, X, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToDevice, s));
+    return XTC_CUDA_OK;
+  }
+  int64_t out_stride[XTC_CUDA_MAX_DIMS];
+  {
+    int64_t st = 1;
+    for (int d = n - 1; d >= 0; --d) { out_stride[d] = st; st *= oshape[d]; }
+  }
+
+  if (ostride[n - 1] == 1) {
+    // innermost axis preserved: row copies
+    RowCopyParams p;
+    const int64_t inner = oshape[n - 1];
+    bool vec = inner % 4 == 0 && aligned16(X) && aligned16(Y);
+    for (int d = 0; d < n - 1; ++d) vec = vec && (ostride[d] % 4 == 0);
+    const int unit = vec ? 4 : 1;
+    p.ndim = n - 1;
+    for (int d = 0; d < n - 1; ++d) { p.out_shape[d] = oshape[d]; p.in_stride[d] = ostride[d]; }
+    p.inner = inner / unit;
+    p.total = total / unit;
+    if (vec)
+      permute_rows_kernel<float4><<<grid_for(p.total, dev), 256, 0, s>>>(
+          reinterpret_cast<const float4*>(X), reinterpret_cast<float4*>(Y), p, 4);
+    else
+      permute_rows_kernel<float><<<grid_for(p.total, dev), 256, 0, s>>>(X, Y, p, 1);
+    XTC_CUDA_CHECK(cudaGetLastError());
+    return XTC_CUDA_OK;
+  }
+
+  // General case: find the output dim that walks the input's innermost axis.
+  int oc = -1;
+  for (int d = 0; d < n; ++d) if (ostride[d] == 1) oc = d;
+  XTC_REQUIRE(oc >= 0, "transpose: internal error (no unit-stride axis)");
+  Tile2DParams p;
+  p.R = oshape[n - 1];
+  p.in_r_stride = ostride[n - 1];
+  p.C = oshape[oc];
+  p.out_c_stride = out_stride[oc];
+  p.nbatch_dims = 0;
+  int64_t nbatch = 1;
+  for (int d = 0; d < n - 1; ++d) {
+    if (d == oc) continue;
+    p.batch_shape[p.nbatch_dims] = oshape[d];
+    p.batch_in_stride[p.nbatch_dims] = ostride[d];
+    p.batch_out_stride[p.nbatch_dims] = out_stride[d];
+    nbatch *= oshape[d];
+    ++p.nbatch_dims;
+  }
+  constexpr int TILE = 64;
+  p.tiles_r = (p.R + TILE - 1) / TILE;
+  p.tiles_c = (p.C + TILE - 1) / TILE;
+  bool vin = aligned16(X) && p.in_r_stride % 4 == 0;
+  bool vout = aligned16(Y) && p.out_c_stride % 4 == 0;
+  for (int d = 0; d < p.nbatch_dims; ++d) {
+    vin = vin && p.batch_in_stride[d] % 4 == 0;
+    vout = vout && p.batch_out_stride[d] % 4 == 0;
+  }
+  p.vec_in = vin;
+  p.vec_out = vout;
+  const int64_t blocks = nbatch * p.tiles_r * p.tiles_c;
+  XTC_REQUIRE(blocks < (1ll << 31), "transpose: too many tiles");
+  transpose_tile_kernel<TILE><<<static_cast<unsigned>(blocks), 256, 0, s>>>(X, Y, p);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_pad_f32(const float* X, float* Y, int ndim, const int64_t* shape,
+                                const int64_t* lo, const int64_t* hi, float value, void* stream) {
+  XTC_REQUIRE(ndim >= 1 && ndim <= XTC_CUDA_MAX_DIMS, "pad: rank %d not in [1,%d]", ndim,
+              XTC_CUDA_MAX_DIMS);
+  XTC_REQUIRE(shape && lo && hi, "pad: NULL shape/widths");
+  PadParams p;
+  p.ndim = ndim;
+  p.value = value;
+  int64_t total = 1, in_total = 1;
+  for (int d = 0; d < ndim; ++d) {
+    XTC_REQUIRE(shape[d] >= 0, "pad: negative extent");
+    p.in_shape[d] = shape[d];
+    p.out_shape[d] = shape[d] + lo[d] + hi[d];
+    XTC_REQUIRE(p.out_shape[d] >= 0, "pad: axis %d cropped below zero", d);
+    p.lo[d] = lo[d];
+    total *= p.out_shape[d];
+    in_total *= shape[d];
+  }
+  if (total == 0) return XTC_CUDA_OK;
+  XTC_REQUIRE(Y && (X || in_total == 0), "pad: NULL operand");
+  {
+    int64_t st = 1;
+    for (int d = ndim - 1; d >= 0; --d) { p.in_stride[d] = st; st *= shape[d]; }
+  }
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int last = ndim - 1;
+  const bool vec = aligned16(X) && aligned16(Y) && shape[last] % 4 == 0 && lo[last] % 4 == 0 &&
+                   hi[last] % 4 == 0 && in_total > 0;
+  if (vec) {
+    p.in_shape[last] /= 4;
+    p.out_shape[last] /= 4;
+    p.lo[last] /= 4;
+    for (int d = 0; d < last; ++d) p.in_stride[d] /= 4;
+    p.total = total / 4;
+    pad_kernel<float4><<<grid_for(p.total, dev), 256, 0, s>>>(
+        reinterpret_cast<const float4*>(X), reinterpret_cast<float4*>(Y), p);
+  } else {
+    p.total = total;
+    pad_kernel<float><<<grid_for(p.total, dev), 256, 0, s>>>(X, Y, p);
+  }
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}

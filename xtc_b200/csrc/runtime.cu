@@ -1,0 +1,411 @@
+// Device runtime behind the C ABI: error strings, device/memory/stream calls,
+// tensor-map encoding, plans (lowered graphs), the CUDA-event evaluation loop
+// and the tensor-pipe peak probe.
+#include <stdarg.h>
+
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace xtc {
+
+// ---------------------------------------------------------------------------
+// error string (thread local)
+// ---------------------------------------------------------------------------
+static thread_local char g_error[1024] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* get_error() { return g_error; }
+
+// ---------------------------------------------------------------------------
+// per-device state
+// ---------------------------------------------------------------------------
+static constexpr int MAX_DEVICES = 64;
+static std::mutex g_mutex;
+static int* g_status[MAX_DEVICES] = {};
+static int g_sms[MAX_DEVICES] = {};
+
+int* device_status_word(int dev) {
+  if (dev < 0 || dev >= MAX_DEVICES) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_status[dev]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+    if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+int sm_count(int dev) {
+  if (dev < 0 || dev >= MAX_DEVICES) return 1;
+  if (g_sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 1;
+    g_sms[dev] = n;
+  }
+  return g_sms[dev];
+}
+
+static void* driver_entry(const char* name) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+  if (q != cudaDriverEntryPointSuccess) return nullptr;
+  return fn;
+}
+encode_tiled_fn get_encode_tiled() {
+  static encode_tiled_fn fn = reinterpret_cast<encode_tiled_fn>(driver_entry("cuTensorMapEncodeTiled"));
+  return fn;
+}
+encode_im2col_fn get_encode_im2col() {
+  static encode_im2col_fn fn = reinterpret_cast<encode_im2col_fn>(driver_entry("cuTensorMapEncodeIm2col"));
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+  encode_tiled_fn enc = get_encode_tiled();
+  if (!enc) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return XTC_CUDA_ERR_RUNTIME;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * sizeof(float)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (%d): base=%p rows=%llu cols=%llu ld=%llu box=%ux%u",
+              static_cast<int>(r), base, (unsigned long long)rows, (unsigned long long)cols,
+              (unsigned long long)ld, box_cols, box_rows);
+    return XTC_CUDA_ERR_INVALID;
+  }
+  return XTC_CUDA_OK;
+}
+
+}  // namespace xtc
+
+using namespace xtc;
+
+// ---------------------------------------------------------------------------
+// device / memory / streams
+// ---------------------------------------------------------------------------
+extern "C" int xtc_cuda_abi_version(void) { return XTC_CUDA_ABI_VERSION; }
+extern "C" const char* xtc_cuda_last_error(void) { return get_error(); }
+
+extern "C" int xtc_cuda_device_count(int* count) {
+  XTC_REQUIRE(count != nullptr, "device_count: NULL");
+  *count = 0;
+  XTC_CUDA_CHECK(cudaGetDeviceCount(count));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_set_device(int device) {
+  XTC_CUDA_CHECK(cudaSetDevice(device));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_get_device(int* device) {
+  XTC_REQUIRE(device != nullptr, "get_device: NULL");
+  XTC_CUDA_CHECK(cudaGetDevice(device));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_device_name(int device, char* buf, size_t buf_len) {
+  XTC_REQUIRE(buf && buf_len > 0, "device_name: NULL buffer");
+  cudaDeviceProp prop;
+  XTC_CUDA_CHECK(cudaGetDeviceProperties(&prop, device));
+  snprintf(buf, buf_len, "%s", prop.name);
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_malloc(void** ptr, size_t bytes) {
+  XTC_REQUIRE(ptr != nullptr, "malloc: NULL");
+  *ptr = nullptr;
+  if (bytes == 0) bytes = 256;
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    set_error("malloc: out of device memory (%zu bytes)", bytes);
+    return XTC_CUDA_ERR_NOMEM;
+  }
+  XTC_CUDA_CHECK(e);
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_free(void* ptr) {
+  if (ptr) XTC_CUDA_CHECK(cudaFree(ptr));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_host_alloc(void** ptr, size_t bytes) {
+  XTC_REQUIRE(ptr != nullptr, "host_alloc: NULL");
+  *ptr = nullptr;
+  if (bytes == 0) bytes = 256;
+  XTC_CUDA_CHECK(cudaMallocHost(ptr, bytes));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_host_free(void* ptr) {
+  if (ptr) XTC_CUDA_CHECK(cudaFreeHost(ptr));
+  return XTC_CUDA_OK;
+}
+static int copy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind, void* stream) {
+  if (bytes == 0) return XTC_CUDA_OK;
+  XTC_REQUIRE(dst && src, "memcpy: NULL pointer");
+  XTC_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, kind, static_cast<cudaStream_t>(stream)));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream) {
+  return copy(dst, src, bytes, cudaMemcpyHostToDevice, stream);
+}
+extern "C" int xtc_cuda_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream) {
+  return copy(dst, src, bytes, cudaMemcpyDeviceToHost, stream);
+}
+extern "C" int xtc_cuda_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream) {
+  return copy(dst, src, bytes, cudaMemcpyDeviceToDevice, stream);
+}
+extern "C" int xtc_cuda_memset(void* dst, int byte_value, size_t bytes, void* stream) {
+  if (bytes == 0) return XTC_CUDA_OK;
+  XTC_REQUIRE(dst != nullptr, "memset: NULL pointer");
+  XTC_CUDA_CHECK(cudaMemsetAsync(dst, byte_value, bytes, static_cast<cudaStream_t>(stream)));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_stream_create(void** stream) {
+  XTC_REQUIRE(stream != nullptr, "stream_create: NULL");
+  cudaStream_t s;
+  XTC_CUDA_CHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  *stream = s;
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_stream_destroy(void* stream) {
+  if (stream) XTC_CUDA_CHECK(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_stream_synchronize(void* stream) {
+  XTC_CUDA_CHECK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_device_synchronize(void) {
+  XTC_CUDA_CHECK(cudaDeviceSynchronize());
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_device_status(int* status) {
+  XTC_REQUIRE(status != nullptr, "device_status: NULL");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  int* word = device_status_word(dev);
+  XTC_REQUIRE(word != nullptr, "device_status: status word unavailable");
+  XTC_CUDA_CHECK(cudaDeviceSynchronize());
+  XTC_CUDA_CHECK(cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status != 0) {
+    XTC_CUDA_CHECK(cudaMemset(word, 0, sizeof(int)));
+    set_error("a kernel's bounded wait gave up (device status %d)", *status);
+  }
+  return XTC_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// plans
+// ---------------------------------------------------------------------------
+struct xtc_cuda_plan {
+  std::vector<xtc_cuda_step> steps;
+  int n_inputs = 0, n_outputs = 0;
+  std::vector<size_t> slot_bytes;
+  std::vector<void*> owned;       // intermediates, index = slot - n_io (nullptr for io slots)
+  std::vector<void*> workspace;   // per step
+  std::vector<size_t> workspace_bytes;
+  std::vector<void*> staging;     // device copies of io slots for run_host (lazy)
+  int device = 0;
+};
+
+static int step_workspace(const xtc_cuda_step& s, size_t* bytes) {
+  *bytes = 0;
+  if (s.kind == XTC_CUDA_STEP_GEMM)
+    return xtc_cuda_gemm_workspace_bytes(s.dims[0], s.dims[1], s.dims[2], s.flags, &s.cfg, bytes);
+  if (s.kind == XTC_CUDA_STEP_CONV2D)
+    return xtc_cuda_conv2d_workspace_bytes(s.dims[0], s.dims[1], s.dims[2], s.dims[3], s.dims[4],
+                                           s.dims[5], s.aux0[0], (int)s.aux0[1], (int)s.aux0[2],
+                                           (int)s.aux1[0], (int)s.aux1[1], (int)s.aux1[2],
+                                           (int)s.aux1[3], &s.cfg, bytes);
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_plan_create(xtc_cuda_plan** plan, const xtc_cuda_step* steps, int n_steps,
+                                    int n_inputs, int n_outputs, int n_slots,
+                                    const size_t* slot_bytes) {
+  XTC_REQUIRE(plan != nullptr, "plan_create: NULL plan");
+  *plan = nullptr;
+  XTC_REQUIRE(steps && n_steps > 0, "plan_create: no steps");
+  XTC_REQUIRE(n_inputs >= 0 && n_outputs > 0 && n_slots >= n_inputs + n_outputs && slot_bytes,
+              "plan_create: bad slot counts (%d inputs, %d outputs, %d slots)", n_inputs,
+              n_outputs, n_slots);
+  for (int i = 0; i < n_steps; ++i) {
+    const xtc_cuda_step& s = steps[i];
+    XTC_REQUIRE(s.kind >= XTC_CUDA_STEP_GEMM && s.kind <= XTC_CUDA_STEP_COPY,
+                "plan_create: step %d has unknown kind %d", i, s.kind);
+    XTC_REQUIRE(s.in0 >= 0 && s.in0 < n_slots && s.out >= 0 && s.out < n_slots &&
+                    s.in1 >= -1 && s.in1 < n_slots,
+                "plan_create: step %d references a slot out of range", i);
+    XTC_REQUIRE(s.out >= n_inputs, "plan_create: step %d writes a graph input", i);
+  }
+  xtc_cuda_plan* p = new xtc_cuda_plan();
+  p->steps.assign(steps, steps + n_steps);
+  p->n_inputs = n_inputs;
+  p->n_outputs = n_outputs;
+  p->slot_bytes.assign(slot_bytes, slot_bytes + n_slots);
+  p->owned.assign(n_slots, nullptr);
+  p->workspace.assign(n_steps, nullptr);
+  p->workspace_bytes.assign(n_steps, 0);
+  p->staging.assign(n_inputs + n_outputs, nullptr);
+  int rc = XTC_CUDA_OK;
+  if (cudaGetDevice(&p->device) != cudaSuccess) rc = XTC_CUDA_ERR_RUNTIME;
+  for (int s = n_inputs + n_outputs; s < n_slots && rc == XTC_CUDA_OK; ++s)
+    rc = xtc_cuda_malloc(&p->owned[s], p->slot_bytes[s]);
+  for (int i = 0; i < n_steps && rc == XTC_CUDA_OK; ++i) {
+    size_t need = 0;
+    rc = step_workspace(p->steps[i], &need);
+    if (rc == XTC_CUDA_OK && need > 0) {
+      rc = xtc_cuda_malloc(&p->workspace[i], need);
+      p->workspace_bytes[i] = need;
+    }
+  }
+  if (rc != XTC_CUDA_OK) {
+    xtc_cuda_plan_destroy(p);
+    return rc;
+  }
+  *plan = p;
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_plan_destroy(xtc_cuda_plan* plan) {
+  if (!plan) return XTC_CUDA_OK;
+  for (void* q : plan->owned) if (q) cudaFree(q);
+  for (void* q : plan->workspace) if (q) cudaFree(q);
+  for (void* q : plan->staging) if (q) cudaFree(q);
+  delete plan;
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_plan_step_count(const xtc_cuda_plan* plan, int* n_steps) {
+  XTC_REQUIRE(plan && n_steps, "plan_step_count: NULL");
+  *n_steps = static_cast<int>(plan->steps.size());
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* stream) {
+  XTC_REQUIRE(plan && io, "plan_run: NULL plan or io");
+  const int n_io = plan->n_inputs + plan->n_outputs;
+  auto slot = [&](int s) -> void* { return s < n_io ? io[s] : plan->owned[s]; };
+  for (size_t i = 0; i < plan->steps.size(); ++i) {
+    const xtc_cuda_step& s = plan->steps[i];
+    const float* in0 = static_cast<const float*>(slot(s.in0));
+    const float* in1 = s.in1 >= 0 ? static_cast<const float*>(slot(s.in1)) : nullptr;
+    float* out = static_cast<float*>(slot(s.out));
+    int rc = XTC_CUDA_OK;
+    switch (s.kind) {
+      case XTC_CUDA_STEP_GEMM:
+        rc = xtc_cuda_gemm_f32(in0, in1, out, s.dims[0], s.dims[1], s.dims[2], s.dims[3],
+                               s.dims[4], s.dims[5], s.flags, s.relu_threshold, &s.cfg,
+                               plan->workspace[i], plan->workspace_bytes[i], stream);
+        break;
+      case XTC_CUDA_STEP_CONV2D:
+        rc = xtc_cuda_conv2d_nhwc_f32(in0, in1, out, s.dims[0], s.dims[1], s.dims[2], s.dims[3],
+                                      s.dims[4], s.dims[5], s.aux0[0], (int)s.aux0[1],
+                                      (int)s.aux0[2], (int)s.aux1[0], (int)s.aux1[1],
+                                      (int)s.aux1[2], (int)s.aux1[3], s.flags, s.relu_threshold,
+                                      &s.cfg, plan->workspace[i], plan->workspace_bytes[i], stream);
+        break;
+      case XTC_CUDA_STEP_TRANSPOSE: {
+        int32_t axes[XTC_CUDA_MAX_DIMS];
+        for (int d = 0; d < s.ndim; ++d) axes[d] = static_cast<int32_t>(s.aux0[d]);
+        rc = xtc_cuda_transpose_f32(in0, out, s.ndim, s.dims, axes, stream);
+        break;
+      }
+      case XTC_CUDA_STEP_PAD:
+        rc = xtc_cuda_pad_f32(in0, out, s.ndim, s.dims, s.aux0, s.aux1, s.pad_value, stream);
+        break;
+      case XTC_CUDA_STEP_RELU:
+        rc = xtc_cuda_relu_f32(in0, out, s.dims[0], s.relu_threshold, stream);
+        break;
+      case XTC_CUDA_STEP_COPY:
+        rc = xtc_cuda_memcpy_d2d(out, in0, static_cast<size_t>(s.dims[0]) * 4, stream);
+        break;
+      default:
+        set_error("plan_run: unknown step kind %d", s.kind);
+        rc = XTC_CUDA_ERR_INVALID;
+    }
+    if (rc != XTC_CUDA_OK) return rc;
+  }
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_plan_run_host(xtc_cuda_plan* plan, void* const* io) {
+  XTC_REQUIRE(plan && io, "plan_run_host: NULL plan or io");
+  const int n_io = plan->n_inputs + plan->n_outputs;
+  int rc;
+  for (int s = 0; s < n_io; ++s) {
+    XTC_REQUIRE(io[s] != nullptr, "plan_run_host: io[%d] is NULL", s);
+    if (!plan->staging[s] && (rc = xtc_cuda_malloc(&plan->staging[s], plan->slot_bytes[s])))
+      return rc;
+  }
+  for (int s = 0; s < plan->n_inputs; ++s)
+    if ((rc = xtc_cuda_memcpy_h2d(plan->staging[s], io[s], plan->slot_bytes[s], nullptr))) return rc;
+  if ((rc = xtc_cuda_plan_run(plan, plan->staging.data(), nullptr))) return rc;
+  for (int s = plan->n_inputs; s < n_io; ++s)
+    if ((rc = xtc_cuda_memcpy_d2h(io[s], plan->staging[s], plan->slot_bytes[s], nullptr))) return rc;
+  XTC_CUDA_CHECK(cudaStreamSynchronize(nullptr));
+  int status = 0;
+  if ((rc = xtc_cuda_device_status(&status))) return rc;
+  return status == 0 ? XTC_CUDA_OK : XTC_CUDA_ERR_DEVICE_TIMEOUT;
+}
+
+extern "C" int xtc_cuda_evaluate(xtc_cuda_plan* plan, void* const* io, int repeat, int number,
+                                 int min_repeat_ms, double* results) {
+  XTC_REQUIRE(plan && io && results, "evaluate: NULL argument");
+  XTC_REQUIRE(repeat > 0 && number >= 0 && min_repeat_ms >= 0, "evaluate: bad repeat/number/min_repeat_ms");
+  cudaStream_t s;
+  XTC_CUDA_CHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  cudaEvent_t e0, e1;
+  XTC_CUDA_CHECK(cudaEventCreate(&e0));
+  XTC_CUDA_CHECK(cudaEventCreate(&e1));
+  int rc = XTC_CUDA_OK;
+  if (number > 0) {
+    rc = xtc_cuda_plan_run(plan, io, s);  // warm-up, untimed
+    if (rc == XTC_CUDA_OK && cudaStreamSynchronize(s) != cudaSuccess) rc = XTC_CUDA_ERR_RUNTIME;
+  } else {
+    number = 1;
+  }
+  for (int r = 0; r < repeat && rc == XTC_CUDA_OK; ++r) {
+    long attempts = number;
+    for (;;) {
+      cudaEventRecord(e0, s);
+      for (long a = 0; a < attempts && rc == XTC_CUDA_OK; ++a) rc = xtc_cuda_plan_run(plan, io, s);
+      cudaEventRecord(e1, s);
+      if (rc != XTC_CUDA_OK) break;
+      cudaError_t e = cudaEventSynchronize(e1);
+      if (e != cudaSuccess) {
+        set_error("evaluate: %s", cudaGetErrorString(e));
+        rc = XTC_CUDA_ERR_RUNTIME;
+        break;
+      }
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      if (ms >= static_cast<float>(min_repeat_ms) || attempts > (1l << 24)) {
+        results[r] = static_cast<double>(ms) * 1e-3 / static_cast<double>(attempts);
+        break;
+      }
+      attempts *= 2;
+    }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaStreamDestroy(s);
+  if (rc != XTC_CUDA_OK) return rc;
+  int status = 0;
+  if ((rc = xtc_cuda_device_status(&status))) return rc;
+  return status == 0 ? XTC_CUDA_OK : XTC_CUDA_ERR_DEVICE_TIMEOUT;
+}
