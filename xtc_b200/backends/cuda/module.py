@@ -1,0 +1,244 @@
+"""Module, Evaluator and Executor of the CUDA backend.
+
+Same contracts as the reference's host and GPU targets
+(``targets/host/HostModule.py:26-135``, ``HostEvaluator.py:28-120``,
+``targets/accelerator/gpu/GPUEvaluator.py:47-112``): ``evaluate()`` returns
+``(results, code, message)`` with ``repeat`` floats of seconds per call,
+``validate=True`` first compares one run against the graph's NumPy evaluation
+with ``np.allclose``, caller-provided output arrays are written in place.
+
+Differences, all deliberate: inputs live in device memory during timing (the
+reference maps host memory into the GPU, ``GPUEvaluator.py:67-78``), time is
+CUDA-event time of the launches (``xtc_cuda_evaluate``), and ``rtol`` / ``atol``
+are configurable because TF32 results on non-integer data do not satisfy
+NumPy's default tolerances.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+from typing import Any, Callable
+
+import numpy as np
+
+from ... import capi
+from ...capi import byref, c_void_p
+from ...runtimes.cuda import CudaDevice, NDArray
+from ...utils.numpy import np_init
+from .lowering import Plan
+
+
+class PlanHandle:
+    """Owns one ``xtc_cuda_plan`` on one device."""
+
+    def __init__(self, plan: Plan, device: CudaDevice) -> None:
+        self.plan = plan
+        self.device = device
+        self.lib = device.lib
+        device.activate()
+        n = len(plan.steps)
+        steps = (capi.Step * n)(*[s.to_c() for s in plan.steps])
+        sizes = (ctypes.c_size_t * len(plan.slot_bytes))(*plan.slot_bytes)
+        self.handle = c_void_p()
+        capi.check(self.lib.xtc_cuda_plan_create(byref(self.handle), steps, n, plan.n_inputs,
+                                                 plan.n_outputs, len(plan.slot_bytes), sizes))
+
+    def _io(self, pointers: list[int]) -> ctypes.Array:
+        assert len(pointers) == self.plan.n_inputs + self.plan.n_outputs
+        return (c_void_p * len(pointers))(*pointers)
+
+    def run(self, pointers: list[int], stream: int | None = None) -> None:
+        """Launch on device pointers (asynchronous on ``stream``)."""
+        self.device.activate()
+        capi.check(self.lib.xtc_cuda_plan_run(self.handle, self._io(pointers),
+                                              c_void_p(stream) if stream else None))
+
+    def run_host(self, arrays: list[np.ndarray]) -> None:
+        """Host arrays in, host arrays out (copies inside), synchronous."""
+        self.device.activate()
+        ptrs = [a.ctypes.data for a in arrays]
+        capi.check(self.lib.xtc_cuda_plan_run_host(self.handle, self._io(ptrs)))
+
+    def evaluate(self, pointers: list[int], repeat: int, number: int,
+                 min_repeat_ms: int) -> list[float]:
+        self.device.activate()
+        results = (ctypes.c_double * repeat)()
+        capi.check(self.lib.xtc_cuda_evaluate(self.handle, self._io(pointers), repeat, number,
+                                              min_repeat_ms, results))
+        return [float(x) for x in results]
+
+    def close(self) -> None:
+        if self.handle is not None and self.handle.value:
+            self.device.activate()
+            self.lib.xtc_cuda_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class CudaModule:
+    def __init__(self, name: str, payload_name: str, file_name: str, file_type: str,
+                 plan: Plan, graph: Any = None, backend: Any = None, **kwargs: Any) -> None:
+        self._name = name
+        self._payload_name = payload_name
+        self._file_name = file_name
+        self._file_type = file_type
+        self._plan = plan
+        self._graph = graph
+        self._backend = backend
+        self._bare_ptr = True
+        self._np_inputs_spec = backend.np_inputs_spec if backend is not None else None
+        self._np_outputs_spec = backend.np_outputs_spec if backend is not None else None
+        self._reference_impl = backend.reference_impl if backend is not None else None
+
+    name = property(lambda self: self._name)
+    payload_name = property(lambda self: self._payload_name)
+    file_name = property(lambda self: self._file_name)
+    file_type = property(lambda self: self._file_type)
+    plan = property(lambda self: self._plan)
+    graph = property(lambda self: self._graph)
+
+    def export(self) -> None:
+        raise NotImplementedError("export is not implemented (nor is it in the reference's host module)")
+
+    def get_evaluator(self, **kwargs: Any) -> "CudaEvaluator":
+        return CudaEvaluator(self, **kwargs)
+
+    def get_executor(self, **kwargs: Any) -> "CudaExecutor":
+        return CudaExecutor(self, **kwargs)
+
+
+class CudaEvaluator:
+    def __init__(self, module: CudaModule, **kwargs: Any) -> None:
+        self._module = module
+        self._repeat = kwargs.get("repeat", 1)
+        self._min_repeat_ms = kwargs.get("min_repeat_ms", 100)
+        self._number = kwargs.get("number", 1)
+        self._validate = kwargs.get("validate", False)
+        self._parameters = kwargs.get("parameters")
+        self._init_zero = kwargs.get("init_zero", False)
+        self._np_inputs_spec = kwargs.get("np_inputs_spec", module._np_inputs_spec)
+        self._np_outputs_spec = kwargs.get("np_outputs_spec", module._np_outputs_spec)
+        self._reference_impl = kwargs.get("reference_impl", module._reference_impl)
+        self._pmu_counters = kwargs.get("pmu_counters", [])
+        self._rtol = kwargs.get("rtol", 1e-5)
+        self._atol = kwargs.get("atol", 1e-8)
+        device = kwargs.get("device", kwargs.get("runtime"))
+        self._device = device if isinstance(device, CudaDevice) else CudaDevice(int(device or 0))
+
+    @property
+    def module(self) -> CudaModule:
+        return self._module
+
+    def _host_parameters(self) -> tuple[list[Any], list[Any]]:
+        """(inputs, outputs) as NumPy arrays or device-resident NDArrays."""
+        if self._parameters is None:
+            assert self._np_inputs_spec is not None and self._np_outputs_spec is not None
+            init = np.zeros if self._init_zero else np.empty
+            ins = [np_init(spec["shape"], spec["dtype"]) for spec in self._np_inputs_spec()]
+            outs = [init(shape=spec["shape"], dtype=spec["dtype"]) for spec in self._np_outputs_spec()]
+            return ins, outs
+        ins, outs = self._parameters
+        return list(ins), list(outs)
+
+    def evaluate(self) -> tuple[list[float], int, str]:
+        plan = self._module.plan
+        dev = self._device
+        try:
+            if not dev.detect_accelerator():
+                return ([], 1, f"no CUDA device {dev.ordinal} available")
+            handle = PlanHandle(plan, dev)
+        except (capi.XtcCudaError, RuntimeError) as e:
+            return ([], 1, f"Error creating the plan: {e}")
+        owned: list[c_void_p] = []
+        try:
+            ins, outs = self._host_parameters()
+            pointers: list[int] = []
+            for arr, nbytes in zip(ins + outs, plan.slot_bytes):
+                if isinstance(arr, NDArray) and arr.is_on_device():
+                    assert arr.nbytes == nbytes, "parameter size does not match the graph"
+                    pointers.append(arr.data)
+                    continue
+                host = arr.numpy() if isinstance(arr, NDArray) else arr
+                assert isinstance(host, np.ndarray) and host.nbytes == nbytes, (
+                    "parameter size does not match the graph")
+                ptr = dev.memory_allocate(nbytes)
+                owned.append(ptr)
+                pointers.append(int(ptr.value))
+            n_in = plan.n_inputs
+            for arr, ptr, layout in zip(ins, pointers[:n_in], plan.input_layouts):
+                if not (isinstance(arr, NDArray) and arr.is_on_device()):
+                    host = arr.numpy() if isinstance(arr, NDArray) else arr
+                    if layout is not None and list(layout) == [1, 0]:
+                        host = host.T  # the graph declares this input as stored transposed
+                    host = np.ascontiguousarray(host)
+                    dev.memory_copy_to(c_void_p(ptr), host, host.nbytes)
+            if self._init_zero:
+                for ptr, nbytes in zip(pointers[n_in:], plan.slot_bytes[n_in:]):
+                    dev.memory_fill_zero(c_void_p(ptr), nbytes)
+
+            def read_outputs() -> list[np.ndarray]:
+                result = []
+                for i, (arr, ptr) in enumerate(zip(outs, pointers[n_in:])):
+                    shape = plan.slot_shapes[n_in + i]
+                    host = np.empty(shape, dtype=np.float32)
+                    dev.memory_copy_from(c_void_p(ptr), host, host.nbytes)
+                    result.append(host)
+                return result
+
+            if self._validate:
+                assert self._reference_impl is not None
+                ref_ins = [a.numpy() if isinstance(a, NDArray) else np.asarray(a) for a in ins]
+                ref_outs = [np.empty(plan.slot_shapes[n_in + i], dtype=np.float32)
+                            for i in range(plan.n_outputs)]
+                self._reference_impl(*ref_ins, *ref_outs)
+                handle.run(pointers)
+                dev.synchronize()
+                if dev.status() != 0:
+                    return ([], 1, "Error in execution: a kernel's bounded wait gave up")
+                for ref, got in zip(ref_outs, read_outputs()):
+                    if not np.allclose(ref, got, rtol=self._rtol, atol=self._atol):
+                        return ([], 1, "Error in validation: outputs differ")
+
+            if self._pmu_counters:
+                # Hardware counters need a profiler attached to the process; without one
+                # every counter reads as unavailable, which the reference reports as -1
+                # (csrcs/runtimes/host/evaluate_perf.c:110-113).
+                handle.run(pointers)
+                dev.synchronize()
+                results = [-1.0] * (self._repeat * len(self._pmu_counters))
+            else:
+                results = handle.evaluate(pointers, self._repeat, self._number, self._min_repeat_ms)
+
+            if self._parameters is not None:
+                for arr, got in zip(outs, read_outputs()):
+                    if isinstance(arr, np.ndarray):
+                        np.copyto(arr, got.reshape(arr.shape))
+            return (results, 0, "")
+        except capi.XtcCudaError as e:
+            return ([], 1, f"Error in execution: {e}")
+        finally:
+            for ptr in owned:
+                try:
+                    dev.memory_free(ptr)
+                except capi.XtcCudaError:
+                    pass
+            handle.close()
+
+
+class CudaExecutor:
+    def __init__(self, module: CudaModule, **kwargs: Any) -> None:
+        self._evaluator = CudaEvaluator(module, repeat=1, min_repeat_ms=0, number=1, **kwargs)
+
+    def execute(self) -> int:
+        _, code, _ = self._evaluator.evaluate()
+        return code
+
+    @property
+    def module(self) -> CudaModule:
+        return self._evaluator.module
