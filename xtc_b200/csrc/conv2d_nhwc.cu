@@ -113,6 +113,7 @@ int launch_conv_tc(const ConvArgs& a) {
   p.tiles_n = static_cast<int>((N + BN - 1) / BN);
   p.conv_cblocks = static_cast<int>((a.C + BK - 1) / BK);
   p.k_blocks = static_cast<int>(a.R * a.S) * p.conv_cblocks;
+  p.chunk_kblocks = p.k_blocks;
   p.relu = a.relu;
   p.relu_threshold = a.thr;
   p.status = device_status_word(dev);

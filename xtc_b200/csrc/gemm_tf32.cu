@@ -131,6 +131,8 @@ int launch_tc(const LaunchArgs& a) {
   p.tiles_m = static_cast<int>((a.M + BM - 1) / BM);
   p.tiles_n = static_cast<int>((a.N + BN - 1) / BN);
   p.k_blocks = static_cast<int>((a.K + BK - 1) / BK);
+  // 3xTF32: hand the accumulator to the fp32 register sum every 256 elements of K
+  p.chunk_kblocks = SPLIT3 ? (256 / BK) : p.k_blocks;
   p.relu = a.relu;
   p.relu_threshold = a.thr;
   p.status = device_status_word(dev);
@@ -164,9 +166,10 @@ int dispatch_major(const LaunchArgs& a) {
 template <bool SPLIT3, bool TMA_STORE>
 int dispatch_tile(const LaunchArgs& a, int tile_n, int tile_k) {
   const int ks = tile_k == 64 ? 2 : 1;
-  if (SPLIT3 && ks == 2 && tile_n == 256) {
-    // 2 x (128+256) x 64 x 4 bytes per stage leaves a single stage: not a pipeline
-    set_error("gemm: tile 128x256x64 is not available in 3xTF32 mode");
+  if (SPLIT3 && tile_n == 256) {
+    // the epilogue keeps the running fp32 sum of a whole tile row in registers:
+    // 128 columns per thread is the most that fits
+    set_error("gemm: tile_n=256 is not available in 3xTF32 mode (use 64 or 128)");
     return XTC_CUDA_ERR_UNSUPPORTED;
   }
   switch (tile_n) {
@@ -177,8 +180,10 @@ int dispatch_tile(const LaunchArgs& a, int tile_n, int tile_k) {
       return ks == 1 ? dispatch_major<128, 1, SPLIT3, TMA_STORE>(a)
                      : dispatch_major<128, 2, SPLIT3, TMA_STORE>(a);
     case 256:
-      if (ks == 1) return dispatch_major<256, 1, SPLIT3, TMA_STORE>(a);
-      if constexpr (!SPLIT3) return dispatch_major<256, 2, SPLIT3, TMA_STORE>(a);
+      if constexpr (!SPLIT3) {
+        return ks == 1 ? dispatch_major<256, 1, SPLIT3, TMA_STORE>(a)
+                       : dispatch_major<256, 2, SPLIT3, TMA_STORE>(a);
+      }
   }
   set_error("gemm: unsupported tile_n=%d tile_k=%d (tile_n in {64,128,256}, tile_k in {32,64})",
             tile_n, tile_k);
@@ -269,7 +274,8 @@ extern "C" int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64
   if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
 
   XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM, "gemm: tile_m=%d unsupported (only %d)", c.tile_m, BM);
-  const int tile_n = c.tile_n ? c.tile_n : default_tile_n(M, N, sm_count(dev));
+  int tile_n = c.tile_n ? c.tile_n : default_tile_n(M, N, sm_count(dev));
+  if (c.precision == XTC_CUDA_PRECISION_3XTF32 && c.tile_n == 0 && tile_n > 128) tile_n = 128;
   const int tile_k = c.tile_k ? c.tile_k : 32;
   const bool tma_store = (c.epilogue == 2) && tma_addressable(C, ldc);
 

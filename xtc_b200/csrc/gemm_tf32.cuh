@@ -37,6 +37,7 @@ struct GemmParams {
   int64_t ldc;
   int M, N, K;
   int tiles_m, tiles_n, k_blocks;
+  int chunk_kblocks;  // K stages accumulated in one TMEM buffer before the epilogue takes it
   int relu;
   float relu_threshold;
   int* status;
@@ -210,67 +211,71 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
+    // The K loop of a tile is cut into chunks of p.chunk_kblocks stages; each
+    // chunk accumulates into the next TMEM buffer and is handed to the epilogue.
+    // The TF32 mode uses one chunk per tile.  The 3xTF32 mode uses short chunks
+    // that the epilogue sums in fp32 registers: the tensor core truncates when it
+    // adds into its accumulator, and a short chain keeps that error below 1e-5.
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
-      int local = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
-        const int acc = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
-          atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_DRAIN);
-          failed = true;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&full[stage], phase)) {
-            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+      int acc_iter = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+        for (int kb0 = 0; kb0 < p.k_blocks && !failed; kb0 += p.chunk_kblocks, ++acc_iter) {
+          const int acc = acc_iter & 1;
+          const uint32_t acc_phase = (acc_iter >> 1) & 1;
+          if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_DRAIN);
             failed = true;
             break;
           }
           tc_fence_after();
-          const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * L::STAGE_BYTES);
-          const uint32_t sB = sA + L::A_BYTES;
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          const int kb_end = min(kb0 + p.chunk_kblocks, p.k_blocks);
+          for (int kb = kb0; kb < kb_end; ++kb) {
+            if (!mbar_wait(&full[stage], phase)) {
+              atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+              failed = true;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * L::STAGE_BYTES);
+            const uint32_t sB = sA + L::A_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < BK / 8; ++kk) {
-            uint32_t aoff, boff;
-            if (!A_MN) aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-            else aoff = kk * 1024;
-            if (B_MN) boff = kk * 1024;
-            else boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
-            const uint32_t acc_in = (kb | kk) != 0;
-            if (!SPLIT3) {
-              uint64_t ad = A_MN ? umma_smem_desc(sA + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                                 : umma_smem_desc(sA + aoff, 16, 1024, UMMA_SWIZZLE_128B);
-              uint64_t bd = B_MN ? umma_smem_desc(sB + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                                 : umma_smem_desc(sB + boff, 16, 1024, UMMA_SWIZZLE_128B);
-              umma_tf32(d_tmem, ad, bd, idesc, acc_in);
-            } else {
-              const uint32_t lo = L::A_BYTES + L::B_BYTES;
-              uint64_t ah = A_MN ? umma_smem_desc(sA + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                                 : umma_smem_desc(sA + aoff, 16, 1024, UMMA_SWIZZLE_128B);
-              uint64_t bh = B_MN ? umma_smem_desc(sB + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                                 : umma_smem_desc(sB + boff, 16, 1024, UMMA_SWIZZLE_128B);
-              uint64_t al = A_MN ? umma_smem_desc(sA + lo + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                                 : umma_smem_desc(sA + lo + aoff, 16, 1024, UMMA_SWIZZLE_128B);
-              uint64_t bl = B_MN ? umma_smem_desc(sB + lo + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                                 : umma_smem_desc(sB + lo + boff, 16, 1024, UMMA_SWIZZLE_128B);
-              // small cross terms first, the dominant hi*hi product last
-              umma_tf32(d_tmem, al, bh, idesc, acc_in);
-              umma_tf32(d_tmem, ah, bl, idesc, 1);
-              umma_tf32(d_tmem, ah, bh, idesc, 1);
+            for (int kk = 0; kk < BK / 8; ++kk) {
+              uint32_t aoff, boff;
+              if (!A_MN) aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+              else aoff = kk * 1024;
+              if (B_MN) boff = kk * 1024;
+              else boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
+              const uint32_t acc_in = (kb > kb0) || (kk != 0);
+              auto desc_a = [&](uint32_t base) {
+                return A_MN ? umma_smem_desc(base + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                            : umma_smem_desc(base + aoff, 16, 1024, UMMA_SWIZZLE_128B);
+              };
+              auto desc_b = [&](uint32_t base) {
+                return B_MN ? umma_smem_desc(base + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                            : umma_smem_desc(base + boff, 16, 1024, UMMA_SWIZZLE_128B);
+              };
+              if (!SPLIT3) {
+                umma_tf32(d_tmem, desc_a(sA), desc_b(sB), idesc, acc_in);
+              } else {
+                const uint32_t lo = L::A_BYTES + L::B_BYTES;
+                // small cross terms first, the dominant hi*hi product last
+                umma_tf32(d_tmem, desc_a(sA + lo), desc_b(sB), idesc, acc_in);
+                umma_tf32(d_tmem, desc_a(sA), desc_b(sB + lo), idesc, 1);
+                umma_tf32(d_tmem, desc_a(sA), desc_b(sB), idesc, 1);
+              }
+            }
+            tc_commit(&empty[stage]);  // stage reusable once these MMAs retire
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1;
             }
           }
-          tc_commit(&empty[stage]);  // stage reusable once these MMAs retire
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          if (!failed) tc_commit(&acc_full[acc]);
         }
-        if (!failed) tc_commit(&acc_full[acc]);
       }
     }
   } else {
@@ -278,54 +283,40 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const int epi_id = warp - 2;
     float* stage_buf = reinterpret_cast<float*>(epi + epi_id * (2 * 32 * 32 * 4));
-    int local = 0;
+    int acc_iter = 0;
     int buf = 0;
     const bool vec_ok = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-    for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
-      int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-      const int m0 = tm * BM, n0 = tn * BN;
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1;
-      if (!mbar_wait(&acc_full[acc], acc_phase)) {
-        if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
-        failed = true;
-        break;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+
+    // relu + store of one 32-row x 32-column block held one row per lane
+    auto store_block = [&](uint32_t (&r)[32], int m0, int col0) {
+      if (p.relu) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), p.relu_threshold));
       }
-      tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
-        tmem_ld_wait();
-        if (p.relu) {
+      if (TMA_STORE) {
+        // Stage the block in shared memory with the 128-byte swizzle the store's
+        // tensor map expects, then one lane issues the bulk store.
+        float* sb = stage_buf + buf * (32 * 32);
+        tma_store_wait_read<1>();  // the buffer used two stores ago is free
+        __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), p.relu_threshold));
+        for (int j = 0; j < 8; ++j) {
+          const int chunk = j ^ (lane & 7);
+          float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          *reinterpret_cast<float4*>(sb + lane * 32 + chunk * 4) = v;
         }
-        const int col0 = n0 + c * 32;
-        if (TMA_STORE) {
-          // Stage the 32x32 block in shared memory with the 128-byte swizzle
-          // the store's tensor map expects, then one lane issues the store.
-          float* sb = stage_buf + buf * (32 * 32);
-          tma_store_wait_read<1>();  // the buffer used two stores ago is free
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int chunk = j ^ (lane & 7);
-            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-            *reinterpret_cast<float4*>(sb + lane * 32 + chunk * 4) = v;
-          }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M) {
-            tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
-          }
-          if (lane == 0) tma_store_commit();
-          buf ^= 1;
-        } else if (row < p.M) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M)
+          tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
+        if (lane == 0) tma_store_commit();
+        buf ^= 1;
+      } else {
+        const int row = m0 + quad * 32 + lane;
+        if (row < p.M) {
           float* dst = p.C + static_cast<int64_t>(row) * p.ldc + col0;
           if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
@@ -341,10 +332,58 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
-      // all TMEM reads of this warp are complete (wait::ld above): release the buffer
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    };
+
+    for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      float sum[SPLIT3 ? BN : 1];
+      if (SPLIT3) {
+#pragma unroll
+        for (int i = 0; i < (SPLIT3 ? BN : 1); ++i) sum[i] = 0.f;
+      }
+      for (int kb0 = 0; kb0 < p.k_blocks && !failed; kb0 += p.chunk_kblocks, ++acc_iter) {
+        const int acc = acc_iter & 1;
+        const uint32_t acc_phase = (acc_iter >> 1) & 1;
+        if (!mbar_wait(&acc_full[acc], acc_phase)) {
+          if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        if (SPLIT3) {
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + lane_base + acc * BN + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sum[(SPLIT3 ? c * 32 : 0) + (SPLIT3 ? i : 0)] += __uint_as_float(r[i]);
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + lane_base + acc * BN + c * 32, r);
+            tmem_ld_wait();
+            store_block(r, m0, n0 + c * 32);
+          }
+        }
+        // all TMEM reads of this warp are complete (wait::ld above): release the buffer
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      }
+      if (SPLIT3 && !failed) {
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(sum[(SPLIT3 ? c * 32 : 0) + (SPLIT3 ? i : 0)]);
+          store_block(r, m0, n0 + c * 32);
+        }
+      }
     }
     if (TMA_STORE) tma_store_wait_all<0>();
   }
