@@ -244,6 +244,9 @@ def lower(graph: Any, node_configs: dict[str, dict] | None = None,
         fused: list[str] = []
         if op.name in ("matmul", "conv2d"):
             cfg.setdefault("precision", PRECISIONS[precision])
+            if cfg["precision"] == capi.PRECISION_3XTF32 and cfg.get("tile_n", 0) > 128:
+                # the 3xTF32 epilogue sums a tile row in registers: at most 128 columns
+                cfg["tile_n"] = 128
             out_uid, flags, thr = n.uid, 0, 0.0
             relu = relu_of.get(n.uid)
             if relu is not None:
