@@ -104,6 +104,38 @@ int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64
 int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int flags,
                                   const xtc_cuda_gemm_config* cfg, size_t* bytes);
 
+/* The 3xTF32 GEMM for callers that must not allocate device memory.  This entry
+ * point has no counterpart in the reference.
+ *
+ * Who needs it: code that runs after the application has handed the whole GPU
+ * to its own memory pool (a cudaMalloc made now would fail, or carve memory out
+ * from under that pool), and code on a latency-critical path where the implicit
+ * device-wide synchronisation of cudaMalloc / cudaFree is not acceptable.  Such
+ * a caller cannot provide the workspace xtc_cuda_gemm_f32 wants for the operand
+ * split either, so here the split lives in a fixed 32 MiB array that is part of
+ * the library image: every GPU that loads the library holds those 32 MiB until
+ * the process exits.
+ *
+ * C[M,N] = A * B (+ relu), operands dense (lda = K or M, ldb = N or K, ldc = N),
+ * 16-byte aligned, row lengths multiples of 4; flags as for xtc_cuda_gemm_f32.
+ * Limit: 2 * (round256(4*M*K) + round256(4*K*N)) <= 32 MiB, i.e. about
+ * M*K + K*N <= 4 Mi elements; larger problems are refused with
+ * XTC_CUDA_ERR_INVALID and a message that states both sizes.
+ *
+ * The call makes no cudaMalloc / cudaFree and calls no allocating library
+ * routine.  The first call on each device looks up the device address of the
+ * built-in array (cudaGetSymbolAddress, with that device current); make that
+ * first call before starting any stream capture.  All calls share the one
+ * array: two calls whose kernels can overlap on the GPU (different streams, no
+ * ordering between them) race on it; calls on one stream are safe.  The array
+ * keeps the previous call's contents, which is harmless: every byte the GEMM
+ * reads is rewritten by the split kernels of the same call first.  A bounded
+ * wait that gives up inside this variant is recorded in a word of the library
+ * image, not in the word xtc_cuda_device_status reads. */
+int xtc_cuda_gemm_f32_3xtf32_noalloc(const float* A, const float* B, float* C, int64_t M,
+                                     int64_t N, int64_t K, int flags, float relu_threshold,
+                                     void* stream);
+
 /* Y[B,OH,OW,F] = conv2d(pad(X[B,H,W,C]), Wt[R,S,C,F]) (+ optional relu), NHWC x
  * HWIO, stride (stride_h, stride_w).  pad_* is a zero padding of H and W fused
  * into the operand fetch (the reference needs a separate O.pad node for it).

@@ -111,6 +111,10 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
          c_int, c_float, POINTER(GemmConfig), c_void_p, c_size_t, c_void_p],
     ),
+    "xtc_cuda_gemm_f32_3xtf32_noalloc": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_float, c_void_p],
+    ),
     "xtc_cuda_gemm_workspace_bytes": (
         c_int, [c_int64, c_int64, c_int64, c_int, POINTER(GemmConfig), POINTER(c_size_t)],
     ),

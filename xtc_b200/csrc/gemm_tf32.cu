@@ -1,4 +1,6 @@
 // Host launchers of the TF32 GEMM kernel and the CUDA-core fallback GEMM.
+#include <mutex>
+
 #include "gemm_tf32.cuh"
 
 namespace xtc {
@@ -81,6 +83,7 @@ struct LaunchArgs {
   float thr;
   int stages;
   cudaStream_t stream;
+  int* status = nullptr;  // status word to use instead of the per-device one
 };
 
 template <int BN, int KSPANS, int A_MODE, bool B_MN, bool SPLIT3, bool TMA_STORE>
@@ -135,7 +138,7 @@ int launch_tc(const LaunchArgs& a) {
   p.chunk_kblocks = SPLIT3 ? (256 / BK) : p.k_blocks;
   p.relu = a.relu;
   p.relu_threshold = a.thr;
-  p.status = device_status_word(dev);
+  p.status = a.status ? a.status : device_status_word(dev);
   XTC_REQUIRE(p.status != nullptr, "gemm: device status word unavailable");
 
   auto kernel = gemm_tf32_kernel<BN, KSPANS, A_MODE, B_MN, SPLIT3, TMA_STORE>;
@@ -302,4 +305,82 @@ extern "C" int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64
   XTC_REQUIRE(c.precision == XTC_CUDA_PRECISION_TF32, "gemm: unknown precision %d", c.precision);
   return tma_store ? dispatch_tile<false, true>(a, tile_n, tile_k)
                    : dispatch_tile<false, false>(a, tile_n, tile_k);
+}
+
+// ---------------------------------------------------------------------------
+// 3xTF32 GEMM that allocates nothing
+// ---------------------------------------------------------------------------
+namespace {
+// Scratch for the hi/lo operand split, resident in every GPU that loads the
+// library until the process exits.
+constexpr size_t NOALLOC_SCRATCH_BYTES = 32u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+static __device__ __align__(256) int g_noalloc_status[64];
+
+struct NoallocDevice {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // device addresses, resolved once per device
+  int* status = nullptr;
+};
+std::mutex g_noalloc_mutex;
+NoallocDevice g_noalloc[64];
+}  // namespace
+
+extern "C" int xtc_cuda_gemm_f32_3xtf32_noalloc(const float* A, const float* B, float* C,
+                                                int64_t M, int64_t N, int64_t K, int flags,
+                                                float relu_threshold, void* stream) {
+  XTC_REQUIRE(A && B && C, "gemm_noalloc: NULL operand");
+  XTC_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_noalloc: empty problem");
+  XTC_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm_noalloc: dimension too large");
+  const bool a_t = flags & XTC_CUDA_GEMM_A_TRANSPOSED;
+  const bool b_t = flags & XTC_CUDA_GEMM_B_TRANSPOSED;
+  const int64_t lda = a_t ? M : K, ldb = b_t ? K : N, ldc = N;
+  XTC_REQUIRE(tma_addressable(A, lda) && tma_addressable(B, ldb),
+              "gemm_noalloc: operands must be 16-byte aligned with row lengths that are multiples of 4");
+  const size_t a_bytes = align256(static_cast<size_t>(M) * K * 4);
+  const size_t b_bytes = align256(static_cast<size_t>(K) * N * 4);
+  const size_t need = 2 * a_bytes + 2 * b_bytes;
+  XTC_REQUIRE(need <= NOALLOC_SCRATCH_BYTES,
+              "gemm_noalloc: M*K + K*N = %lld elements need %zu bytes of scratch, the built-in "
+              "scratch holds %zu (use xtc_cuda_gemm_f32 with a caller workspace for larger problems)",
+              (long long)(M * K + K * N), need, NOALLOC_SCRATCH_BYTES);
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  XTC_REQUIRE(dev >= 0 && dev < 64, "gemm_noalloc: device ordinal %d out of range", dev);
+  NoallocDevice nd;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc[dev].ready) {
+      // In host code the array names are only handles: the addresses the kernels
+      // need come from the runtime, once per device, with that device current.
+      void* p = nullptr;
+      XTC_CUDA_CHECK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+      g_noalloc[dev].scratch = static_cast<unsigned char*>(p);
+      XTC_CUDA_CHECK(cudaGetSymbolAddress(&p, g_noalloc_status));
+      g_noalloc[dev].status = static_cast<int*>(p);
+      g_noalloc[dev].ready = true;
+    }
+    nd = g_noalloc[dev];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* Ahi = reinterpret_cast<float*>(nd.scratch);
+  float* Alo = reinterpret_cast<float*>(nd.scratch + a_bytes);
+  float* Bhi = reinterpret_cast<float*>(nd.scratch + 2 * a_bytes);
+  float* Blo = reinterpret_cast<float*>(nd.scratch + 2 * a_bytes + b_bytes);
+  // Every byte of the scratch that the GEMM reads is rewritten by the two split
+  // kernels below, so nothing left by an earlier call has to be cleared.
+  int rc;
+  if ((rc = xtc_cuda_split_tf32(A, Ahi, Alo, M * K, stream))) return rc;
+  if ((rc = xtc_cuda_split_tf32(B, Bhi, Blo, K * N, stream))) return rc;
+  LaunchArgs a;
+  a.A = Ahi; a.Alo = Alo; a.B = Bhi; a.Blo = Blo; a.C = C;
+  a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldb = ldb; a.ldc = ldc;
+  a.a_t = a_t; a.b_t = b_t;
+  a.relu = flags & XTC_CUDA_FUSE_RELU;
+  a.thr = relu_threshold;
+  a.stages = 0;
+  a.stream = s;
+  a.status = nd.status;
+  const int tile_n = N <= 64 ? 64 : 128;
+  return dispatch_tile<true, false>(a, tile_n, 32);
 }
