@@ -378,7 +378,8 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         a_blk = torch.rand(rows, K, device="cuda", generator=gen) * 2 - 1
         genb = torch.Generator(device="cuda").manual_seed(4)
         b = torch.randn(K, N, device="cuda", generator=genb) / math.sqrt(8192)
-        c_full = torch.empty(M, N, device="cuda")
+        c_full = torch.empty(M, N, device="cuda") if args.exchange == "nccl" else None
+        c_blk = torch.empty(rows, N, device="cuda")  # target of the compute-only timing
         row_lo = rank * rows
 
         def compute(lo: int, hi: int, _stream) -> None:
@@ -396,14 +397,24 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
                     ccfg = configs.build("c5", rows=hi - lo)
                     chunk_handles[hi - lo] = PlanHandle(
                         configs.compile_config(ccfg, precision=args.precision).plan, dev)
-        op = RowShardedMatmul(c_full, world, rank, compute, chunks=args.chunks)
+        if args.exchange == "peer":
+            from xtc_b200.dist import PeerStoreMatmul
+            gemm_cfg = dict(module.plan.steps[-1].config)
+            op = PeerStoreMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
+                                 config=gemm_cfg)
+            result_block_ptr = op.c_block
+            sharding = (f"rows of A and C split over {world} ranks, B replicated; the GEMM epilogue "
+                        f"stores each C tile into every rank's C over NVLink (fused all-gather)")
+        else:
+            op = RowShardedMatmul(c_full, world, rank, compute, chunks=args.chunks)
+            result_block_ptr = c_full[row_lo:row_lo + rows].data_ptr()
+            sharding = f"rows of A and C split over {world} ranks, B replicated, NCCL all-gather of C"
         step = lambda i: op.step(stream)
         total_flops = 2 * M * N * K
         local_cfg = cfg
         h2d = a_blk.numel() * 4
         d2h = rows * N * 4
-        launches = 1 if args.chunks <= 1 else args.chunks
-        sharding = f"rows of A and C split over {world} ranks, B replicated, NCCL all-gather of C"
+        launches = 1 if (args.chunks <= 1 or args.exchange == "peer") else args.chunks
     elif workload == "c3":
         sh = BatchSharded(32, world, rank)
         cfg = configs.build("c3", batch=sh.local_batch)
@@ -437,7 +448,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
     # compute-only time of the local block (no exchange), for the roofline line
     comp_total, comp_per = time_device_steps(
         torch, lambda i: handle.run(
-            [a_blk.data_ptr(), b.data_ptr(), c_full[row_lo:row_lo + rows].data_ptr()], stream)
+            [a_blk.data_ptr(), b.data_ptr(), c_blk.data_ptr()], stream)
         if workload == "c5" else step(i), max(3, min(args.steps, 10)), 1, barrier)
     kernel_sec = statistics.median(comp_per)
 
@@ -450,7 +461,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         def e2e_step() -> None:
             a_blk.copy_(host_a, non_blocking=True)
             op.step(stream)
-            host_c.copy_(c_full[row_lo:row_lo + rows], non_blocking=True)
+            dev.lib.xtc_cuda_memcpy_d2h(host_c.data_ptr(), result_block_ptr, rows * N * 4, stream)
             torch.cuda.synchronize()
     else:
         host_x = torch.empty(x.shape, pin_memory=True)
@@ -506,6 +517,8 @@ def main() -> None:
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
     ap.add_argument("--fuse-transpose", action="store_true")
     ap.add_argument("--chunks", type=int, default=1, help="row chunks overlapped with the exchange (N>1)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="c5 at N>1: fused peer stores in the GEMM epilogue, or an NCCL all-gather")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
     args = ap.parse_args()

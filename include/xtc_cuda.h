@@ -104,6 +104,29 @@ int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64
 int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int flags,
                                   const xtc_cuda_gemm_config* cfg, size_t* bytes);
 
+/* xtc_cuda_gemm_f32 whose epilogue also writes every output tile to the same
+ * position of n_extra (<= 7) further buffers with the pitch ldc: the copies of C
+ * held by the other GPUs of the box, mapped into this process with
+ * xtc_cuda_ipc_import.  This fuses the all-gather of a row-sharded matmul into
+ * the GEMM: rank r passes C = its own full-size buffer + r's row offset and the
+ * peers' buffers + the same offset.  Stores to peers are plain 128-bit stores
+ * over NVLink; the caller orders them against readers on the other GPUs (a
+ * stream-ordered collective or barrier after the call).  The reference has no
+ * multi-GPU execution (its GPU runtime is pinned to device 0,
+ * src/xtc/runtimes/accelerator/gpu/GPUDevice.py:95-97); this implements the
+ * partitioning the benchmark configuration asks for. */
+int xtc_cuda_gemm_f32_bcast(const float* A, const float* B, float* C, float* const* extra_dst,
+                            int n_extra, int64_t M, int64_t N, int64_t K, int64_t lda,
+                            int64_t ldb, int64_t ldc, int flags, float relu_threshold,
+                            const xtc_cuda_gemm_config* cfg, void* workspace,
+                            size_t workspace_bytes, void* stream);
+/* Share a device allocation (from xtc_cuda_malloc) with the other processes of
+ * the box: export fills a 64-byte handle to send them; import maps the peer's
+ * allocation here; release unmaps it.  Same remark: no reference counterpart. */
+int xtc_cuda_ipc_export(void* device_ptr, void* handle64);
+int xtc_cuda_ipc_import(const void* handle64, void** device_ptr);
+int xtc_cuda_ipc_release(void* device_ptr);
+
 /* The 3xTF32 GEMM for callers that must not allocate device memory.  This entry
  * point has no counterpart in the reference.
  *
@@ -218,8 +241,13 @@ typedef struct xtc_cuda_plan xtc_cuda_plan;
 int xtc_cuda_plan_create(xtc_cuda_plan** plan, const xtc_cuda_step* steps, int n_steps,
                          int n_inputs, int n_outputs, int n_slots, const size_t* slot_bytes);
 int xtc_cuda_plan_destroy(xtc_cuda_plan* plan);
-/* io[n_inputs + n_outputs]: device pointers.  Asynchronous on `stream`. */
+/* io[n_inputs + n_outputs]: device pointers.  Asynchronous on `stream`.  The
+ * launches of a run are captured into a CUDA graph the first time a given set of
+ * io pointers is seen and replayed with one graph launch afterwards (the
+ * reference pays a host call per node instead, evaluate_perf.c:99-103). */
 int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* stream);
+/* enabled = 0 turns graph replay off (every run issues its launches directly). */
+int xtc_cuda_plan_set_graph_mode(xtc_cuda_plan* plan, int enabled);
 /* io: HOST pointers.  Copies inputs to the device, runs, copies outputs back,
  * synchronises: the call the per-module payload makes, equivalent to calling
  * the reference payload with host memory (src/xtc/utils/cfunc.py:89-110). */

@@ -1,0 +1,110 @@
+"""Row-sharded matmul on two GPUs: NCCL all-gather and the fused peer-store GEMM.
+
+Skipped on boxes with fewer than two GPUs.  Two child processes (one per GPU)
+run the same code `bench.py --gpus N` runs; every rank must end with the full
+product, equal bit for bit to what one GPU computes alone and within the TF32
+tolerance of the float64 oracle.
+"""
+
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+pytestmark = pytest.mark.gpu
+
+TF32_TOL = 1e-2
+
+
+def _gpu_count() -> int:
+    try:
+        from xtc_b200.runtimes.cuda import CudaDevice
+
+        return CudaDevice.count()
+    except Exception:
+        return 0
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+
+    from oracle import xtc_oracle as xo
+    from xtc_b200 import capi, configs
+    from xtc_b200.backends.cuda.module import PlanHandle
+    from xtc_b200.dist import PeerStoreMatmul, RowShardedMatmul
+    from xtc_b200.runtimes.cuda import CudaDevice
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dev = CudaDevice(rank)
+    dev.activate()
+    try:
+        a, b = xo.config_inputs("c5", 16)  # A [4096, 512], B [512, 512]
+        m, k = a.shape
+        n = b.shape[1]
+        rows = m // world
+        y64 = a.astype(np.float64) @ b.astype(np.float64)
+        a_blk = torch.from_numpy(a[rank * rows:(rank + 1) * rows]).cuda()
+        b_dev = torch.from_numpy(b).cuda()
+        stream = torch.cuda.current_stream().cuda_stream
+
+        # what one GPU computes alone, for the bit-for-bit comparison
+        a_all = torch.from_numpy(a).cuda()
+        single = torch.empty(m, n, device="cuda")
+        full = PlanHandle(configs.compile_config(configs.build("c5", rows=m, scale=16)).plan, dev)
+        full.run([a_all.data_ptr(), b_dev.data_ptr(), single.data_ptr()], stream)
+        torch.cuda.synchronize()
+        single = single.cpu().numpy()
+        assert xo.rel_err(single, y64) <= TF32_TOL
+
+        module = configs.compile_config(configs.build("c5", rows=rows, scale=16))
+        handle = PlanHandle(module.plan, dev)
+
+        # ---- NCCL all-gather -----------------------------------------------------
+        c_full = torch.zeros(m, n, device="cuda")
+
+        def compute(lo, hi, _s):
+            assert (lo, hi) == (rank * rows, (rank + 1) * rows)
+            handle.run([a_blk.data_ptr(), b_dev.data_ptr(), c_full[lo:hi].data_ptr()], stream)
+
+        RowShardedMatmul(c_full, world, rank, compute).step(stream)
+        torch.cuda.synchronize()
+        assert np.array_equal(c_full.cpu().numpy(), single)
+
+        # ---- fused peer stores -----------------------------------------------------
+        op = PeerStoreMatmul(dev, a_blk.data_ptr(), b_dev.data_ptr(), m, n, k, world, rank,
+                             config=dict(module.plan.steps[-1].config))
+        for _ in range(2):
+            op.step(stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        got = op.result()
+        assert np.array_equal(got, single), "every rank must hold the full product"
+        op.close()
+        assert dev.status() == 0
+        Path(out_dir, f"ok{rank}").write_text("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_row_sharded_matmul_on_two_gpus(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))

@@ -36,6 +36,7 @@ class PlanHandle:
         self.plan = plan
         self.device = device
         self.lib = device.lib
+        self._io_cache: dict[tuple, ctypes.Array] = {}
         device.activate()
         n = len(plan.steps)
         steps = (capi.Step * n)(*[s.to_c() for s in plan.steps])
@@ -45,14 +46,24 @@ class PlanHandle:
                                                  plan.n_outputs, len(plan.slot_bytes), sizes))
 
     def _io(self, pointers: list[int]) -> ctypes.Array:
-        assert len(pointers) == self.plan.n_inputs + self.plan.n_outputs
-        return (c_void_p * len(pointers))(*pointers)
+        key = tuple(pointers)
+        arr = self._io_cache.get(key)
+        if arr is None:
+            assert len(pointers) == self.plan.n_inputs + self.plan.n_outputs
+            if len(self._io_cache) > 1024:
+                self._io_cache.clear()
+            arr = self._io_cache[key] = (c_void_p * len(pointers))(*pointers)
+        return arr
+
+    def set_graph_mode(self, enabled: bool) -> None:
+        capi.check(self.lib.xtc_cuda_plan_set_graph_mode(self.handle, int(enabled)))
 
     def run(self, pointers: list[int], stream: int | None = None) -> None:
-        """Launch on device pointers (asynchronous on ``stream``)."""
-        self.device.activate()
-        capi.check(self.lib.xtc_cuda_plan_run(self.handle, self._io(pointers),
-                                              c_void_p(stream) if stream else None))
+        """Launch on device pointers (asynchronous on ``stream``).  The device of
+        the plan must be the calling thread's current device (``device.activate()``)."""
+        rc = self.lib.xtc_cuda_plan_run(self.handle, self._io(pointers), stream)
+        if rc:
+            capi.check(rc)
 
     def run_host(self, arrays: list[np.ndarray]) -> None:
         """Host arrays in, host arrays out (copies inside), synchronous."""

@@ -111,6 +111,15 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
          c_int, c_float, POINTER(GemmConfig), c_void_p, c_size_t, c_void_p],
     ),
+    "xtc_cuda_gemm_f32_bcast": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int64, c_int64, c_int64,
+         c_int64, c_int64, c_int64, c_int, c_float, POINTER(GemmConfig), c_void_p, c_size_t,
+         c_void_p],
+    ),
+    "xtc_cuda_ipc_export": (c_int, [c_void_p, c_void_p]),
+    "xtc_cuda_ipc_import": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "xtc_cuda_ipc_release": (c_int, [c_void_p]),
     "xtc_cuda_gemm_f32_3xtf32_noalloc": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_float, c_void_p],
@@ -145,6 +154,7 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "xtc_cuda_plan_destroy": (c_int, [c_void_p]),
     "xtc_cuda_plan_run": (c_int, [c_void_p, POINTER(c_void_p), c_void_p]),
+    "xtc_cuda_plan_set_graph_mode": (c_int, [c_void_p, c_int]),
     "xtc_cuda_plan_run_host": (c_int, [c_void_p, POINTER(c_void_p)]),
     "xtc_cuda_evaluate": (
         c_int, [c_void_p, POINTER(c_void_p), c_int, c_int, c_int, POINTER(c_double)],

@@ -84,6 +84,8 @@ struct LaunchArgs {
   int stages;
   cudaStream_t stream;
   int* status = nullptr;  // status word to use instead of the per-device one
+  int n_extra = 0;        // further copies of C to write (broadcast epilogue)
+  float* extra[7] = {};
 };
 
 template <int BN, int KSPANS, int A_MODE, bool B_MN, bool SPLIT3, bool TMA_STORE>
@@ -140,6 +142,8 @@ int launch_tc(const LaunchArgs& a) {
   p.relu_threshold = a.thr;
   p.status = a.status ? a.status : device_status_word(dev);
   XTC_REQUIRE(p.status != nullptr, "gemm: device status word unavailable");
+  p.n_extra = TMA_STORE ? a.n_extra : 0;
+  for (int d = 0; d < p.n_extra; ++d) p.extra_dst[d] = a.extra[d];
 
   auto kernel = gemm_tf32_kernel<BN, KSPANS, A_MODE, B_MN, SPLIT3, TMA_STORE>;
   const int smem = L::total(stages, TMA_STORE);
@@ -244,10 +248,10 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
   return XTC_CUDA_OK;
 }
 
-extern "C" int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N,
-                                 int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int flags,
-                                 float relu_threshold, const xtc_cuda_gemm_config* cfg,
-                                 void* workspace, size_t workspace_bytes, void* stream) {
+static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                     int64_t lda, int64_t ldb, int64_t ldc, int flags, float relu_threshold,
+                     const xtc_cuda_gemm_config* cfg, void* workspace, size_t workspace_bytes,
+                     void* stream, int n_extra, float* const* extra) {
   XTC_REQUIRE(A && B && C, "gemm: NULL operand");
   XTC_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %lldx%lldx%lld", (long long)M,
               (long long)N, (long long)K);
@@ -274,13 +278,24 @@ extern "C" int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64
   a.stream = static_cast<cudaStream_t>(stream);
 
   const bool tma_ok = tma_addressable(A, lda) && tma_addressable(B, ldb);
+  if (n_extra > 0) {
+    XTC_REQUIRE(n_extra <= 7 && extra != nullptr, "gemm_bcast: at most 7 extra destinations");
+    XTC_REQUIRE(tma_ok && tma_addressable(C, ldc) && c.precision != XTC_CUDA_PRECISION_FP32_SIMT,
+                "gemm_bcast: operands and C must be 16-byte aligned with pitches that are multiples of 4");
+    a.n_extra = n_extra;
+    for (int d = 0; d < n_extra; ++d) {
+      XTC_REQUIRE(tma_addressable(extra[d], ldc), "gemm_bcast: destination %d is NULL or misaligned", d);
+      a.extra[d] = extra[d];
+    }
+  }
   if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
 
   XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM, "gemm: tile_m=%d unsupported (only %d)", c.tile_m, BM);
   int tile_n = c.tile_n ? c.tile_n : default_tile_n(M, N, sm_count(dev));
   if (c.precision == XTC_CUDA_PRECISION_3XTF32 && c.tile_n == 0 && tile_n > 128) tile_n = 128;
   const int tile_k = c.tile_k ? c.tile_k : 32;
-  const bool tma_store = (c.epilogue == 2) && tma_addressable(C, ldc);
+  // the broadcast epilogue reads the tile back from the store staging buffers
+  const bool tma_store = (c.epilogue == 2 || n_extra > 0) && tma_addressable(C, ldc);
 
   if (c.precision == XTC_CUDA_PRECISION_3XTF32) {
     size_t need = 0;
@@ -305,6 +320,47 @@ extern "C" int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64
   XTC_REQUIRE(c.precision == XTC_CUDA_PRECISION_TF32, "gemm: unknown precision %d", c.precision);
   return tma_store ? dispatch_tile<false, true>(a, tile_n, tile_k)
                    : dispatch_tile<false, false>(a, tile_n, tile_k);
+}
+
+extern "C" int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N,
+                                 int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int flags,
+                                 float relu_threshold, const xtc_cuda_gemm_config* cfg,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, flags, relu_threshold, cfg, workspace,
+                   workspace_bytes, stream, 0, nullptr);
+}
+
+extern "C" int xtc_cuda_gemm_f32_bcast(const float* A, const float* B, float* C,
+                                       float* const* extra_dst, int n_extra, int64_t M, int64_t N,
+                                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int flags,
+                                       float relu_threshold, const xtc_cuda_gemm_config* cfg,
+                                       void* workspace, size_t workspace_bytes, void* stream) {
+  XTC_REQUIRE(n_extra >= 0, "gemm_bcast: negative destination count");
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, flags, relu_threshold, cfg, workspace,
+                   workspace_bytes, stream, n_extra, extra_dst);
+}
+
+// Exporting device memory to the other processes of the box (one process per GPU)
+// so that their GEMMs can store into it.
+extern "C" int xtc_cuda_ipc_export(void* device_ptr, void* handle64) {
+  XTC_REQUIRE(device_ptr && handle64, "ipc_export: NULL argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  XTC_CUDA_CHECK(cudaIpcGetMemHandle(&h, device_ptr));
+  memcpy(handle64, &h, 64);
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_ipc_import(const void* handle64, void** device_ptr) {
+  XTC_REQUIRE(device_ptr && handle64, "ipc_import: NULL argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  *device_ptr = nullptr;
+  XTC_CUDA_CHECK(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_ipc_release(void* device_ptr) {
+  if (device_ptr) XTC_CUDA_CHECK(cudaIpcCloseMemHandle(device_ptr));
+  return XTC_CUDA_OK;
 }
 
 // ---------------------------------------------------------------------------

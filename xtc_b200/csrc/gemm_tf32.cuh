@@ -44,6 +44,12 @@ struct GemmParams {
   // implicit-GEMM convolution (A_IM2COL): row m = (image, oh, ow), k = (r, s, c)
   int conv_ohow, conv_ow, conv_c, conv_cblocks, conv_s;
   int conv_stride_h, conv_stride_w, conv_pad_top, conv_pad_left;
+  // Broadcast epilogue: every output tile is also written, with plain coalesced
+  // stores, to the same position of up to 7 more buffers (the copies of C that
+  // peer GPUs hold, mapped into this process), fusing the all-gather of a
+  // row-sharded matmul into the GEMM.
+  int n_extra;
+  float* extra_dst[7];
 };
 
 template <int BN, int KSPANS, bool SPLIT3>
@@ -313,6 +319,24 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M)
           tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
         if (lane == 0) tma_store_commit();
+        if (p.n_extra > 0) {
+          // Read the staged block back row-wise: 8 lanes cover one 128-byte row, so a
+          // warp-wide store writes four full rows -- whole 128-byte lines on the link.
+          const int chunk = lane & 7;
+          const int gcol = col0 + chunk * 4;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r_in = i * 4 + (lane >> 3);
+            const int grow = m0 + quad * 32 + r_in;
+            const float4 v =
+                *reinterpret_cast<const float4*>(sb + r_in * 32 + ((chunk ^ (r_in & 7)) << 2));
+            if (grow < p.M && gcol < p.N) {
+              const int64_t off = static_cast<int64_t>(grow) * p.ldc + gcol;
+              for (int d = 0; d < p.n_extra; ++d)
+                *reinterpret_cast<float4*>(p.extra_dst[d] + off) = v;
+            }
+          }
+        }
         buf ^= 1;
       } else {
         const int row = m0 + quad * 32 + lane;

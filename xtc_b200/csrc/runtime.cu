@@ -220,6 +220,15 @@ struct xtc_cuda_plan {
   std::vector<size_t> workspace_bytes;
   std::vector<void*> staging;     // device copies of io slots for run_host (lazy)
   int device = 0;
+  // CUDA-graph replay: the launches of one run, captured once per distinct set of
+  // io pointers and replayed with a single cudaGraphLaunch afterwards.
+  struct Replay {
+    std::vector<void*> io;
+    cudaGraphExec_t exec;
+  };
+  std::vector<Replay> replays;
+  int graph_mode = 1;
+  cudaStream_t capture_stream = nullptr;
 };
 
 static int step_workspace(const xtc_cuda_step& s, size_t* bytes) {
@@ -286,6 +295,8 @@ extern "C" int xtc_cuda_plan_destroy(xtc_cuda_plan* plan) {
   for (void* q : plan->owned) if (q) cudaFree(q);
   for (void* q : plan->workspace) if (q) cudaFree(q);
   for (void* q : plan->staging) if (q) cudaFree(q);
+  for (auto& r : plan->replays) cudaGraphExecDestroy(r.exec);
+  if (plan->capture_stream) cudaStreamDestroy(plan->capture_stream);
   delete plan;
   return XTC_CUDA_OK;
 }
@@ -296,8 +307,7 @@ extern "C" int xtc_cuda_plan_step_count(const xtc_cuda_plan* plan, int* n_steps)
   return XTC_CUDA_OK;
 }
 
-extern "C" int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* stream) {
-  XTC_REQUIRE(plan && io, "plan_run: NULL plan or io");
+static int plan_launch(xtc_cuda_plan* plan, void* const* io, void* stream) {
   const int n_io = plan->n_inputs + plan->n_outputs;
   auto slot = [&](int s) -> void* { return s < n_io ? io[s] : plan->owned[s]; };
   for (size_t i = 0; i < plan->steps.size(); ++i) {
@@ -340,6 +350,63 @@ extern "C" int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* str
     }
     if (rc != XTC_CUDA_OK) return rc;
   }
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_plan_set_graph_mode(xtc_cuda_plan* plan, int enabled) {
+  XTC_REQUIRE(plan != nullptr, "plan_set_graph_mode: NULL plan");
+  plan->graph_mode = enabled ? 1 : 0;
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* stream) {
+  XTC_REQUIRE(plan && io, "plan_run: NULL plan or io");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!plan->graph_mode) return plan_launch(plan, io, stream);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return plan_launch(plan, io, stream);  // the caller is capturing: just record the launches
+  }
+  const size_t n_io = static_cast<size_t>(plan->n_inputs + plan->n_outputs);
+  for (auto& r : plan->replays) {
+    if (memcmp(r.io.data(), io, n_io * sizeof(void*)) == 0) {
+      XTC_CUDA_CHECK(cudaGraphLaunch(r.exec, s));
+      return XTC_CUDA_OK;
+    }
+  }
+  // First run on these buffers: capture the launches on a private stream.
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  device_status_word(dev);  // allocate outside the capture
+  if (!plan->capture_stream)
+    XTC_CUDA_CHECK(cudaStreamCreateWithFlags(&plan->capture_stream, cudaStreamNonBlocking));
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  bool ok = cudaStreamBeginCapture(plan->capture_stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+  int rc = XTC_CUDA_OK;
+  if (ok) {
+    rc = plan_launch(plan, io, plan->capture_stream);
+    ok = cudaStreamEndCapture(plan->capture_stream, &graph) == cudaSuccess && graph != nullptr;
+  }
+  if (rc != XTC_CUDA_OK) {  // a real argument error: report it, not a capture problem
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    return rc;
+  }
+  if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+  if (graph) cudaGraphDestroy(graph);
+  if (!ok) {
+    cudaGetLastError();
+    plan->graph_mode = 0;  // replay unavailable here: keep launching directly
+    return plan_launch(plan, io, stream);
+  }
+  if (plan->replays.size() >= 256) {
+    cudaGraphExecDestroy(plan->replays.front().exec);
+    plan->replays.erase(plan->replays.begin());
+  }
+  plan->replays.push_back({std::vector<void*>(io, io + n_io), exec});
+  XTC_CUDA_CHECK(cudaGraphLaunch(exec, s));
   return XTC_CUDA_OK;
 }
 

@@ -120,6 +120,93 @@ class RowShardedMatmul:
             main.wait_stream(self._comm_stream)
 
 
+class PeerStoreMatmul:
+    """Row-sharded matmul with the all-gather fused into the GEMM.
+
+    Every rank holds a full-size C allocated through the C ABI and exports it to
+    the other ranks (CUDA IPC).  ``step`` launches ONE kernel per rank,
+    ``xtc_cuda_gemm_f32_bcast``: its epilogue writes each finished tile of the
+    rank's row block into the local C and, with plain stores over NVLink, into
+    the same rows of every peer's C, so the transfer overlaps the tensor-core
+    work tile by tile and needs no SMs of its own.  A tiny stream-ordered
+    all-reduce afterwards is the barrier that tells each rank that all peers'
+    kernels (and therefore their stores into its C) have completed.
+    """
+
+    def __init__(self, device: Any, a_ptr: int, b_ptr: int, m: int, n: int, k: int, world: int,
+                 rank: int, group: Any = None, config: dict | None = None) -> None:
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from . import capi
+
+        assert m % world == 0, f"M ({m}) must be divisible by the number of ranks ({world})"
+        self.device, self.lib = device, device.lib
+        self.world, self.rank, self.group = world, rank, group
+        self.m, self.n, self.k = m, n, k
+        self.rows = m // world
+        self.a_ptr, self.b_ptr = int(a_ptr), int(b_ptr)
+        self.cfg = capi.GemmConfig(**(config or {}))
+        self.c_local = device.memory_allocate(m * n * 4)
+        handle = ctypes.create_string_buffer(64)
+        capi.check(self.lib.xtc_cuda_ipc_export(self.c_local, handle))
+        handles: list[Any] = [None] * world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.imported: list[Any] = []
+        offset = rank * self.rows * n * 4
+        extras = []
+        for r in range(world):
+            if r == rank:
+                continue
+            ptr = ctypes.c_void_p()
+            capi.check(self.lib.xtc_cuda_ipc_import(ctypes.create_string_buffer(handles[r], 64),
+                                                    ctypes.byref(ptr)))
+            self.imported.append(ptr)
+            extras.append(ptr.value + offset)
+        self.extras = (ctypes.c_void_p * max(len(extras), 1))(*extras)
+        self.n_extra = len(extras)
+        self.c_block = self.c_local.value + offset
+        self._flag = torch.zeros(1, device="cuda")
+        self._dist = dist
+
+    def step(self, stream: int | None = None) -> None:
+        from . import capi
+
+        rc = self.lib.xtc_cuda_gemm_f32_bcast(
+            self.a_ptr, self.b_ptr, self.c_block, self.extras, self.n_extra, self.rows, self.n,
+            self.k, self.k, self.n, self.n, 0, 0.0, ctypes_byref(self.cfg), None, 0, stream)
+        if rc:
+            capi.check(rc)
+        if self.world > 1:
+            self._dist.all_reduce(self._flag, group=self.group)  # stream-ordered barrier
+
+    def result(self) -> Any:
+        """The full C of this rank as a NumPy array (synchronises)."""
+        import numpy as np
+
+        out = np.empty((self.m, self.n), np.float32)
+        self.device.memory_copy_from(self.c_local, out, out.nbytes)
+        return out
+
+    def close(self) -> None:
+        if self.world > 1:
+            self._dist.barrier(group=self.group)  # nobody may still be storing into a freed C
+        for ptr in self.imported:
+            self.lib.xtc_cuda_ipc_release(ptr)
+        self.imported = []
+        if self.c_local is not None:
+            self.device.memory_free(self.c_local)
+            self.c_local = None
+
+
+def ctypes_byref(obj: Any) -> Any:
+    import ctypes
+
+    return ctypes.byref(obj)
+
+
 @dataclass
 class BatchSharded:
     """A graph whose leading (batch) dimension is split over the ranks; every rank
