@@ -246,7 +246,8 @@ def bench_graph_device(torch, dev, name: str, steps: int, warmup: int, precision
     def step(i: int) -> None:
         handle.run(sets[i % n_sets][0], stream)
 
-    total, per = time_device_steps(torch, step, steps, warmup)
+    # every buffer set is visited once before timing (first visits record the CUDA graph)
+    total, per = time_device_steps(torch, step, steps, max(warmup, n_sets))
     assert dev.status() == 0, "a kernel reported a bounded-wait timeout"
     info = {"cfg": cfg, "plan": plan, "seconds": total / steps, "per_step": per,
             "n_sets": n_sets, "set_bytes": set_bytes, "handle": handle, "sets": sets}
@@ -490,7 +491,8 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "tf32" if args.precision == "tf32" else args.precision, "data": "synthetic",
             "config": {"workload": workload_name(workload), "sharding": sharding,
-                       "chunks": args.chunks, "kernel_config": module.plan.steps[-1].config,
+                       "chunks": args.chunks,
+                       "exchange": args.exchange if workload == "c5" else "none", "kernel_config": module.plan.steps[-1].config,
                        "l2": "per-rank operands (>= 0.5 GB) exceed the 126 MB L2"
                              if workload == "c5" else "inputs rotate over 8 buffer sets"},
             "roofline": roofline_of(local_cfg, kernel_sec, peaks, workload, sustained=True),

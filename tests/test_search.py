@@ -1,0 +1,95 @@
+"""The search strategy and the exploration driver (host logic on CPU; one small
+exhaustive search on the GPU)."""
+
+import csv
+
+import pytest
+
+from xtc_b200.backends.cuda import Backend
+from xtc_b200.search import Exploration, ExplorationConfig, Strategies
+from xtc_b200.search.explore import conv2d_graph, matmul_graph
+
+
+def test_strategy_space_is_legal_and_maps_one_to_one():
+    graph = matmul_graph(4096, 4096, 4096)
+    strat = Strategies.create("cuda_gemm", graph)
+    space = list(strat.exhaustive())
+    assert len(space) == len({tuple(s) for s in space}) > 40
+    assert strat.sample_names == ["tile_m", "tile_n", "tile_k", "stages", "tma_store"]
+    for s in space:
+        assert strat.is_legal(s)
+        sch = Backend(graph).get_scheduler(strict=True)  # strict: an illegal point would raise
+        strat.generate(sch, s)
+        cfg = sch.schedule().node_configs()["C"]
+        assert (cfg["tile_m"], cfg["tile_n"], cfg["tile_k"]) == tuple(s[:3])
+        assert cfg.get("stages", 0) == s[3] and cfg.get("epilogue", 0) == (2 if s[4] else 0)
+    # the shared-memory filter: 128x256x64 leaves room for 2 stages, not for 3
+    assert strat.is_legal([128, 256, 64, 2, 0]) and not strat.is_legal([128, 256, 64, 3, 0])
+    assert not strat.is_legal([128, 96, 32, 0, 0])
+    assert strat.sample(5, seed=1) == strat.sample(5, seed=1) and len(strat.sample(5, 1)) == 5
+    for level in range(4):
+        assert strat.is_legal(strat.default_schedule(level))
+
+
+def test_strategy_targets_the_contraction_of_a_fused_graph():
+    graph = matmul_graph(256, 256, 256, relu=True)
+    strat = Strategies.create("cuda_gemm", graph)
+    assert strat.node_name == "C"
+    sch = Backend(graph).get_scheduler()
+    strat.generate(sch, [128, 128, 64, 3, 1])
+    assert sch.schedule().node_configs() == {
+        "C": {"tile_m": 128, "tile_n": 128, "tile_k": 64, "stages": 3, "epilogue": 2}}
+    conv = conv2d_graph(2, 8, 8, 64, 3, 3, 32, 1, 1)
+    cs = Strategies.create("cuda_gemm", conv)
+    assert all(s[0] == 128 for s in cs.exhaustive())
+    sch = Backend(conv).get_scheduler(strict=True)
+    cs.generate(sch, [128, 64, 64, 0, 0])
+    assert sch.schedule().node_configs()["O"] == {"tile_n": 64, "tile_k": 64}
+    with pytest.raises(KeyError):
+        Strategies.create("nope", graph)
+
+
+def test_exploration_csv_and_resume(tmp_path, monkeypatch):
+    out = tmp_path / "res.csv"
+    cfg = ExplorationConfig(operator="matmul", dims=[512, 512, 512], search="random", trials=6,
+                            output=str(out), peak_flops=1e15, jobs=2,
+                            explore_dir=str(tmp_path / "x"))
+    calls = []
+
+    def fake_eval(self, module, sample):
+        calls.append(list(sample))
+        return (sample, 0, 1e-6 * (1 + sample[1] / 64), "cuda")
+
+    monkeypatch.setattr(Exploration, "evaluate_one", fake_eval)
+    exp = Exploration(cfg)
+    results = exp.run()
+    assert len(results) == 6 and len(calls) == 6
+    rows = list(csv.DictReader(open(out)))
+    assert list(rows[0].keys()) == ["tile_m", "tile_n", "tile_k", "stages", "tma_store", "X", "time",
+                                    "peak", "backend"]
+    assert len(rows) == 6 and all(r["backend"] == "cuda" for r in rows)
+    best_sample, best_time = exp.best()
+    assert best_time == min(float(r["time"]) for r in rows)
+    # peak = (FMAs / peak rate) / time
+    assert float(rows[0]["peak"]) == pytest.approx(512 ** 3 / 1e15 / float(rows[0]["time"]))
+    # resume: nothing is evaluated twice, new samples are appended
+    cfg2 = ExplorationConfig(**{**cfg.__dict__, "trials": 9, "resume": True})
+    Exploration(cfg2).run()
+    assert len(calls) == 9
+    assert len(list(csv.DictReader(open(out)))) == 9
+
+
+@pytest.mark.gpu
+def test_exhaustive_search_on_gpu(tmp_path):
+    out = tmp_path / "res.csv"
+    cfg = ExplorationConfig(operator="matmul_relu", dims=[1024, 1024, 512], search="exhaustive",
+                            output=str(out), validate=True, repeat=2, number=3, min_repeat_ms=1,
+                            strategy_options={"tile_k": (32,), "stages": (0, 3)},
+                            explore_dir=str(tmp_path / "x"))
+    exp = Exploration(cfg)
+    results = exp.run()
+    assert results and all(code == 0 for _, code, _, _ in results)
+    rows = list(csv.DictReader(open(out)))
+    assert len(rows) == len(results)
+    assert all(0 < float(r["peak"]) <= 1.5 for r in rows)
+    assert exp.best() is not None

@@ -29,7 +29,7 @@ from typing import Any
 
 DEFAULT_ROOT = "."
 
-LEGAL_TILE_M = (128,)
+LEGAL_TILE_M = (128, 256)
 LEGAL_TILE_N = (64, 128, 256)
 LEGAL_TILE_K = (32, 64)
 MAX_STAGES = 8

@@ -1,7 +1,7 @@
 // Host launchers of the TF32 GEMM kernel and the CUDA-core fallback GEMM.
 #include <mutex>
 
-#include "gemm_tf32.cuh"
+#include "gemm_tf32_pair.cuh"
 
 namespace xtc {
 
@@ -161,6 +161,101 @@ int launch_tc(const LaunchArgs& a) {
   return XTC_CUDA_OK;
 }
 
+// CTA-pair kernel (tile rows 256): TF32 only, always with the TMA-store epilogue.
+template <int BN, int KSPANS, bool A_MN, bool B_MN>
+int launch_pair(const LaunchArgs& a) {
+  using L = PairSmem<BN, KSPANS>;
+  constexpr int BK = L::BK;
+  const int max_stages = L::max_stages();
+  int stages = a.stages <= 0 ? max_stages : a.stages;
+  if (stages > max_stages) stages = max_stages;
+  if (stages < 2) stages = 2;
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  rc = A_MN ? make_tmap_2d(&tmA, a.A, a.K, a.M, a.lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+            : make_tmap_2d(&tmA, a.A, a.M, a.K, a.lda, 32, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = B_MN ? make_tmap_2d(&tmB, a.B, a.K, a.N, a.ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+            : make_tmap_2d(&tmB, a.B, a.N, a.K, a.ldb, 32, BN / 2, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  if ((rc = make_tmap_2d(&tmC, a.C, a.M, a.N, a.ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = a.C;
+  p.ldc = a.ldc;
+  p.M = static_cast<int>(a.M);
+  p.N = static_cast<int>(a.N);
+  p.K = static_cast<int>(a.K);
+  p.tiles_m = static_cast<int>((a.M + 2 * BM - 1) / (2 * BM));
+  p.tiles_n = static_cast<int>((a.N + BN - 1) / BN);
+  p.k_blocks = static_cast<int>((a.K + BK - 1) / BK);
+  p.chunk_kblocks = p.k_blocks;
+  p.relu = a.relu;
+  p.relu_threshold = a.thr;
+  p.status = a.status ? a.status : device_status_word(dev);
+  XTC_REQUIRE(p.status != nullptr, "gemm: device status word unavailable");
+  p.n_extra = a.n_extra;
+  for (int d = 0; d < p.n_extra; ++d) p.extra_dst[d] = a.extra[d];
+
+  auto kernel = gemm_tf32_pair_kernel<BN, KSPANS, A_MN, B_MN>;
+  const int smem = L::total(stages);
+  static thread_local int configured_dev = -1;
+  static thread_local int configured_smem = 0;
+  static thread_local int max_pairs = 0;
+  if (configured_dev != dev || configured_smem < smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    // how many 2-CTA clusters the device can hold at once with this footprint
+    cudaLaunchConfig_t lc;
+    memset(&lc, 0, sizeof(lc));
+    lc.gridDim = dim3(static_cast<unsigned>(sm_count(dev) & ~1), 1, 1);
+    lc.blockDim = dim3(NUM_THREADS, 1, 1);
+    lc.dynamicSmemBytes = static_cast<size_t>(smem);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    lc.attrs = &attr;
+    lc.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &lc) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count(dev) / 2;
+    }
+    max_pairs = n;
+    configured_dev = dev;
+    configured_smem = smem;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kernel<<<2 * pairs, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmC, p, stages);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+int dispatch_pair(const LaunchArgs& a, int tile_n, int tile_k) {
+  const int ks = tile_k == 64 ? 2 : 1;
+#define XTC_PAIR_CASE(BN_, KS_)                                                              \
+  if (tile_n == BN_ && ks == KS_) {                                                          \
+    if (!a.a_t && !a.b_t) return launch_pair<BN_, KS_, false, true>(a);                      \
+    if (a.a_t && !a.b_t) return launch_pair<BN_, KS_, true, true>(a);                        \
+    if (!a.a_t && a.b_t) return launch_pair<BN_, KS_, false, false>(a);                      \
+    return launch_pair<BN_, KS_, true, false>(a);                                            \
+  }
+  XTC_PAIR_CASE(64, 1)
+  XTC_PAIR_CASE(64, 2)
+  XTC_PAIR_CASE(128, 1)
+  XTC_PAIR_CASE(128, 2)
+  XTC_PAIR_CASE(256, 1)
+  XTC_PAIR_CASE(256, 2)
+#undef XTC_PAIR_CASE
+  set_error("gemm: unsupported tile_n=%d tile_k=%d for the CTA-pair kernel", tile_n, tile_k);
+  return XTC_CUDA_ERR_UNSUPPORTED;
+}
+
 template <int BN, int KSPANS, bool SPLIT3, bool TMA_STORE>
 int dispatch_major(const LaunchArgs& a) {
   // a_t: A stored [K,M] -> MN-major A.  b_t: B stored [N,K] -> K-major B.
@@ -290,7 +385,13 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   }
   if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
 
-  XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM, "gemm: tile_m=%d unsupported (only %d)", c.tile_m, BM);
+  XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM || c.tile_m == 2 * BM,
+              "gemm: tile_m=%d unsupported (128, or 256 for the CTA-pair kernel)", c.tile_m);
+  if (c.tile_m == 2 * BM) {
+    XTC_REQUIRE(c.precision == XTC_CUDA_PRECISION_TF32, "gemm: tile_m=256 is a TF32-only configuration");
+    XTC_REQUIRE(tma_addressable(C, ldc), "gemm: tile_m=256 needs a 16-byte aligned C with ldc %% 4 == 0");
+    return dispatch_pair(a, c.tile_n ? c.tile_n : 256, c.tile_k ? c.tile_k : 32);
+  }
   int tile_n = c.tile_n ? c.tile_n : default_tile_n(M, N, sm_count(dev));
   if (c.precision == XTC_CUDA_PRECISION_3XTF32 && c.tile_n == 0 && tile_n > 128) tile_n = 128;
   const int tile_k = c.tile_k ? c.tile_k : 32;

@@ -1,0 +1,278 @@
+// TF32 GEMM on CTA pairs (tcgen05 cta_group::2): two SMs share one 256 x BN MMA.
+//
+// Each CTA of a 2-CTA cluster loads its own 128 rows of A and its own half of
+// the B tile (BN/2 columns), so per SM the shared-memory traffic for B halves
+// compared with the single-CTA kernel, which is what limits that kernel.  The
+// even CTA (the leader) issues the MMAs for both; each CTA's 128 x BN slice of
+// the accumulator lives in its own TMEM and is drained by its own epilogue.
+//
+// Synchronisation across the pair (no multicast anywhere):
+//   full[s]      leader only.  Both producers' TMA loads report their bytes to it.
+//   empty[s]     one per CTA.  The leader commits to both after the MMAs of a stage.
+//   acc_full[a]  one per CTA.  The leader commits to both after the last MMA of a tile.
+//   acc_empty[a] leader only, 8 arrivals: the 4 epilogue warps of both CTAs.
+#pragma once
+#include "gemm_tf32.cuh"
+
+namespace xtc {
+
+template <int BN, int KSPANS>
+struct PairSmem {
+  static constexpr int BK = 32 * KSPANS;
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = (BN / 2) * BK * 4;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * 32 * 32 * 4;
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int max_stages() {
+    int s = (232448 - 1024 - BAR_BYTES - EPI_BYTES) / STAGE_BYTES;
+    return s > 8 ? 8 : s;
+  }
+  static constexpr int total(int stages) { return 1024 + BAR_BYTES + EPI_BYTES + stages * STAGE_BYTES; }
+};
+
+template <int BN, int KSPANS, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, const GemmParams p,
+                      const int stages) {
+  using L = PairSmem<BN, KSPANS>;
+  constexpr int BK = L::BK;
+  constexpr int HALF = BN / 2;
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* ring = smem;
+  uint8_t* epi = ring + static_cast<size_t>(stages) * L::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + L::EPI_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + 8;
+  uint64_t* acc_full = bars + 16;
+  uint64_t* acc_empty = bars + 18;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the other CTA's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x BN
+  bool failed = false;
+
+  if (warp == 0) {
+    // ---------------------- TMA producer (one per CTA) ------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
+        const int n0 = tn * BN + static_cast<int>(rank) * HALF;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
+            failed = true;
+            break;
+          }
+          uint8_t* sA = ring + static_cast<size_t>(stage) * L::STAGE_BYTES;
+          uint8_t* sB = sA + L::A_BYTES;
+          if (leader) mbar_arrive_expect_tx(&full[stage], 2 * L::STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+#pragma unroll
+            for (int s = 0; s < KSPANS; ++s)
+              tma_load_2d_pair(sA + s * (BM * 128), &tmA, bar, k0 + s * 32, m0);
+          } else {
+#pragma unroll
+            for (int g = 0; g < BM / 32; ++g)
+              tma_load_2d_pair(sA + g * (BK * 128), &tmA, bar, m0 + g * 32, k0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int g = 0; g < HALF / 32; ++g)
+              tma_load_2d_pair(sB + g * (BK * 128), &tmB, bar, n0 + g * 32, k0);
+          } else {
+#pragma unroll
+            for (int s = 0; s < KSPANS; ++s)
+              tma_load_2d_pair(sB + s * (HALF * 128), &tmB, bar, k0 + s * 32, n0);
+          }
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------ MMA issuer (leader CTA) -------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_tf32(2 * BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_DRAIN);
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            uint32_t aoff, boff;
+            if (!A_MN) aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+            else aoff = kk * 1024;
+            if (B_MN) boff = kk * 1024;
+            else boff = (kk >> 2) * (HALF * 128) + (kk & 3) * 32;
+            const uint64_t ad =
+                A_MN ? umma_smem_desc(sA + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                     : umma_smem_desc(sA + aoff, 16, 1024, UMMA_SWIZZLE_128B);
+            const uint64_t bd =
+                B_MN ? umma_smem_desc(sB + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
+                     : umma_smem_desc(sB + boff, 16, 1024, UMMA_SWIZZLE_128B);
+            umma_tf32_pair(d_tmem, ad, bd, idesc, (kb | kk) != 0);
+          }
+          // both CTAs may refill this stage once the MMAs above have read it
+          const uint32_t e = smem_u32(&empty[stage]);
+          tc_commit_pair(map_to_cta(e, 0));
+          tc_commit_pair(map_to_cta(e, 1));
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!failed) {
+          const uint32_t f = smem_u32(&acc_full[acc]);
+          tc_commit_pair(map_to_cta(f, 0));
+          tc_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------- epilogue (both CTAs) ---------------------------
+    const int quad = warp & 3;
+    const int epi_id = warp - 2;
+    float* stage_buf = reinterpret_cast<float*>(epi + epi_id * (2 * 32 * 32 * 4));
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    int local = 0;
+    int buf = 0;
+    for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
+      const int n0 = tn * BN;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase)) {
+        if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + lane_base + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (p.relu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), p.relu_threshold));
+        }
+        const int col0 = n0 + c * 32;
+        float* sb = stage_buf + buf * (32 * 32);
+        tma_store_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int chunk = j ^ (lane & 7);
+          float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          *reinterpret_cast<float4*>(sb + lane * 32 + chunk * 4) = v;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M)
+          tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
+        if (lane == 0) tma_store_commit();
+        if (p.n_extra > 0) {
+          const int chunk = lane & 7;
+          const int gcol = col0 + chunk * 4;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r_in = i * 4 + (lane >> 3);
+            const int grow = m0 + quad * 32 + r_in;
+            const float4 v =
+                *reinterpret_cast<const float4*>(sb + r_in * 32 + ((chunk ^ (r_in & 7)) << 2));
+            if (grow < p.M && gcol < p.N) {
+              const int64_t off = static_cast<int64_t>(grow) * p.ldc + gcol;
+              for (int d = 0; d < p.n_extra; ++d)
+                *reinterpret_cast<float4*>(p.extra_dst[d] + off) = v;
+            }
+          }
+        }
+        buf ^= 1;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+    }
+    tma_store_wait_all<0>();
+  }
+
+  if (failed) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace xtc

@@ -1,0 +1,146 @@
+"""Search strategies over the kernels' real parameter space.
+
+A strategy turns a sample (a flat list of ints, the reference's convention,
+``search/strategies.py:22-164`` of the reference's ``itf/search/strategy.py``)
+into ordinary scheduler calls -- ``tile / unroll / vectorize / parallelize`` --
+on the contraction node of a graph, so the same sample works through any
+front end that drives the ``Scheduler`` interface.  The reference's strategies
+enumerate divisors of the loop extents and prune with CPU notions (vector
+width, register count, L1/L2 footprint; ``search/strategies.py:150-171,
+555-620``); here the space is what the CUDA kernels implement and the filter
+is the shared-memory budget of the pipeline.
+
+Sample layout of ``cuda_gemm`` (also used for conv2d):
+    [tile_m, tile_n, tile_k, stages, tma_store]
+"""
+
+from __future__ import annotations
+
+import itertools
+import random
+from typing import Any, Callable
+
+SMEM_BUDGET = 232448 - 1024 - 1024  # dynamic shared memory minus alignment slack and barriers
+EPILOGUE_STAGING = 4 * 2 * 32 * 32 * 4
+
+
+def contraction_node(graph: Any) -> Any:
+    nodes = [n for n in graph.nodes.values() if n.operation.name in ("matmul", "conv2d")]
+    if not nodes:
+        raise ValueError("the graph has no matmul or conv2d node to schedule")
+    return nodes[-1]
+
+
+class StrategyCudaGemm:
+    """Exhaustive / random search over CTA tile, K per stage, pipeline depth, epilogue."""
+
+    name = "cuda_gemm"
+    sample_names = ["tile_m", "tile_n", "tile_k", "stages", "tma_store"]
+
+    TILE_M = (128, 256)
+    TILE_N = (64, 128, 256)
+    TILE_K = (32, 64)
+    STAGES = (0, 2, 3, 4, 6)  # 0 = as deep as shared memory allows
+
+    def __init__(self, graph: Any, tile_m: tuple[int, ...] | None = None,
+                 tile_n: tuple[int, ...] | None = None, tile_k: tuple[int, ...] | None = None,
+                 stages: tuple[int, ...] | None = None, **_ignored: Any) -> None:
+        self._graph = graph
+        self._node = contraction_node(graph)
+        self._op = self._node.operation
+        self._is_conv = self._op.name == "conv2d"
+        self.tile_m = tuple(tile_m or ((128,) if self._is_conv else self.TILE_M))
+        self.tile_n = tuple(tile_n or self.TILE_N)
+        self.tile_k = tuple(tile_k or self.TILE_K)
+        self.stages = tuple(stages or self.STAGES)
+
+    @property
+    def graph(self) -> Any:
+        return self._graph
+
+    @property
+    def node_name(self) -> str:
+        return self._node.name
+
+    # -- the space ----------------------------------------------------------------
+    @staticmethod
+    def stage_bytes(tile_m: int, tile_n: int, tile_k: int) -> int:
+        """Shared memory one pipeline stage takes in one CTA."""
+        if tile_m == 256:  # CTA pair: each CTA holds 128 rows of A and half of the B tile
+            return (128 + tile_n // 2) * tile_k * 4
+        return (128 + tile_n) * tile_k * 4
+
+    def is_legal(self, sample: list[int]) -> bool:
+        tm, tn, tk, st, tma = sample
+        if tm not in self.TILE_M or tn not in self.TILE_N or tk not in self.TILE_K:
+            return False
+        if tma not in (0, 1) or not (st == 0 or 2 <= st <= 8):
+            return False
+        if self._is_conv and tm != 128:
+            return False
+        budget = SMEM_BUDGET - (EPILOGUE_STAGING if (tma or tm == 256) else 0)
+        depth = max(st, 2)
+        return depth * self.stage_bytes(tm, tn, tk) <= budget
+
+    def exhaustive(self):
+        for s in itertools.product(self.tile_m, self.tile_n, self.tile_k, self.stages, (0, 1)):
+            s = list(s)
+            if self.is_legal(s):
+                yield s
+
+    def sample(self, num: int, seed: int | None = 0) -> list[list[int]]:
+        space = list(self.exhaustive())
+        rng = random.Random(seed)
+        rng.shuffle(space)
+        return space[: max(num, 0)]
+
+    def default_schedule(self, opt_level: int = 2) -> list[int]:
+        """O0: smallest tiles, shallow pipeline; O3: the widest tile, deepest pipeline."""
+        if opt_level <= 0:
+            return [128, 64, 32, 2, 0]
+        if opt_level == 1:
+            return [128, 128, 32, 0, 0]
+        if opt_level == 2 or self._is_conv:
+            return [128, 256 if not self._is_conv else 64, 32 if not self._is_conv else 64, 0, 1]
+        return [256, 256, 32, 0, 1]
+
+    # -- sample -> scheduler calls ---------------------------------------------------
+    def generate(self, scheduler: Any, sample: list[int]) -> None:
+        tm, tn, tk, st, tma = [int(v) for v in sample]
+        dims = list(self._op.dims)
+        target = scheduler.node(self.node_name) if hasattr(scheduler, "node") else scheduler
+        if self._is_conv:
+            col, red = dims[3], dims[6]
+            target.tile(col, {f"{col}1": tn})
+            target.tile(red, {f"{red}1": tk})
+            target.parallelize(dims[:3])
+        else:
+            row, col, red = dims
+            target.tile(row, {f"{row}1": tm})
+            target.tile(col, {f"{col}1": tn})
+            target.tile(red, {f"{red}1": tk})
+            target.parallelize([row, col])
+        if st:
+            target.unroll({f"{red}1": st})
+        if tma:
+            target.vectorize([f"{col}1"])
+
+
+class Strategies:
+    """Name -> strategy registry (cf. ``search/strategies.py:1190-1283``)."""
+
+    _registry: dict[str, Callable[..., Any]] = {"cuda_gemm": StrategyCudaGemm}
+
+    @classmethod
+    def register(cls, name: str, factory: Callable[..., Any]) -> None:
+        cls._registry[name] = factory
+
+    @classmethod
+    def names(cls) -> list[str]:
+        return sorted(cls._registry)
+
+    @classmethod
+    def create(cls, name: str, graph: Any, **options: Any) -> Any:
+        if name not in cls._registry:
+            raise KeyError(f"unknown strategy {name!r}; known: {cls.names()}")
+        return cls._registry[name](graph, **options)
