@@ -41,10 +41,10 @@ def test_strategy_targets_the_contraction_of_a_fused_graph():
         "C": {"tile_m": 128, "tile_n": 128, "tile_k": 64, "stages": 3, "epilogue": 2}}
     conv = conv2d_graph(2, 8, 8, 64, 3, 3, 32, 1, 1)
     cs = Strategies.create("cuda_gemm", conv)
-    assert all(s[0] == 128 for s in cs.exhaustive())
+    assert {s[0] for s in cs.exhaustive()} == {128, 256}
     sch = Backend(conv).get_scheduler(strict=True)
     cs.generate(sch, [128, 64, 64, 0, 0])
-    assert sch.schedule().node_configs()["O"] == {"tile_n": 64, "tile_k": 64}
+    assert sch.schedule().node_configs()["O"] == {"tile_m": 128, "tile_n": 64, "tile_k": 64}
     with pytest.raises(KeyError):
         Strategies.create("nope", graph)
 

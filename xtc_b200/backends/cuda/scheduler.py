@@ -185,8 +185,9 @@ class CudaNodeScheduler:
         if self.op_name == "matmul" and len(self.dims) == 3:
             return self.dims[0], self.dims[1], self.dims[2]
         if self.op_name == "conv2d" and len(self.dims) == 7:
-            # rows are the b*h*w output pixels (always 128 per CTA); columns f; reduction c
-            return None, self.dims[3], self.dims[6]
+            # rows are the fused b*h*w output pixels: the first tile of w sets how many
+            # consecutive pixels a CTA (128) or a CTA pair (256) takes; columns f; reduction c
+            return self.dims[2], self.dims[3], self.dims[6]
         return None, None, None
 
     def kernel_config(self, strict: bool) -> dict[str, int]:

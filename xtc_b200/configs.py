@@ -73,9 +73,10 @@ def inputs(name: str, scale: int = 1, batch: int | None = None) -> list[np.ndarr
     raise KeyError(name)
 
 
-def _gemm_schedule(tile_n: int, tile_k: int, stages: int = 0, tma_store: bool = True):
+def _gemm_schedule(tile_n: int, tile_k: int, stages: int = 0, tma_store: bool = True,
+                   tile_m: int = 128):
     def apply(sch: Any) -> None:
-        sch.tile("i", {"i1": 128})
+        sch.tile("i", {"i1": tile_m})  # 256 rows = the CTA-pair kernel
         sch.tile("j", {"j1": tile_n})
         sch.tile("k", {"k1": tile_k})
         if stages:
@@ -116,7 +117,7 @@ def build(name: str, scale: int = 1, batch: int | None = None, rows: int | None 
             m_ = O.matmul(a, b, name="mm")
             O.relu(m_, name="relu")
         return Config(name, gb.graph, "mm", [(n, n), (n, n)], (n, n), 2 * n ** 3, 12 * n * n,
-                      "tensor", "", _gemm_schedule(256, 32))
+                      "tensor", "", _gemm_schedule(256, 64, tile_m=256))
     if name == "c3":
         bsz = batch if batch is not None else _scaled(32, s)
         x = O.tensor((bsz, 56, 56, 64), "float32", name="X")
@@ -138,7 +139,7 @@ def build(name: str, scale: int = 1, batch: int | None = None, rows: int | None 
             O.matmul(t, w, name="mm")
         return Config(name, gb.graph, "mm", [(n, n), (n, j)], (n, j), 2 * n * n * j,
                       4 * (n * n + n * j + n * j) + 8 * n * n, "tensor", "",
-                      _gemm_schedule(128, 64))
+                      _gemm_schedule(256, 64, tile_m=256))
     if name == "c5":
         k = _scaled(8192, s)
         m = rows if rows is not None else _scaled(65536, s)
@@ -147,7 +148,8 @@ def build(name: str, scale: int = 1, batch: int | None = None, rows: int | None 
         with O.graph(name="c5_matmul") as gb:
             O.matmul(a, b, name="C")
         return Config(name, gb.graph, "C", [(m, k), (k, k)], (m, k), 2 * m * k * k,
-                      4 * (2 * m * k + k * k), "tensor", "rows", _gemm_schedule(256, 32))
+                      4 * (2 * m * k + k * k), "tensor", "rows",
+                      _gemm_schedule(256, 32, tile_m=256))
     raise KeyError(name)
 
 

@@ -6,7 +6,7 @@
 // tensor map's bounding box starts at -pad and out-of-bounds reads return 0),
 // relu into the epilogue.  Shapes TMA cannot address (C or F not a multiple of
 // 4) run on a direct CUDA-core kernel.
-#include "gemm_tf32.cuh"
+#include "gemm_tf32_pair.cuh"
 
 namespace xtc {
 
@@ -143,6 +143,76 @@ int launch_conv_tc(const ConvArgs& a) {
   return XTC_CUDA_OK;
 }
 
+// 256 output pixels per CTA pair: each CTA fetches its own 128 pixels and half of
+// the filter columns.
+template <int BN, int KSPANS>
+int launch_conv_pair(const ConvArgs& a) {
+  using L = PairSmem<BN, KSPANS>;
+  constexpr int BK = L::BK;
+  const int max_stages = L::max_stages();
+  int stages = a.stages <= 0 ? max_stages : a.stages;
+  if (stages > max_stages) stages = max_stages;
+  if (stages < 2) stages = 2;
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  const int64_t M = a.B * a.OH * a.OW, N = a.F, K = a.R * a.S * a.C;
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = make_tmap_im2col(&tmA, a, BM))) return rc;
+  if ((rc = make_tmap_2d(&tmB, a.Wt, K, N, N, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return rc;
+  if ((rc = make_tmap_2d(&tmC, a.Y, M, N, N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = a.Y;
+  p.ldc = N;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.tiles_m = static_cast<int>((M + 2 * BM - 1) / (2 * BM));
+  p.tiles_n = static_cast<int>((N + BN - 1) / BN);
+  p.conv_cblocks = static_cast<int>((a.C + BK - 1) / BK);
+  p.k_blocks = static_cast<int>(a.R * a.S) * p.conv_cblocks;
+  p.chunk_kblocks = p.k_blocks;
+  p.relu = a.relu;
+  p.relu_threshold = a.thr;
+  p.status = device_status_word(dev);
+  XTC_REQUIRE(p.status != nullptr, "conv2d: device status word unavailable");
+  p.conv_ohow = static_cast<int>(a.OH * a.OW);
+  p.conv_ow = static_cast<int>(a.OW);
+  p.conv_c = static_cast<int>(a.C);
+  p.conv_s = static_cast<int>(a.S);
+  p.conv_stride_h = a.sh;
+  p.conv_stride_w = a.sw;
+  p.conv_pad_top = a.pt;
+  p.conv_pad_left = a.pl;
+  auto kernel = gemm_tf32_pair_kernel<BN, KSPANS, A_IM2COL, true>;
+  const int smem = L::total(stages);
+  static thread_local int configured_dev = -1;
+  static thread_local int configured_smem = 0;
+  if (configured_dev != dev || configured_smem < smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured_dev = dev;
+    configured_smem = smem;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int max_pairs = sm_count(dev) / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kernel<<<2 * pairs, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmC, p, stages);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+int dispatch_conv_pair(const ConvArgs& a, int tile_n, int tile_k) {
+  const int ks = tile_k == 64 ? 2 : 1;
+  switch (tile_n) {
+    case 64: return ks == 1 ? launch_conv_pair<64, 1>(a) : launch_conv_pair<64, 2>(a);
+    case 128: return ks == 1 ? launch_conv_pair<128, 1>(a) : launch_conv_pair<128, 2>(a);
+    case 256: return ks == 1 ? launch_conv_pair<256, 1>(a) : launch_conv_pair<256, 2>(a);
+  }
+  set_error("conv2d: unsupported tile_n=%d", tile_n);
+  return XTC_CUDA_ERR_UNSUPPORTED;
+}
+
 template <bool TMA_STORE>
 int dispatch_conv(const ConvArgs& a, int tile_n, int tile_k) {
   const int ks = tile_k == 64 ? 2 : 1;
@@ -225,10 +295,12 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     XTC_CUDA_CHECK(cudaGetLastError());
     return XTC_CUDA_OK;
   }
-  XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM, "conv2d: tile_m=%d unsupported (only %d)", c.tile_m, BM);
+  XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM || c.tile_m == 2 * BM,
+              "conv2d: tile_m=%d unsupported (128, or 256 for the CTA-pair kernel)", c.tile_m);
   int tile_n = c.tile_n;
   if (tile_n == 0) tile_n = F <= 64 ? 64 : (F <= 128 ? 128 : 256);
   int tile_k = c.tile_k ? c.tile_k : (C % 64 == 0 ? 64 : 32);
   const bool tma_store = c.epilogue == 2 && a16(Y);
+  if (c.tile_m == 2 * BM && a16(Y)) return dispatch_conv_pair(a, tile_n, tile_k);
   return tma_store ? dispatch_conv<true>(a, tile_n, tile_k) : dispatch_conv<false>(a, tile_n, tile_k);
 }

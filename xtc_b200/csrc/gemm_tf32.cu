@@ -385,6 +385,15 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   }
   if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
 
+  // Library default for large problems: 256x256 tiles on CTA pairs (at least one
+  // tile per pair of SMs), which halves the shared-memory traffic for B per SM.
+  if (c.tile_m == 0 && c.tile_n == 0 && c.precision == XTC_CUDA_PRECISION_TF32 &&
+      tma_addressable(C, ldc) &&
+      ((M + 255) / 256) * ((N + 255) / 256) >= sm_count(dev) / 2) {
+    c.tile_m = 2 * BM;
+    c.tile_n = 256;
+    if (c.tile_k == 0) c.tile_k = 32;
+  }
   XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM || c.tile_m == 2 * BM,
               "gemm: tile_m=%d unsupported (128, or 256 for the CTA-pair kernel)", c.tile_m);
   if (c.tile_m == 2 * BM) {

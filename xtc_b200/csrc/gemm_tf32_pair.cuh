@@ -31,7 +31,7 @@ struct PairSmem {
   static constexpr int total(int stages) { return 1024 + BAR_BYTES + EPI_BYTES + stages * STAGE_BYTES; }
 };
 
-template <int BN, int KSPANS, bool A_MN, bool B_MN>
+template <int BN, int KSPANS, int A_MODE, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB,
@@ -39,6 +39,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                       const int stages) {
   using L = PairSmem<BN, KSPANS>;
   constexpr int BK = L::BK;
+  constexpr bool A_MN = A_MODE == A_MNMAJOR;
   constexpr int HALF = BN / 2;
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 
@@ -98,6 +99,14 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
         const int n0 = tn * BN + static_cast<int>(rank) * HALF;
+        int img = 0, ih0 = 0, iw0 = 0;  // input pixel under the filter origin of row m0
+        if (A_MODE == A_IM2COL) {
+          img = m0 / p.conv_ohow;
+          const int rem = m0 - img * p.conv_ohow;
+          const int oh = rem / p.conv_ow;
+          ih0 = oh * p.conv_stride_h - p.conv_pad_top;
+          iw0 = (rem - oh * p.conv_ow) * p.conv_stride_w - p.conv_pad_left;
+        }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
@@ -108,8 +117,18 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           uint8_t* sB = sA + L::A_BYTES;
           if (leader) mbar_arrive_expect_tx(&full[stage], 2 * L::STAGE_BYTES);
           const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
-          const int k0 = kb * BK;
-          if (!A_MN) {
+          int k0 = kb * BK;
+          if (A_MODE == A_IM2COL) {
+            const int rs = kb / p.conv_cblocks;
+            const int c0 = (kb - rs * p.conv_cblocks) * BK;
+            const int fr = rs / p.conv_s;
+            const int fs = rs - fr * p.conv_s;
+            k0 = rs * p.conv_c + c0;
+#pragma unroll
+            for (int s = 0; s < KSPANS; ++s)
+              tma_load_im2col_4d_pair(sA + s * (BM * 128), &tmA, bar, c0 + s * 32, iw0, ih0, img,
+                                      static_cast<uint16_t>(fs), static_cast<uint16_t>(fr));
+          } else if (A_MODE == A_KMAJOR) {
 #pragma unroll
             for (int s = 0; s < KSPANS; ++s)
               tma_load_2d_pair(sA + s * (BM * 128), &tmA, bar, k0 + s * 32, m0);

@@ -49,7 +49,7 @@ class StrategyCudaGemm:
         self._node = contraction_node(graph)
         self._op = self._node.operation
         self._is_conv = self._op.name == "conv2d"
-        self.tile_m = tuple(tile_m or ((128,) if self._is_conv else self.TILE_M))
+        self.tile_m = tuple(tile_m or self.TILE_M)
         self.tile_n = tuple(tile_n or self.TILE_N)
         self.tile_k = tuple(tile_k or self.TILE_K)
         self.stages = tuple(stages or self.STAGES)
@@ -75,8 +75,6 @@ class StrategyCudaGemm:
         if tm not in self.TILE_M or tn not in self.TILE_N or tk not in self.TILE_K:
             return False
         if tma not in (0, 1) or not (st == 0 or 2 <= st <= 8):
-            return False
-        if self._is_conv and tm != 128:
             return False
         budget = SMEM_BUDGET - (EPILOGUE_STAGING if (tma or tm == 256) else 0)
         depth = max(st, 2)
@@ -110,7 +108,8 @@ class StrategyCudaGemm:
         dims = list(self._op.dims)
         target = scheduler.node(self.node_name) if hasattr(scheduler, "node") else scheduler
         if self._is_conv:
-            col, red = dims[3], dims[6]
+            row, col, red = dims[2], dims[3], dims[6]
+            target.tile(row, {f"{row}1": tm})  # pixels per CTA (128) or CTA pair (256)
             target.tile(col, {f"{col}1": tn})
             target.tile(red, {f"{red}1": tk})
             target.parallelize(dims[:3])
