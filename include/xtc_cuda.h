@@ -88,7 +88,9 @@ typedef struct xtc_cuda_gemm_config {
   int32_t stages;    /* shared-memory ring depth (0 = as many as fit)             */
   int32_t precision; /* XTC_CUDA_PRECISION_*                                      */
   int32_t epilogue;  /* 0 = default; 1 = direct global stores; 2 = TMA stores     */
-  int32_t reserved[2];
+  int32_t variant;   /* conv2d: 0 = auto; 1 = im2col fetch per filter tap;
+                        2 = resident weights + halo tiles (stride 1 only)          */
+  int32_t reserved;
 } xtc_cuda_gemm_config;
 
 /* C[M,N] = A[M,K] * B[K,N]  (+ optional relu).  Replaces the loop nest the

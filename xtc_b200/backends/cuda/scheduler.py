@@ -228,6 +228,10 @@ class CudaNodeScheduler:
         inner_col = col_tiles[-1] if col_tiles else make_loop_name(DEFAULT_ROOT, col)
         if inner_col in self.vectorization:
             cfg["epilogue"] = 2
+        if self.op_name == "conv2d" and any(1 in idx for idx in self.packed_buffers.values()):
+            # pack_at(_, 1): keep operand 1 (the filter bank) packed in shared memory for
+            # the whole kernel -> the resident-weights / halo-tile convolution
+            cfg["variant"] = 2
         return cfg
 
     def node_schedule(self, strict: bool = False) -> CudaNodeSchedule:

@@ -57,7 +57,8 @@ class GemmConfig(Structure):
         ("stages", c_int32),
         ("precision", c_int32),
         ("epilogue", c_int32),
-        ("reserved", c_int32 * 2),
+        ("variant", c_int32),
+        ("reserved", c_int32),
     ]
 
 

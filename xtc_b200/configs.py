@@ -87,8 +87,14 @@ def _gemm_schedule(tile_n: int, tile_k: int, stages: int = 0, tma_store: bool = 
     return apply
 
 
-def _conv_schedule(tile_n: int, tile_k: int, tma_store: bool = False):
+def _conv_schedule(tile_n: int, tile_k: int, tma_store: bool = False, resident: bool = True):
     def apply(sch: Any) -> None:
+        if resident:
+            # filter bank packed in shared memory for the whole kernel, input fetched as
+            # halo tiles: no per-tap tile parameters to choose
+            sch.pack_at("b", 1)
+            sch.parallelize(["b", "h", "w"])
+            return
         sch.tile("f", {"f1": tile_n})
         sch.tile("c", {"c1": tile_k})
         sch.parallelize(["b", "h", "w"])

@@ -1,0 +1,246 @@
+// Stride-1 NHWC convolution with resident weights and halo tiles.
+//
+// The im2col kernel fetches every input pixel once per filter tap (R*S times)
+// and every weight once per output tile; both come from L2 and the fill rate
+// of shared memory is what bounds it.  This kernel removes both re-fetches:
+//
+//  * the whole filter bank [R*S*C, F] is loaded into shared memory once per CTA
+//    and stays there (it must fit: R*S*C*BN*4 bytes);
+//  * output positions are numbered over the PADDED image grid,
+//      q = (b*Hp + oh)*Wp + ow,   Hp = H + pads, Wp = W + pads,
+//    so that the input pixel tap (r, s) needs for position q is simply pixel
+//    q + r*Wp + s of the zero-padded input in the same numbering.  A tile of
+//    128 consecutive positions therefore needs ONE run of
+//    P = 128 + (R-1)*Wp + (S-1) consecutive padded pixels, fetched once per
+//    32-channel slab by a single im2col-mode TMA copy whose bounding box is the
+//    padded image (out-of-bounds pixels, i.e. the padding, arrive as zeros);
+//  * the MMA of tap (r, s) reads its A operand from that run at a byte offset of
+//    (r*Wp + s)*128: a K-major SWIZZLE_128B operand may start at any 128-byte
+//    row because the swizzle is a function of the absolute shared-memory address.
+//
+// Positions with oh >= OH or ow >= OW are computed and not stored (a few
+// percent of extra MMA work).  Accumulators are double buffered in TMEM; relu is
+// fused into the epilogue.
+#pragma once
+#include "gemm_tf32.cuh"
+
+namespace xtc {
+
+struct ConvHaloParams {
+  float* Y;
+  int* status;
+  long long Q;            // B * Hp * Wp positions
+  int tiles;              // ceil(Q / 128)
+  int Hp, Wp, OH, OW, F;
+  int nslab;              // ceil(C / 32)
+  int C;
+  int taps, S;            // R*S, S
+  int pad_left, pad_top;
+  int stage_bytes;        // P * 128 rounded up to 1024: distance between stages
+  int stage_tx;           // P * 128: bytes one halo copy delivers
+  int stages;
+  int relu;
+  float relu_threshold;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                   const ConvHaloParams p) {
+  using namespace dev;
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr int WBLOCK = BN * 128;  // bytes of weights per (tap, slab): 32 k-rows x BN columns
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* wts = smem;  // taps * nslab * WBLOCK
+  uint8_t* ring = wts + static_cast<size_t>(p.taps) * p.nslab * WBLOCK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(p.stages) * p.stage_bytes);
+  uint64_t* full = bars;           // [stages]
+  uint64_t* empty = bars + 8;      // [stages]
+  uint64_t* acc_full = bars + 16;  // [2]
+  uint64_t* acc_empty = bars + 18; // [2]
+  uint64_t* wbar = bars + 20;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmX);
+    prefetch_tmap(&tmW);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], EPI_WARPS);
+    }
+    mbar_init(wbar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int plane = p.Hp * p.Wp;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------ producer --------------------------------
+    if (lane == 0) {
+      // the filter bank, once
+      mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(p.taps * p.nslab * WBLOCK));
+      for (int tap = 0; tap < p.taps; ++tap)
+        for (int slab = 0; slab < p.nslab; ++slab)
+#pragma unroll
+          for (int g = 0; g < BN / 32; ++g)
+            tma_load_2d(wts + (static_cast<size_t>(tap) * p.nslab + slab) * WBLOCK + g * 4096, &tmW,
+                        wbar, g * 32, tap * p.C + slab * 32);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < p.tiles && !failed; tile += gridDim.x) {
+        const long long q0 = static_cast<long long>(tile) * BM;
+        const int img = static_cast<int>(q0 / plane);
+        const int rem = static_cast<int>(q0 - static_cast<long long>(img) * plane);
+        const int ih = rem / p.Wp - p.pad_top;
+        const int iw = rem % p.Wp - p.pad_left;
+        for (int slab = 0; slab < p.nslab; ++slab) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
+            failed = true;
+            break;
+          }
+          mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(p.stage_tx));
+          tma_load_im2col_4d(ring + static_cast<size_t>(stage) * p.stage_bytes, &tmX, &full[stage],
+                             slab * 32, iw, ih, img, 0, 0);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(BM, BN, false, true);
+      if (!mbar_wait(wbar, 0)) {
+        atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+        failed = true;
+      }
+      const uint32_t w0 = smem_u32(wts);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int tile = blockIdx.x; tile < p.tiles && !failed; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_DRAIN);
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int slab = 0; slab < p.nslab; ++slab) {
+          if (!mbar_wait(&full[stage], phase)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * p.stage_bytes);
+          for (int tap = 0; tap < p.taps; ++tap) {
+            const int r = tap / p.S;
+            const uint32_t a_tap = sA + static_cast<uint32_t>(r * p.Wp + (tap - r * p.S)) * 128u;
+            const uint32_t b_tap = w0 + static_cast<uint32_t>(tap * p.nslab + slab) * WBLOCK;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t ad = umma_smem_desc(a_tap + kk * 32, 16, 1024, UMMA_SWIZZLE_128B);
+              const uint64_t bd =
+                  umma_smem_desc(b_tap + kk * 1024, 4096, 512, UMMA_SWIZZLE_128B_BASE32B);
+              umma_tf32(d_tmem, ad, bd, idesc, (slab | tap | kk) != 0);
+            }
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!failed) tc_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const bool vec_ok = (p.F % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < p.tiles && !failed; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase)) {
+        if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const long long q = static_cast<long long>(tile) * BM + quad * 32 + lane;
+      const int img = static_cast<int>(q / plane);
+      const int rem = static_cast<int>(q - static_cast<long long>(img) * plane);
+      const int oh = rem / p.Wp;
+      const int ow = rem - oh * p.Wp;
+      const bool valid = q < p.Q && oh < p.OH && ow < p.OW;
+      float* dst = p.Y + ((static_cast<long long>(img) * p.OH + oh) * p.OW + ow) * p.F;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + lane_base + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (p.relu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), p.relu_threshold));
+        }
+        if (valid) {
+          const int col0 = c * 32;
+          if (vec_ok && col0 + 32 <= p.F) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              reinterpret_cast<float4*>(dst + col0)[j] =
+                  make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                              __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.F) dst[col0 + i] = __uint_as_float(r[i]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  if (failed) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  }
+  // the weights copy must have landed before this CTA's shared memory is released
+  if (warp == 0 && lane == 0 && !failed) mbar_wait(wbar, 0);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace xtc

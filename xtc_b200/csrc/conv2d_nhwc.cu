@@ -6,6 +6,7 @@
 // tensor map's bounding box starts at -pad and out-of-bounds reads return 0),
 // relu into the epilogue.  Shapes TMA cannot address (C or F not a multiple of
 // 4) run on a direct CUDA-core kernel.
+#include "conv2d_halo.cuh"
 #include "gemm_tf32_pair.cuh"
 
 namespace xtc {
@@ -141,6 +142,106 @@ int launch_conv_tc(const ConvArgs& a) {
   kernel<<<grid, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmZ, tmZ, tmC, p, stages);
   XTC_CUDA_CHECK(cudaGetLastError());
   return XTC_CUDA_OK;
+}
+
+// ---- resident weights + halo tiles (conv2d_halo.cuh) ------------------------------
+struct HaloPlan {
+  bool ok = false;
+  int bn = 0, stages = 0, P = 0, stage_bytes = 0, nslab = 0, smem = 0;
+};
+
+// Whether the halo kernel can run this convolution, and with what footprint.
+HaloPlan plan_halo(const ConvArgs& a) {
+  HaloPlan h;
+  if (a.sh != 1 || a.sw != 1 || a.F > 256) return h;
+  const int64_t Wp = a.W + a.pl + a.pr;
+  const int64_t P = BM + (a.R - 1) * Wp + (a.S - 1);
+  if (P > 1024 || a.pl > 127 || a.pt > 127 || a.pr > 127 || a.pb > 127) return h;
+  h.bn = a.F <= 64 ? 64 : (a.F <= 128 ? 128 : 256);
+  h.P = static_cast<int>(P);
+  h.stage_bytes = static_cast<int>((P * 128 + 1023) / 1024 * 1024);
+  h.nslab = static_cast<int>((a.C + 31) / 32);
+  const int64_t wbytes = a.R * a.S * h.nslab * h.bn * 128;
+  const int64_t budget = 232448 - 1024 - 1024;
+  const int64_t stages = (budget - wbytes) / h.stage_bytes;
+  if (stages < 2) return h;
+  h.stages = static_cast<int>(stages > 8 ? 8 : stages);
+  h.smem = static_cast<int>(1024 + 1024 + wbytes + static_cast<int64_t>(h.stages) * h.stage_bytes);
+  h.ok = true;
+  return h;
+}
+
+template <int BN>
+int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
+  encode_im2col_fn enc = get_encode_im2col();
+  XTC_REQUIRE(enc != nullptr, "cuTensorMapEncodeIm2col is not available from this driver");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  const int64_t Hp = a.H + a.pt + a.pb, Wp = a.W + a.pl + a.pr;
+  // One copy = P consecutive pixels of the zero-padded image grid: the bounding
+  // box is the padded image, so the traversal wraps rows and images by itself.
+  CUtensorMap tmX, tmW;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W),
+                        static_cast<cuuint64_t>(a.H), static_cast<cuuint64_t>(a.B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(a.C) * 4, static_cast<cuuint64_t>(a.W * a.C) * 4,
+                           static_cast<cuuint64_t>(a.H * a.W * a.C) * 4};
+  int lower[2] = {-a.pl, -a.pt};
+  int upper[2] = {a.pr, a.pb};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.X), dims, strides,
+                   lower, upper, 32, static_cast<cuuint32_t>(h.P), estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  XTC_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeIm2col (halo) failed (%d)", static_cast<int>(r));
+  int rc;
+  if ((rc = make_tmap_2d(&tmW, a.Wt, a.R * a.S * a.C, a.F, a.F, 32, 32,
+                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)))
+    return rc;
+
+  ConvHaloParams p;
+  memset(&p, 0, sizeof(p));
+  p.Y = a.Y;
+  p.status = device_status_word(dev);
+  XTC_REQUIRE(p.status != nullptr, "conv2d: device status word unavailable");
+  p.Q = a.B * Hp * Wp;
+  p.tiles = static_cast<int>((p.Q + BM - 1) / BM);
+  p.Hp = static_cast<int>(Hp);
+  p.Wp = static_cast<int>(Wp);
+  p.OH = static_cast<int>(a.OH);
+  p.OW = static_cast<int>(a.OW);
+  p.F = static_cast<int>(a.F);
+  p.nslab = h.nslab;
+  p.C = static_cast<int>(a.C);
+  p.taps = static_cast<int>(a.R * a.S);
+  p.S = static_cast<int>(a.S);
+  p.pad_left = a.pl;
+  p.pad_top = a.pt;
+  p.stage_bytes = h.stage_bytes;
+  p.stage_tx = h.P * 128;
+  p.stages = a.stages >= 2 && a.stages < h.stages ? a.stages : h.stages;
+  p.relu = a.relu;
+  p.relu_threshold = a.thr;
+
+  auto kernel = conv2d_halo_kernel<BN>;
+  static thread_local int configured_dev = -1;
+  static thread_local int configured_smem = 0;
+  if (configured_dev != dev || configured_smem < h.smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem));
+    configured_dev = dev;
+    configured_smem = h.smem;
+  }
+  const int grid = p.tiles < sm_count(dev) ? p.tiles : sm_count(dev);
+  kernel<<<grid, NUM_THREADS, h.smem, a.stream>>>(tmX, tmW, p);
+  XTC_CUDA_CHECK(cudaGetLastError());
+  return XTC_CUDA_OK;
+}
+
+int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
+  switch (h.bn) {
+    case 64: return launch_conv_halo<64>(a, h);
+    case 128: return launch_conv_halo<128>(a, h);
+    default: return launch_conv_halo<256>(a, h);
+  }
 }
 
 // 256 output pixels per CTA pair: each CTA fetches its own 128 pixels and half of
@@ -294,6 +395,19 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
         stride_h, stride_w, pad_top, pad_left, a.relu, a.thr);
     XTC_CUDA_CHECK(cudaGetLastError());
     return XTC_CUDA_OK;
+  }
+  XTC_REQUIRE(c.variant >= 0 && c.variant <= 2, "conv2d: unknown variant %d", c.variant);
+  if (c.variant != 1) {
+    // Resident weights + halo tiles: chosen when asked for, and by default when
+    // the caller named no im2col-kernel parameter (pixel tile, K per stage).
+    const HaloPlan h = plan_halo(a);
+    const bool wanted = c.variant == 2 || (c.tile_m == 0 && c.tile_k == 0);
+    if (h.ok && wanted) return dispatch_conv_halo(a, h);
+    if (c.variant == 2) {
+      set_error("conv2d: the resident-weights variant needs stride 1 and a filter bank of at most "
+                "%d bytes next to two halo stages (R*S*C*F too large here)", 232448 - 2048);
+      return XTC_CUDA_ERR_UNSUPPORTED;
+    }
   }
   XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM || c.tile_m == 2 * BM,
               "conv2d: tile_m=%d unsupported (128, or 256 for the CTA-pair kernel)", c.tile_m);
