@@ -333,6 +333,22 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= swizzle << 61;
   return d;
 }
+// The same descriptor as two 32-bit halves.  The issuing thread builds the halves
+// once per pipeline stage and then only adds (byte offset >> 4) to the low half
+// for every MMA: the start address sits in its low 14 bits, and one thread has
+// to issue an MMA every few dozen cycles, so the per-MMA instruction count matters.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3ffff) >> 4) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+}
+__device__ __forceinline__ uint32_t umma_desc_hi(uint32_t sbo_bytes, uint32_t swizzle) {
+  return ((sbo_bytes >> 4) & 0x3fff) | (1u << 14) | (swizzle << 29);
+}
+__device__ __forceinline__ uint64_t umma_desc_pack(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor for kind::tf32, fp32 accumulate.  a_mn / b_mn select an
 // MN-major (transposed) operand; M and N are the instruction tile extents.
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, bool a_mn, bool b_mn) {

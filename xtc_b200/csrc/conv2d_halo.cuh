@@ -156,16 +156,26 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           }
           tc_fence_after();
           const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * p.stage_bytes);
-          for (int tap = 0; tap < p.taps; ++tap) {
-            const int r = tap / p.S;
-            const uint32_t a_tap = sA + static_cast<uint32_t>(r * p.Wp + (tap - r * p.S)) * 128u;
-            const uint32_t b_tap = w0 + static_cast<uint32_t>(tap * p.nslab + slab) * WBLOCK;
+          // descriptor halves once per stage; per MMA only the low half moves
+          const uint32_t a_hi = umma_desc_hi(1024, static_cast<uint32_t>(UMMA_SWIZZLE_128B));
+          const uint32_t b_hi = umma_desc_hi(512, static_cast<uint32_t>(UMMA_SWIZZLE_128B_BASE32B));
+          uint32_t a_row = umma_desc_lo(sA, 16);  // tap (r, 0)
+          uint32_t b_lo = umma_desc_lo(w0 + static_cast<uint32_t>(slab) * WBLOCK, 4096);
+          const uint32_t b_step = static_cast<uint32_t>(p.nslab) * (WBLOCK >> 4);
+          const uint32_t row_step = static_cast<uint32_t>(p.Wp) * 8u;  // Wp pixels x 128 B >> 4
+          uint32_t first = slab == 0 ? 0u : 1u;
+          for (int tap = 0, s = 0; tap < p.taps; ++tap) {
+            const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * 8u;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t ad = umma_smem_desc(a_tap + kk * 32, 16, 1024, UMMA_SWIZZLE_128B);
-              const uint64_t bd =
-                  umma_smem_desc(b_tap + kk * 1024, 4096, 512, UMMA_SWIZZLE_128B_BASE32B);
-              umma_tf32(d_tmem, ad, bd, idesc, (slab | tap | kk) != 0);
+              umma_tf32(d_tmem, umma_desc_pack(a_lo + kk * 2, a_hi),
+                        umma_desc_pack(b_lo + kk * 64, b_hi), idesc, first | (kk != 0));
+            }
+            first = 1u;
+            b_lo += b_step;
+            if (++s == p.S) {
+              s = 0;
+              a_row += row_step;
             }
           }
           tc_commit(&empty[stage]);

@@ -248,30 +248,34 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tc_fence_after();
             const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * L::STAGE_BYTES);
             const uint32_t sB = sA + L::A_BYTES;
+            // descriptor halves once per stage; per MMA only the low half moves
+            const uint32_t a_hi = A_MN ? umma_desc_hi(512, (uint32_t)UMMA_SWIZZLE_128B_BASE32B)
+                                       : umma_desc_hi(1024, (uint32_t)UMMA_SWIZZLE_128B);
+            const uint32_t b_hi = B_MN ? umma_desc_hi(512, (uint32_t)UMMA_SWIZZLE_128B_BASE32B)
+                                       : umma_desc_hi(1024, (uint32_t)UMMA_SWIZZLE_128B);
+            const uint32_t a_lo = umma_desc_lo(sA, A_MN ? BK * 128 : 16);
+            const uint32_t b_lo = umma_desc_lo(sB, B_MN ? BK * 128 : 16);
+            const uint32_t first = kb > kb0 ? 1u : 0u;
 #pragma unroll
             for (int kk = 0; kk < BK / 8; ++kk) {
-              uint32_t aoff, boff;
-              if (!A_MN) aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-              else aoff = kk * 1024;
-              if (B_MN) boff = kk * 1024;
-              else boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
-              const uint32_t acc_in = (kb > kb0) || (kk != 0);
-              auto desc_a = [&](uint32_t base) {
-                return A_MN ? umma_smem_desc(base + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                            : umma_smem_desc(base + aoff, 16, 1024, UMMA_SWIZZLE_128B);
-              };
-              auto desc_b = [&](uint32_t base) {
-                return B_MN ? umma_smem_desc(base + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                            : umma_smem_desc(base + boff, 16, 1024, UMMA_SWIZZLE_128B);
-              };
+              // byte offsets of K step kk inside the stage, >> 4
+              const uint32_t aoff =
+                  (A_MN ? kk * 1024 : (kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
+              const uint32_t boff =
+                  (B_MN ? kk * 1024 : (kk >> 2) * (BN * 128) + (kk & 3) * 32) >> 4;
+              const uint32_t acc_in = first | (kk != 0);
               if (!SPLIT3) {
-                umma_tf32(d_tmem, desc_a(sA), desc_b(sB), idesc, acc_in);
+                umma_tf32(d_tmem, umma_desc_pack(a_lo + aoff, a_hi),
+                          umma_desc_pack(b_lo + boff, b_hi), idesc, acc_in);
               } else {
-                const uint32_t lo = L::A_BYTES + L::B_BYTES;
+                constexpr uint32_t lo = (L::A_BYTES + L::B_BYTES) >> 4;  // the lo-part tiles
                 // small cross terms first, the dominant hi*hi product last
-                umma_tf32(d_tmem, desc_a(sA + lo), desc_b(sB), idesc, acc_in);
-                umma_tf32(d_tmem, desc_a(sA), desc_b(sB + lo), idesc, 1);
-                umma_tf32(d_tmem, desc_a(sA), desc_b(sB), idesc, 1);
+                umma_tf32(d_tmem, umma_desc_pack(a_lo + lo + aoff, a_hi),
+                          umma_desc_pack(b_lo + boff, b_hi), idesc, acc_in);
+                umma_tf32(d_tmem, umma_desc_pack(a_lo + aoff, a_hi),
+                          umma_desc_pack(b_lo + lo + boff, b_hi), idesc, 1);
+                umma_tf32(d_tmem, umma_desc_pack(a_lo + aoff, a_hi),
+                          umma_desc_pack(b_lo + boff, b_hi), idesc, 1);
               }
             }
             tc_commit(&empty[stage]);  // stage reusable once these MMAs retire

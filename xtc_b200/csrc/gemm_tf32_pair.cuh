@@ -179,20 +179,20 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           tc_fence_after();
           const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * L::STAGE_BYTES);
           const uint32_t sB = sA + L::A_BYTES;
+          const uint32_t a_hi = A_MN ? umma_desc_hi(512, (uint32_t)UMMA_SWIZZLE_128B_BASE32B)
+                                     : umma_desc_hi(1024, (uint32_t)UMMA_SWIZZLE_128B);
+          const uint32_t b_hi = B_MN ? umma_desc_hi(512, (uint32_t)UMMA_SWIZZLE_128B_BASE32B)
+                                     : umma_desc_hi(1024, (uint32_t)UMMA_SWIZZLE_128B);
+          const uint32_t a_lo = umma_desc_lo(sA, A_MN ? BK * 128 : 16);
+          const uint32_t b_lo = umma_desc_lo(sB, B_MN ? BK * 128 : 16);
+          const uint32_t first = kb != 0 ? 1u : 0u;
 #pragma unroll
           for (int kk = 0; kk < BK / 8; ++kk) {
-            uint32_t aoff, boff;
-            if (!A_MN) aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-            else aoff = kk * 1024;
-            if (B_MN) boff = kk * 1024;
-            else boff = (kk >> 2) * (HALF * 128) + (kk & 3) * 32;
-            const uint64_t ad =
-                A_MN ? umma_smem_desc(sA + aoff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                     : umma_smem_desc(sA + aoff, 16, 1024, UMMA_SWIZZLE_128B);
-            const uint64_t bd =
-                B_MN ? umma_smem_desc(sB + boff, BK * 128, 512, UMMA_SWIZZLE_128B_BASE32B)
-                     : umma_smem_desc(sB + boff, 16, 1024, UMMA_SWIZZLE_128B);
-            umma_tf32_pair(d_tmem, ad, bd, idesc, (kb | kk) != 0);
+            const uint32_t aoff = (A_MN ? kk * 1024 : (kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
+            const uint32_t boff =
+                (B_MN ? kk * 1024 : (kk >> 2) * (HALF * 128) + (kk & 3) * 32) >> 4;
+            umma_tf32_pair(d_tmem, umma_desc_pack(a_lo + aoff, a_hi),
+                           umma_desc_pack(b_lo + boff, b_hi), idesc, first | (kk != 0));
           }
           // both CTAs may refill this stage once the MMAs above have read it
           const uint32_t e = smem_u32(&empty[stage]);
