@@ -90,7 +90,10 @@ typedef struct xtc_cuda_gemm_config {
   int32_t epilogue;  /* 0 = default; 1 = direct global stores; 2 = TMA stores     */
   int32_t variant;   /* conv2d: 0 = auto; 1 = im2col fetch per filter tap;
                         2 = resident weights + halo tiles (stride 1 only)          */
-  int32_t reserved;
+  int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 = auto (used
+                        when there are fewer tiles than SMs), 1 = off.  Needs the
+                        workspace of xtc_cuda_gemm_workspace_bytes, zeroed before its
+                        first use (the kernel leaves its counters zero again)        */
 } xtc_cuda_gemm_config;
 
 /* C[M,N] = A[M,K] * B[K,N]  (+ optional relu).  Replaces the loop nest the

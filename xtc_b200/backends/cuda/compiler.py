@@ -109,11 +109,11 @@ def payload_source(plan: Plan) -> str:
     for s in plan.steps:
         cfg = s.to_c().cfg
         steps.append(
-            "  {%d, %d, %d, %d, %d, %d, (float)%r, (float)%r, %s, %s, %s, {%d, %d, %d, %d, %d, %d, %d, 0}}"
+            "  {%d, %d, %d, %d, %d, %d, (float)%r, (float)%r, %s, %s, %s, {%d, %d, %d, %d, %d, %d, %d, %d}}"
             % (s.KIND_CODES[s.kind], s.in0, s.in1, s.out, s.flags, s.ndim, float(s.relu_threshold),
                float(s.pad_value), _c_array(s.dims, capi.MAX_DIMS), _c_array(s.aux0, capi.MAX_DIMS),
                _c_array(s.aux1, capi.MAX_DIMS), cfg.tile_m, cfg.tile_n, cfg.tile_k, cfg.stages,
-               cfg.precision, cfg.epilogue, cfg.variant))
+               cfg.precision, cfg.epilogue, cfg.variant, cfg.split_k))
     params = ", ".join(f"void* a{i}" for i in range(n_io))
     args = ", ".join(f"a{i}" for i in range(n_io))
     name = "".join(c if c.isalnum() or c == "_" else "_" for c in plan.name)

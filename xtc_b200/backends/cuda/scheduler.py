@@ -15,6 +15,9 @@ mapping side is new: for a contraction node (matmul / conv2d)
                                                                  persistent over output tiles
   fuse_producer_at(_, idx)                                    -> fold the transpose producing
                                                                  operand idx into the GEMM
+  split(k, {n segments})   matmul reduction cut into segments -> split-K over n CTAs per tile
+  pack_at(_, 1)            conv2d filter bank packed on chip  -> resident weights + halo tiles
+  tile rows 256                                               -> CTA pairs (two SMs per MMA)
 
 Values the kernels do not implement are snapped to the nearest legal value
 (``strict=False``, the default, so that any schedule written for another
@@ -228,6 +231,9 @@ class CudaNodeScheduler:
         inner_col = col_tiles[-1] if col_tiles else make_loop_name(DEFAULT_ROOT, col)
         if inner_col in self.vectorization:
             cfg["epilogue"] = 2
+        if self.op_name == "matmul" and red in self.splits and len(self.splits[red]) > 1:
+            # split(k, {...}): the reduction cut into segments that run concurrently
+            cfg["split_k"] = len(self.splits[red])
         if self.op_name == "conv2d" and any(1 in idx for idx in self.packed_buffers.values()):
             # pack_at(_, 1): keep operand 1 (the filter bank) packed in shared memory for
             # the whole kernel -> the resident-weights / halo-tile convolution

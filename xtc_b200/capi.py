@@ -58,7 +58,7 @@ class GemmConfig(Structure):
         ("precision", c_int32),
         ("epilogue", c_int32),
         ("variant", c_int32),
-        ("reserved", c_int32),
+        ("split_k", c_int32),
     ]
 
 

@@ -115,6 +115,8 @@ int launch_conv_tc(const ConvArgs& a) {
   p.conv_cblocks = static_cast<int>((a.C + BK - 1) / BK);
   p.k_blocks = static_cast<int>(a.R * a.S) * p.conv_cblocks;
   p.chunk_kblocks = p.k_blocks;
+  p.split_k = 1;
+  p.split_kblocks = p.k_blocks;
   p.relu = a.relu;
   p.relu_threshold = a.thr;
   p.status = device_status_word(dev);

@@ -86,6 +86,9 @@ struct LaunchArgs {
   int* status = nullptr;  // status word to use instead of the per-device one
   int n_extra = 0;        // further copies of C to write (broadcast epilogue)
   float* extra[7] = {};
+  int split_k = 1;        // CTAs per output tile along K (needs partials + counters)
+  float* partials = nullptr;
+  int* counters = nullptr;
 };
 
 template <int BN, int KSPANS, int A_MODE, bool B_MN, bool SPLIT3, bool TMA_STORE>
@@ -144,6 +147,12 @@ int launch_tc(const LaunchArgs& a) {
   XTC_REQUIRE(p.status != nullptr, "gemm: device status word unavailable");
   p.n_extra = TMA_STORE ? a.n_extra : 0;
   for (int d = 0; d < p.n_extra; ++d) p.extra_dst[d] = a.extra[d];
+  const int want_split = (SPLIT3 || a.partials == nullptr || a.counters == nullptr) ? 1 : a.split_k;
+  p.split_kblocks = (p.k_blocks + want_split - 1) / want_split;
+  p.split_k = (p.k_blocks + p.split_kblocks - 1) / p.split_kblocks;
+  p.partials = a.partials;
+  p.tile_counters = a.counters;
+  if (p.split_k > 1) p.chunk_kblocks = p.split_kblocks;
 
   auto kernel = gemm_tf32_kernel<BN, KSPANS, A_MODE, B_MN, SPLIT3, TMA_STORE>;
   const int smem = L::total(stages, TMA_STORE);
@@ -154,7 +163,7 @@ int launch_tc(const LaunchArgs& a) {
     configured_dev = dev;
     configured_smem = smem;
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.split_k;
   const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
   kernel<<<grid, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmAlo, tmBlo, tmC, p, stages);
   XTC_CUDA_CHECK(cudaGetLastError());
@@ -327,6 +336,36 @@ static int default_tile_n(int64_t M, int64_t N, int sms) {
   return tm * ((N + 127) / 128) >= sms / 2 ? 128 : 64;
 }
 
+// What the single-CTA TF32 kernel will run with for a problem and a request:
+// tile shape and the split-K factor (1 = none).  Used by the launcher and by the
+// workspace query so that both agree.
+struct TfShape {
+  int tile_n, tile_k, split_k, tiles;
+};
+static TfShape resolve_tf32_shape(int64_t M, int64_t N, int64_t K, const xtc_cuda_gemm_config& c,
+                                  int sms) {
+  TfShape s;
+  s.tile_n = c.tile_n ? c.tile_n : default_tile_n(M, N, sms);
+  s.tile_k = c.tile_k ? c.tile_k : 32;
+  if (s.tile_n != 64 && s.tile_n != 128 && s.tile_n != 256) s.tile_n = 128;  // rejected later
+  if (s.tile_k != 32 && s.tile_k != 64) s.tile_k = 32;
+  s.tiles = static_cast<int>(((M + BM - 1) / BM) * ((N + s.tile_n - 1) / s.tile_n));
+  const int k_blocks = static_cast<int>((K + s.tile_k - 1) / s.tile_k);
+  int want = c.split_k;
+  if (want == 0) {
+    // auto: only when at least half of the SMs would otherwise idle and K is long
+    want = (s.tiles * 2 <= sms && k_blocks >= 4) ? sms / s.tiles : 1;
+    if (want > k_blocks / 2) want = k_blocks / 2;
+    if (want > 16) want = 16;
+  }
+  if (want > k_blocks) want = k_blocks;
+  if (want < 1 || c.precision != XTC_CUDA_PRECISION_TF32) want = 1;
+  // no empty splits: recompute the count from the per-split length
+  const int per = (k_blocks + want - 1) / want;
+  s.split_k = (k_blocks + per - 1) / per;
+  return s;
+}
+
 }  // namespace xtc
 
 using namespace xtc;
@@ -334,11 +373,25 @@ using namespace xtc;
 extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int flags,
                                              const xtc_cuda_gemm_config* cfg, size_t* bytes) {
   XTC_REQUIRE(bytes != nullptr, "gemm_workspace_bytes: bytes is NULL");
+  XTC_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_workspace_bytes: empty problem");
   (void)flags;
   *bytes = 0;
-  if (cfg && cfg->precision == XTC_CUDA_PRECISION_3XTF32) {
+  xtc_cuda_gemm_config c;
+  memset(&c, 0, sizeof(c));
+  if (cfg) c = *cfg;
+  if (c.precision == XTC_CUDA_PRECISION_3XTF32) {
     // hi and lo parts of both operands, each a dense copy
     *bytes = 2 * align256(static_cast<size_t>(M) * K * 4) + 2 * align256(static_cast<size_t>(K) * N * 4);
+    return XTC_CUDA_OK;
+  }
+  if (c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m != 2 * BM) {
+    int dev = 0;
+    int sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
+    const TfShape s = resolve_tf32_shape(M, N, K, c, sms);
+    if (s.split_k > 1)  // tile counters, then the partial tiles [split][tile][128][tile_n]
+      *bytes = align256(static_cast<size_t>(s.tiles) * 4) +
+               static_cast<size_t>(s.split_k) * s.tiles * BM * s.tile_n * 4;
   }
   return XTC_CUDA_OK;
 }
@@ -401,9 +454,23 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
     XTC_REQUIRE(tma_addressable(C, ldc), "gemm: tile_m=256 needs a 16-byte aligned C with ldc %% 4 == 0");
     return dispatch_pair(a, c.tile_n ? c.tile_n : 256, c.tile_k ? c.tile_k : 32);
   }
-  int tile_n = c.tile_n ? c.tile_n : default_tile_n(M, N, sm_count(dev));
+  const TfShape shp = resolve_tf32_shape(M, N, K, c, sm_count(dev));
+  int tile_n = c.tile_n ? c.tile_n : shp.tile_n;
   if (c.precision == XTC_CUDA_PRECISION_3XTF32 && c.tile_n == 0 && tile_n > 128) tile_n = 128;
   const int tile_k = c.tile_k ? c.tile_k : 32;
+  if (shp.split_k > 1 && n_extra == 0) {
+    const size_t counters = align256(static_cast<size_t>(shp.tiles) * 4);
+    const size_t need = counters + static_cast<size_t>(shp.split_k) * shp.tiles * BM * shp.tile_n * 4;
+    if (workspace != nullptr && workspace_bytes >= need) {
+      a.split_k = shp.split_k;
+      a.counters = static_cast<int*>(workspace);
+      a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counters);
+    } else {
+      // automatic split-K is an optimisation: without a workspace run unsplit
+      XTC_REQUIRE(c.split_k == 0, "gemm: split_k=%d needs %zu bytes of zeroed workspace, got %zu",
+                  c.split_k, need, workspace ? workspace_bytes : static_cast<size_t>(0));
+    }
+  }
   // the broadcast epilogue reads the tile back from the store staging buffers
   const bool tma_store = (c.epilogue == 2 || n_extra > 0) && tma_addressable(C, ldc);
 

@@ -50,6 +50,15 @@ struct GemmParams {
   // row-sharded matmul into the GEMM.
   int n_extra;
   float* extra_dst[7];
+  // Split-K (small problems with fewer tiles than SMs): `split_k` CTAs share one
+  // output tile, each over `split_kblocks` K stages.  Every CTA writes its raw
+  // partial tile to `partials` [split][tile][128][BN]; the last one to arrive on
+  // `tile_counters[tile]` sums the partials in split order (deterministic),
+  // applies the epilogue and resets the counter.
+  int split_k;
+  int split_kblocks;
+  float* partials;
+  int* tile_counters;
 };
 
 template <int BN, int KSPANS, bool SPLIT3>
@@ -140,7 +149,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  // Work items: (tile, K split).  Without split-K there is one item per tile.
+  const int real_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = real_tiles * p.split_k;
   bool failed = false;
 
   if (warp == 0) {
@@ -148,7 +159,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_tiles && !failed; item += gridDim.x) {
+        const int tile = item / p.split_k;
+        const int kb_lo = (item - tile * p.split_k) * p.split_kblocks;
+        const int kb_hi = min(kb_lo + p.split_kblocks, p.k_blocks);
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
@@ -160,7 +174,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           ih0 = oh * p.conv_stride_h - p.conv_pad_top;
           iw0 = (rem - oh * p.conv_ow) * p.conv_stride_w - p.conv_pad_left;
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
             failed = true;
@@ -227,8 +241,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       int acc_iter = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
-        for (int kb0 = 0; kb0 < p.k_blocks && !failed; kb0 += p.chunk_kblocks, ++acc_iter) {
+      for (int item = blockIdx.x; item < num_tiles && !failed; item += gridDim.x) {
+        const int kb_lo = (item % p.split_k) * p.split_kblocks;
+        const int kb_hi = min(kb_lo + p.split_kblocks, p.k_blocks);
+        for (int kb0 = kb_lo; kb0 < kb_hi && !failed; kb0 += p.chunk_kblocks, ++acc_iter) {
           const int acc = acc_iter & 1;
           const uint32_t acc_phase = (acc_iter >> 1) & 1;
           if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
@@ -238,7 +254,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN;
-          const int kb_end = min(kb0 + p.chunk_kblocks, p.k_blocks);
+          const int kb_end = min(kb0 + p.chunk_kblocks, kb_hi);
           for (int kb = kb0; kb < kb_end; ++kb) {
             if (!mbar_wait(&full[stage], phase)) {
               atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
@@ -362,7 +378,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     };
 
-    for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+    const bool split = !SPLIT3 && p.split_k > 1;
+    uint32_t* last_flag = tmem_slot + 1;  // written by one epilogue thread, read by all 128
+    for (int item = blockIdx.x; item < num_tiles && !failed; item += gridDim.x) {
+      const int tile = item / p.split_k;
+      const int my_split = item - tile * p.split_k;
+      const int kb_lo = my_split * p.split_kblocks;
+      const int kb_hi = min(kb_lo + p.split_kblocks, p.k_blocks);
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
@@ -371,7 +393,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < (SPLIT3 ? BN : 1); ++i) sum[i] = 0.f;
       }
-      for (int kb0 = 0; kb0 < p.k_blocks && !failed; kb0 += p.chunk_kblocks, ++acc_iter) {
+      // this thread's row of the partial tile [split][tile][128][BN]
+      float* part_row = nullptr;
+      if (split)
+        part_row = p.partials +
+                   ((static_cast<size_t>(my_split) * real_tiles + tile) * BM + quad * 32 + lane) * BN;
+      for (int kb0 = kb_lo; kb0 < kb_hi && !failed; kb0 += p.chunk_kblocks, ++acc_iter) {
         const int acc = acc_iter & 1;
         const uint32_t acc_phase = (acc_iter >> 1) & 1;
         if (!mbar_wait(&acc_full[acc], acc_phase)) {
@@ -395,7 +422,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t r[32];
             tmem_ld_32x32(tmem_base + lane_base + acc * BN + c * 32, r);
             tmem_ld_wait();
-            store_block(r, m0, n0 + c * 32);
+            if (!split) {
+              store_block(r, m0, n0 + c * 32);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                __stcg(reinterpret_cast<float4*>(part_row + c * 32) + j,
+                       make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+            }
           }
         }
         // all TMEM reads of this warp are complete (wait::ld above): release the buffer
@@ -410,6 +445,45 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(sum[(SPLIT3 ? c * 32 : 0) + (SPLIT3 ? i : 0)]);
           store_block(r, m0, n0 + c * 32);
+        }
+      }
+      if (split && !failed) {
+        // Publish the partial, count arrivals; the CTA that completes the tile reduces.
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int old = atomicAdd(&p.tile_counters[tile], 1);
+          *last_flag = (old == p.split_k - 1) ? 1u : 0u;
+          if (old == p.split_k - 1) p.tile_counters[tile] = 0;  // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool last = *reinterpret_cast<volatile uint32_t*>(last_flag) != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // flag read by all before it is rewritten
+        if (last) {
+          __threadfence();
+          const size_t split_stride = static_cast<size_t>(real_tiles) * BM * BN;
+          const float* row0 = p.partials + (static_cast<size_t>(tile) * BM + quad * 32 + lane) * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            float4 accv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) accv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < p.split_k; ++s) {  // fixed order: bit-reproducible
+              const float4* src = reinterpret_cast<const float4*>(row0 + s * split_stride + c * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 v = __ldcg(src + j);
+                accv[j].x += v.x; accv[j].y += v.y; accv[j].z += v.z; accv[j].w += v.w;
+              }
+            }
+            uint32_t r[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              r[4 * j] = __float_as_uint(accv[j].x); r[4 * j + 1] = __float_as_uint(accv[j].y);
+              r[4 * j + 2] = __float_as_uint(accv[j].z); r[4 * j + 3] = __float_as_uint(accv[j].w);
+            }
+            store_block(r, m0, n0 + c * 32);
+          }
         }
       }
     }

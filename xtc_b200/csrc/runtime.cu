@@ -280,6 +280,9 @@ extern "C" int xtc_cuda_plan_create(xtc_cuda_plan** plan, const xtc_cuda_step* s
     if (rc == XTC_CUDA_OK && need > 0) {
       rc = xtc_cuda_malloc(&p->workspace[i], need);
       p->workspace_bytes[i] = need;
+      // split-K tile counters live at the start of the workspace and must start at zero
+      if (rc == XTC_CUDA_OK && cudaMemset(p->workspace[i], 0, need < 65536 ? need : 65536) != cudaSuccess)
+        rc = XTC_CUDA_ERR_RUNTIME;
     }
   }
   if (rc != XTC_CUDA_OK) {
