@@ -90,8 +90,8 @@ typedef struct xtc_cuda_gemm_config {
   int32_t epilogue;  /* 0 = default; 1 = direct global stores; 2 = TMA stores     */
   int32_t variant;   /* conv2d: 0 = auto; 1 = im2col fetch per filter tap;
                         2 = resident weights + halo tiles (stride 1 only)          */
-  int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 = auto (used
-                        when there are fewer tiles than SMs), 1 = off.  Needs the
+  int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off (the
+                        default: it did not pay on the shapes measured).  Needs the
                         workspace of xtc_cuda_gemm_workspace_bytes, zeroed before its
                         first use (the kernel leaves its counters zero again)        */
 } xtc_cuda_gemm_config;
@@ -257,6 +257,24 @@ int xtc_cuda_plan_set_graph_mode(xtc_cuda_plan* plan, int enabled);
  * synchronises: the call the per-module payload makes, equivalent to calling
  * the reference payload with host memory (src/xtc/utils/cfunc.py:89-110). */
 int xtc_cuda_plan_run_host(xtc_cuda_plan* plan, void* const* io);
+
+/* Pipelined form of xtc_cuda_plan_run_host for a caller that runs the module on
+ * a sequence of host batches (the evaluator's repeat loop,
+ * src/xtc/runtimes/host/evaluator.py:109-141, with host arrays): up to `depth`
+ * runs are in flight, the input copy of run i+1 and the output copy of run i-1
+ * overlapping the kernels of run i on three streams.  Host buffers should be
+ * page-locked (xtc_cuda_host_alloc) for the copies to overlap.
+ * submit() returns once the run is queued; it blocks only while `depth` earlier
+ * runs are still undelivered.  The output buffers of a run are valid after a
+ * later submit() reused its slot or after wait(), which also reports a device
+ * status error.  depth in [1, 8]; the pipeline owns depth sets of device io
+ * buffers.  The plan must outlive the pipeline. */
+typedef struct xtc_cuda_pipeline xtc_cuda_pipeline;
+int xtc_cuda_pipeline_create(xtc_cuda_pipeline** pipe, xtc_cuda_plan* plan, int depth);
+int xtc_cuda_pipeline_submit(xtc_cuda_pipeline* pipe, void* const* io);
+int xtc_cuda_pipeline_wait(xtc_cuda_pipeline* pipe);
+int xtc_cuda_pipeline_destroy(xtc_cuda_pipeline* pipe);
+
 /* CUDA-event twin of evaluate_perf, src/xtc/csrcs/runtimes/host/
  * evaluate_perf.c:63-125: one untimed warm-up call when number > 0, then
  * `repeat` measurements of `number` back-to-back runs, doubling the count until

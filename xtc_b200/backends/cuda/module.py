@@ -71,6 +71,10 @@ class PlanHandle:
         ptrs = [a.ctypes.data for a in arrays]
         capi.check(self.lib.xtc_cuda_plan_run_host(self.handle, self._io(ptrs)))
 
+    def pipeline(self, depth: int = 3) -> "HostPipeline":
+        """Overlapped host-array executor over this plan (``xtc_cuda_pipeline_*``)."""
+        return HostPipeline(self, depth)
+
     def evaluate(self, pointers: list[int], repeat: int, number: int,
                  min_repeat_ms: int) -> list[float]:
         self.device.activate()
@@ -83,6 +87,45 @@ class PlanHandle:
         if self.handle is not None and self.handle.value:
             self.device.activate()
             self.lib.xtc_cuda_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class HostPipeline:
+    """Runs a plan on a sequence of host batches with the input copy, the kernels
+    and the output copy of neighbouring batches overlapped.
+
+    ``submit(arrays)`` queues one run on host arrays (inputs then outputs, the
+    payload's argument order); an output array holds its result once ``wait()``
+    has returned, or once ``depth`` later submits have been accepted.  Page-locked
+    arrays (``CudaDevice.host_alloc`` / ``xtc_cuda_host_alloc``) are needed for
+    the copies to actually overlap."""
+
+    def __init__(self, plan_handle: PlanHandle, depth: int = 3) -> None:
+        self._owner = plan_handle
+        self.lib = plan_handle.lib
+        self.handle: c_void_p | None = c_void_p()
+        plan_handle.device.activate()
+        capi.check(self.lib.xtc_cuda_pipeline_create(byref(self.handle), plan_handle.handle, depth))
+
+    def submit(self, arrays: list[np.ndarray]) -> None:
+        ptrs = [a.ctypes.data for a in arrays]
+        rc = self.lib.xtc_cuda_pipeline_submit(self.handle, self._owner._io(ptrs))
+        if rc:
+            capi.check(rc)
+
+    def wait(self) -> None:
+        capi.check(self.lib.xtc_cuda_pipeline_wait(self.handle))
+
+    def close(self) -> None:
+        if self.handle is not None and self.handle.value:
+            self._owner.device.activate()
+            self.lib.xtc_cuda_pipeline_destroy(self.handle)
             self.handle = None
 
     def __del__(self) -> None:

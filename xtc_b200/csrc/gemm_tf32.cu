@@ -352,12 +352,11 @@ static TfShape resolve_tf32_shape(int64_t M, int64_t N, int64_t K, const xtc_cud
   s.tiles = static_cast<int>(((M + BM - 1) / BM) * ((N + s.tile_n - 1) / s.tile_n));
   const int k_blocks = static_cast<int>((K + s.tile_k - 1) / s.tile_k);
   int want = c.split_k;
-  if (want == 0) {
-    // auto: only when at least half of the SMs would otherwise idle and K is long
-    want = (s.tiles * 2 <= sms && k_blocks >= 4) ? sms / s.tiles : 1;
-    if (want > k_blocks / 2) want = k_blocks / 2;
-    if (want > 16) want = 16;
-  }
+  // 0 (auto) currently means off: measured on 512x1024x256, the extra pass over the
+  // partial tiles (one SM reads split_k tiles from L2 at ~100 GB/s) costs more than
+  // the idle SMs would have gained (10.7 us unsplit, 13.4 us at 2, 19.7 us at 8).
+  if (want == 0) want = 1;
+  (void)sms;
   if (want > k_blocks) want = k_blocks;
   if (want < 1 || c.precision != XTC_CUDA_PRECISION_TF32) want = 1;
   // no empty splits: recompute the count from the per-split length

@@ -433,6 +433,105 @@ extern "C" int xtc_cuda_plan_run_host(xtc_cuda_plan* plan, void* const* io) {
   return status == 0 ? XTC_CUDA_OK : XTC_CUDA_ERR_DEVICE_TIMEOUT;
 }
 
+// ---------------------------------------------------------------------------
+// host pipeline: overlapped H2D copy / run / D2H copy of successive runs
+// ---------------------------------------------------------------------------
+struct xtc_cuda_pipeline {
+  xtc_cuda_plan* plan = nullptr;
+  int depth = 0;
+  long submitted = 0;
+  cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
+  std::vector<std::vector<void*>> staging;  // [depth][n_io] device buffers
+  std::vector<cudaEvent_t> in_done, run_done, out_done;
+};
+
+extern "C" int xtc_cuda_pipeline_destroy(xtc_cuda_pipeline* pipe) {
+  if (!pipe) return XTC_CUDA_OK;
+  if (pipe->s_out) cudaStreamSynchronize(pipe->s_out);
+  for (auto& set : pipe->staging)
+    for (void* q : set)
+      if (q) cudaFree(q);
+  for (auto e : pipe->in_done) cudaEventDestroy(e);
+  for (auto e : pipe->run_done) cudaEventDestroy(e);
+  for (auto e : pipe->out_done) cudaEventDestroy(e);
+  if (pipe->s_in) cudaStreamDestroy(pipe->s_in);
+  if (pipe->s_run) cudaStreamDestroy(pipe->s_run);
+  if (pipe->s_out) cudaStreamDestroy(pipe->s_out);
+  delete pipe;
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_pipeline_create(xtc_cuda_pipeline** pipe, xtc_cuda_plan* plan, int depth) {
+  XTC_REQUIRE(pipe && plan, "pipeline_create: NULL argument");
+  XTC_REQUIRE(depth >= 1 && depth <= 8, "pipeline_create: depth %d not in [1, 8]", depth);
+  *pipe = nullptr;
+  xtc_cuda_pipeline* p = new xtc_cuda_pipeline();
+  p->plan = plan;
+  p->depth = depth;
+  const int n_io = plan->n_inputs + plan->n_outputs;
+  int rc = XTC_CUDA_OK;
+  auto ok = [&](cudaError_t e) {
+    if (e != cudaSuccess && rc == XTC_CUDA_OK) {
+      set_error("pipeline_create: %s", cudaGetErrorString(e));
+      rc = XTC_CUDA_ERR_RUNTIME;
+    }
+  };
+  ok(cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking));
+  ok(cudaStreamCreateWithFlags(&p->s_run, cudaStreamNonBlocking));
+  ok(cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking));
+  p->staging.assign(depth, std::vector<void*>(n_io, nullptr));
+  for (int d = 0; d < depth && rc == XTC_CUDA_OK; ++d) {
+    for (int s = 0; s < n_io && rc == XTC_CUDA_OK; ++s)
+      rc = xtc_cuda_malloc(&p->staging[d][s], plan->slot_bytes[s]);
+    cudaEvent_t e;
+    ok(cudaEventCreateWithFlags(&e, cudaEventDisableTiming)); p->in_done.push_back(e);
+    ok(cudaEventCreateWithFlags(&e, cudaEventDisableTiming)); p->run_done.push_back(e);
+    ok(cudaEventCreateWithFlags(&e, cudaEventDisableTiming)); p->out_done.push_back(e);
+  }
+  if (rc != XTC_CUDA_OK) {
+    xtc_cuda_pipeline_destroy(p);
+    return rc;
+  }
+  *pipe = p;
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_pipeline_submit(xtc_cuda_pipeline* pipe, void* const* io) {
+  XTC_REQUIRE(pipe && io, "pipeline_submit: NULL argument");
+  xtc_cuda_plan* plan = pipe->plan;
+  const int n_io = plan->n_inputs + plan->n_outputs;
+  const int slot = static_cast<int>(pipe->submitted % pipe->depth);
+  // the run that used this slot `depth` submissions ago must have delivered its outputs
+  if (pipe->submitted >= pipe->depth) XTC_CUDA_CHECK(cudaEventSynchronize(pipe->out_done[slot]));
+  std::vector<void*>& dev = pipe->staging[slot];
+  for (int s = 0; s < plan->n_inputs; ++s) {
+    XTC_REQUIRE(io[s] != nullptr, "pipeline_submit: io[%d] is NULL", s);
+    XTC_CUDA_CHECK(cudaMemcpyAsync(dev[s], io[s], plan->slot_bytes[s], cudaMemcpyHostToDevice, pipe->s_in));
+  }
+  XTC_CUDA_CHECK(cudaEventRecord(pipe->in_done[slot], pipe->s_in));
+  XTC_CUDA_CHECK(cudaStreamWaitEvent(pipe->s_run, pipe->in_done[slot], 0));
+  int rc = xtc_cuda_plan_run(plan, dev.data(), pipe->s_run);
+  if (rc != XTC_CUDA_OK) return rc;
+  XTC_CUDA_CHECK(cudaEventRecord(pipe->run_done[slot], pipe->s_run));
+  XTC_CUDA_CHECK(cudaStreamWaitEvent(pipe->s_out, pipe->run_done[slot], 0));
+  for (int s = plan->n_inputs; s < n_io; ++s) {
+    XTC_REQUIRE(io[s] != nullptr, "pipeline_submit: io[%d] is NULL", s);
+    XTC_CUDA_CHECK(cudaMemcpyAsync(io[s], dev[s], plan->slot_bytes[s], cudaMemcpyDeviceToHost, pipe->s_out));
+  }
+  XTC_CUDA_CHECK(cudaEventRecord(pipe->out_done[slot], pipe->s_out));
+  ++pipe->submitted;
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_pipeline_wait(xtc_cuda_pipeline* pipe) {
+  XTC_REQUIRE(pipe != nullptr, "pipeline_wait: NULL argument");
+  XTC_CUDA_CHECK(cudaStreamSynchronize(pipe->s_out));
+  int status = 0;
+  int rc = xtc_cuda_device_status(&status);
+  if (rc != XTC_CUDA_OK) return rc;
+  return status == 0 ? XTC_CUDA_OK : XTC_CUDA_ERR_DEVICE_TIMEOUT;
+}
+
 extern "C" int xtc_cuda_evaluate(xtc_cuda_plan* plan, void* const* io, int repeat, int number,
                                  int min_repeat_ms, double* results) {
   XTC_REQUIRE(plan && io && results, "evaluate: NULL argument");
