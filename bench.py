@@ -200,23 +200,33 @@ def pinned_like(dev, arr: np.ndarray) -> np.ndarray:
 
 def time_device_steps(torch, fn, steps: int, warmup: int, barrier=None):
     """W warm-up calls, then K calls bracketed by synchronize (+ barrier); returns
-    (total seconds, per-call seconds list from events on the current stream)."""
+    (total seconds, list of average seconds per call of each timed segment), both
+    from events on the current stream."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
     if barrier:
         barrier()
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    # An event between two launches costs a few microseconds of stream time, which is
+    # not negligible next to a 10-30 us step: record one every `stride` steps (at most
+    # 16 segments) and report each segment's average step time.
+    stride = max(1, -(-steps // 16))
+    marks = list(range(0, steps, stride)) + [steps]
+    evs = [torch.cuda.Event(enable_timing=True) for _ in marks]
     torch.cuda.synchronize()
     evs[0].record()
+    nxt = 1
     for i in range(steps):
         fn(warmup + i)
-        evs[i + 1].record()
+        if i + 1 == marks[nxt]:
+            evs[nxt].record()
+            nxt += 1
     torch.cuda.synchronize()
     if barrier:
         barrier()
-    per = [evs[i].elapsed_time(evs[i + 1]) * 1e-3 for i in range(steps)]
-    return evs[0].elapsed_time(evs[steps]) * 1e-3, per
+    per = [evs[j].elapsed_time(evs[j + 1]) * 1e-3 / (marks[j + 1] - marks[j])
+           for j in range(len(marks) - 1)]
+    return evs[0].elapsed_time(evs[-1]) * 1e-3, per
 
 
 def bench_graph_device(torch, dev, name: str, steps: int, warmup: int, precision="tf32",

@@ -322,6 +322,7 @@ enum : uint64_t {
   UMMA_SWIZZLE_NONE = 0,
   UMMA_SWIZZLE_128B_BASE32B = 1,  // 128-byte span, 32-byte atoms: MN-major 32-bit operands
   UMMA_SWIZZLE_128B = 2,
+  UMMA_SWIZZLE_64B = 4,
 };
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
                                                    uint32_t sbo_bytes, uint64_t swizzle) {

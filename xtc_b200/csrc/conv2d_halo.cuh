@@ -21,6 +21,28 @@
 // Positions with oh >= OH or ow >= OW are computed and not stored (a few
 // percent of extra MMA work).  Accumulators are double buffered in TMEM; relu is
 // fused into the epilogue.
+//
+// Slab width.  A pipeline stage holds the halo run of one slab of SLAB channels:
+// 32 (128-byte rows, SWIZZLE_128B) or 16 (64-byte rows, SWIZZLE_64B), the latter
+// for layers whose filter bank leaves no room for two 32-channel stages.  The
+// weights keep their 32-row blocks either way; a 16-channel slab reads the upper
+// or lower 16 rows of its block.
+//
+// What bounds this kernel.  A 128 x N x 8 TF32 MMA reads 4 KB of A and N/32 KB of
+// B from shared memory, which delivers 128 B per clock: N = 64 takes 48 clocks
+// (measured; 32 would be the arithmetic), N = 128 takes 64, only N = 256 is bound
+// by the tensor pipe itself (128).  With F = 64 this kernel therefore runs at 2/3
+// of the tensor peak at best, and the halo copies share the same shared-memory
+// bandwidth.  Measured on 32x56x56x64 -> 64, 3x3 (841 tiles over 148 SMs): 6.9 us
+// without any MMA (launch, filter bank, copies, stores), 18.3 us with the MMAs
+// alone, 22.6 us in full.
+//
+// Two issuing threads.  One thread cannot issue tcgen05.mma faster than about one
+// per 55 clocks (measured, whatever N), and the descriptor arithmetic of this loop
+// raises that to ~75.  With DUAL, warps 1 and 2 each issue half of the taps of
+// every slab into an accumulator of their own, and the epilogue adds the two: the
+// shared-memory feed, not the issue loop, sets the pace, and the result does not
+// depend on how the two instruction streams interleave.
 #pragma once
 #include "gemm_tf32.cuh"
 
@@ -30,32 +52,39 @@ struct ConvHaloParams {
   float* Y;
   int* status;
   long long Q;            // B * Hp * Wp positions
-  int tiles;              // ceil(Q / 128)
+  int tiles;              // ceil(Q / 128), or / 256 in the CTA-pair kernel
   int Hp, Wp, OH, OW, F;
-  int nslab;              // ceil(C / 32)
+  int nslab;              // ceil(C / SLAB): halo copies (pipeline stages) per tile
+  int nblk;               // ceil(C / 32): 32-channel weight blocks per tap
   int C;
   int taps, S;            // R*S, S
   int pad_left, pad_top;
-  int stage_bytes;        // P * 128 rounded up to 1024: distance between stages
-  int stage_tx;           // P * 128: bytes one halo copy delivers
+  int stage_bytes;        // P * SLAB * 4 rounded up to 1024: distance between stages
+  int stage_tx;           // P * SLAB * 4: bytes one halo copy delivers
   int stages;
   int relu;
   float relu_threshold;
 };
 
-template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+constexpr int HALO_THREADS = 224;  // producer, two MMA issuers, four epilogue warps
+
+template <int BN, bool DUAL, int SLAB>
+__global__ void __launch_bounds__(HALO_THREADS, 1)
 conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const ConvHaloParams p) {
   using namespace dev;
-  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  constexpr int WBLOCK = BN * 128;  // bytes of weights per (tap, slab): 32 k-rows x BN columns
+  constexpr int NACC = DUAL ? 2 : 1;  // accumulators per tile, one per issuing thread
+  constexpr uint32_t TMEM_COLS = 2 * NACC * BN < 32 ? 32 : 2 * NACC * BN;
+  static_assert(TMEM_COLS <= 512, "accumulators do not fit in TMEM");
+  static_assert(SLAB == 16 || SLAB == 32, "slabs are 16 or 32 channels wide");
+  constexpr int ROW = SLAB * 4;     // bytes per pixel row of a stage
+  constexpr int WBLOCK = BN * 128;  // bytes of weights per (tap, block): 32 k-rows x BN columns
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* wts = smem;  // taps * nslab * WBLOCK
-  uint8_t* ring = wts + static_cast<size_t>(p.taps) * p.nslab * WBLOCK;
+  uint8_t* ring = wts + static_cast<size_t>(p.taps) * p.nblk * WBLOCK;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(p.stages) * p.stage_bytes);
   uint64_t* full = bars;           // [stages]
   uint64_t* empty = bars + 8;      // [stages]
@@ -71,10 +100,10 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     prefetch_tmap(&tmW);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], NACC);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_full[a], NACC);
       mbar_init(&acc_empty[a], EPI_WARPS);
     }
     mbar_init(wbar, 1);
@@ -95,13 +124,13 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     // ------------------------------ producer --------------------------------
     if (lane == 0) {
       // the filter bank, once
-      mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(p.taps * p.nslab * WBLOCK));
+      mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(p.taps * p.nblk * WBLOCK));
       for (int tap = 0; tap < p.taps; ++tap)
-        for (int slab = 0; slab < p.nslab; ++slab)
+        for (int blk = 0; blk < p.nblk; ++blk)
 #pragma unroll
           for (int g = 0; g < BN / 32; ++g)
-            tma_load_2d(wts + (static_cast<size_t>(tap) * p.nslab + slab) * WBLOCK + g * 4096, &tmW,
-                        wbar, g * 32, tap * p.C + slab * 32);
+            tma_load_2d(wts + (static_cast<size_t>(tap) * p.nblk + blk) * WBLOCK + g * 4096, &tmW,
+                        wbar, g * 32, tap * p.C + blk * 32);
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < p.tiles && !failed; tile += gridDim.x) {
@@ -118,7 +147,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           }
           mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(p.stage_tx));
           tma_load_im2col_4d(ring + static_cast<size_t>(stage) * p.stage_bytes, &tmX, &full[stage],
-                             slab * 32, iw, ih, img, 0, 0);
+                             slab * SLAB, iw, ih, img, 0, 0);
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;
@@ -126,15 +155,28 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer -------------------------------
-    if (lane == 0) {
+  } else if (warp <= 2) {
+    // ------------------------------ MMA issuers ------------------------------
+    const int w = warp - 1;
+    if (lane == 0 && w < NACC) {
       constexpr uint32_t idesc = umma_idesc_tf32(BM, BN, false, true);
+      // this thread's share of the taps
+      const int t0 = DUAL ? (w == 0 ? 0 : (p.taps + 1) / 2) : 0;
+      const int t1 = DUAL ? (w == 0 ? (p.taps + 1) / 2 : p.taps) : p.taps;
+      const int r0 = t0 / p.S, s0 = t0 - r0 * p.S;
       if (!mbar_wait(wbar, 0)) {
         atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
         failed = true;
       }
-      const uint32_t w0 = smem_u32(wts);
+      const uint32_t w0 = smem_u32(wts) + static_cast<uint32_t>(t0) * p.nblk * WBLOCK;
+      // A: K-major rows of ROW bytes, 8-row swizzle atoms
+      const uint32_t a_hi = umma_desc_hi(8 * ROW, static_cast<uint32_t>(SLAB == 32 ? UMMA_SWIZZLE_128B
+                                                                                  : UMMA_SWIZZLE_64B));
+      const uint32_t b_hi = umma_desc_hi(512, static_cast<uint32_t>(UMMA_SWIZZLE_128B_BASE32B));
+      const uint32_t b_step = static_cast<uint32_t>(p.nblk) * (WBLOCK >> 4);
+      constexpr uint32_t PIX = ROW >> 4;                               // one pixel row, >> 4
+      const uint32_t row_step = static_cast<uint32_t>(p.Wp) * PIX;  // one image row down
+      const uint32_t a_first = static_cast<uint32_t>(r0) * row_step;
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -147,7 +189,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (acc * NACC + w) * BN;
         for (int slab = 0; slab < p.nslab; ++slab) {
           if (!mbar_wait(&full[stage], phase)) {
             atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
@@ -156,18 +198,15 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           }
           tc_fence_after();
           const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * p.stage_bytes);
-          // descriptor halves once per stage; per MMA only the low half moves
-          const uint32_t a_hi = umma_desc_hi(1024, static_cast<uint32_t>(UMMA_SWIZZLE_128B));
-          const uint32_t b_hi = umma_desc_hi(512, static_cast<uint32_t>(UMMA_SWIZZLE_128B_BASE32B));
-          uint32_t a_row = umma_desc_lo(sA, 16);  // tap (r, 0)
-          uint32_t b_lo = umma_desc_lo(w0 + static_cast<uint32_t>(slab) * WBLOCK, 4096);
-          const uint32_t b_step = static_cast<uint32_t>(p.nslab) * (WBLOCK >> 4);
-          const uint32_t row_step = static_cast<uint32_t>(p.Wp) * 8u;  // Wp pixels x 128 B >> 4
+          uint32_t a_row = umma_desc_lo(sA, 16) + a_first;  // tap (r, 0)
+          // k rows [slab * SLAB, +SLAB) of the filter bank: block slab*SLAB/32, 128 B per k row
+          const uint32_t k0 = static_cast<uint32_t>(slab) * SLAB;
+          uint32_t b_lo = umma_desc_lo(w0 + (k0 >> 5) * WBLOCK + (k0 & 31u) * 128u, 4096);
           uint32_t first = slab == 0 ? 0u : 1u;
-          for (int tap = 0, s = 0; tap < p.taps; ++tap) {
-            const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * 8u;
+          for (int tap = t0, s = s0; tap < t1; ++tap) {
+            const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * PIX;
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < SLAB / 8; ++kk) {
               umma_tf32(d_tmem, umma_desc_pack(a_lo + kk * 2, a_hi),
                         umma_desc_pack(b_lo + kk * 64, b_hi), idesc, first | (kk != 0));
             }
@@ -212,8 +251,17 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + lane_base + acc * BN + c * 32, r);
-        tmem_ld_wait();
+        tmem_ld_32x32(tmem_base + lane_base + acc * NACC * BN + c * 32, r);
+        if (DUAL) {
+          uint32_t r2[32];
+          tmem_ld_32x32(tmem_base + lane_base + (acc * NACC + 1) * BN + c * 32, r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+        } else {
+          tmem_ld_wait();
+        }
         if (p.relu) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)

@@ -1,0 +1,266 @@
+// CTA-pair form of the resident-weights / halo-tile convolution (conv2d_halo.cuh).
+//
+// Two CTAs of a cluster share one 256 x BN MMA (tcgen05 cta_group::2): each CTA
+// owns 128 consecutive output positions and HALF = BN/2 of the filters.  Per
+// CTA the resident filter bank is therefore half as large: layers whose bank does
+// not fit one CTA's shared memory (3x3x64 -> 128, say) still run with resident
+// weights.  Where both kernels fit, the one-CTA kernel is the faster (measured on
+// 3x3x64 -> 64: 22.6 us against 24.4 us, although this one has four halo stages
+// instead of two), so it is only chosen then when asked for with tile_m = 256.
+//
+// Barriers (no multicast anywhere):
+//   wbar         leader only; both CTAs' filter copies report to it.
+//   full[s]      leader only; both CTAs' halo copies report to it.
+//   empty[s]     one per CTA; the leader commits to both.
+//   acc_full[a]  one per CTA; the leader commits to both.
+//   acc_empty[a] leader only, 8 arrivals (4 epilogue warps of each CTA).
+#pragma once
+#include "conv2d_halo.cuh"
+
+namespace xtc {
+
+template <int BN, bool DUAL>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HALO_THREADS, 1)
+conv2d_halo_pair_kernel(const __grid_constant__ CUtensorMap tmX,
+                        const __grid_constant__ CUtensorMap tmW, const ConvHaloParams p) {
+  using namespace dev;
+  constexpr int HALF = BN / 2;
+  constexpr int NACC = DUAL ? 2 : 1;  // accumulators per tile, one per issuing thread
+  constexpr uint32_t TMEM_COLS = 2 * NACC * BN < 32 ? 32 : 2 * NACC * BN;
+  static_assert(TMEM_COLS <= 512, "accumulators do not fit in TMEM");
+  constexpr int WBLOCK = HALF * 128;  // bytes of this CTA's weights per (tap, slab)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* wts = smem;
+  uint8_t* ring = wts + static_cast<size_t>(p.taps) * p.nblk * WBLOCK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(p.stages) * p.stage_bytes);
+  uint64_t* full = bars;           // [stages]
+  uint64_t* empty = bars + 8;      // [stages]
+  uint64_t* acc_full = bars + 16;  // [2]
+  uint64_t* acc_empty = bars + 18; // [2]
+  uint64_t* wbar = bars + 20;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmX);
+    prefetch_tmap(&tmW);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], NACC);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], NACC);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);
+    }
+    mbar_init(wbar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int plane = p.Hp * p.Wp;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------ producer --------------------------------
+    if (lane == 0) {
+      const uint32_t wbar_leader = map_to_cta(smem_u32(wbar), 0);
+      if (leader)
+        mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(2 * p.taps * p.nblk * WBLOCK));
+      for (int tap = 0; tap < p.taps; ++tap)
+        for (int slab = 0; slab < p.nslab; ++slab)
+#pragma unroll
+          for (int g = 0; g < HALF / 32; ++g)
+            tma_load_2d_pair(wts + (static_cast<size_t>(tap) * p.nblk + slab) * WBLOCK + g * 4096,
+                             &tmW, wbar_leader, static_cast<int>(rank) * HALF + g * 32,
+                             tap * p.C + slab * 32);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs) {
+        long long q0 = static_cast<long long>(tile) * (2 * BM) + static_cast<long long>(rank) * BM;
+        if (q0 >= p.Q) q0 = 0;  // nothing of this half is stored; fetch something valid
+        const int img = static_cast<int>(q0 / plane);
+        const int rem = static_cast<int>(q0 - static_cast<long long>(img) * plane);
+        const int ih = rem / p.Wp - p.pad_top;
+        const int iw = rem % p.Wp - p.pad_left;
+        for (int slab = 0; slab < p.nslab; ++slab) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
+            failed = true;
+            break;
+          }
+          if (leader) mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(2 * p.stage_tx));
+          tma_load_im2col_4d_pair(ring + static_cast<size_t>(stage) * p.stage_bytes, &tmX,
+                                  map_to_cta(smem_u32(&full[stage]), 0), slab * 32, iw, ih, img, 0, 0);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp <= 2) {
+    // ------------------------ MMA issuers (leader CTA) ------------------------
+    // Warps 1 and 2 share the taps of every slab (see conv2d_halo.cuh on why two).
+    const int w = warp - 1;
+    if (lane == 0 && leader && w < NACC) {
+      constexpr uint32_t idesc = umma_idesc_tf32(2 * BM, BN, false, true);
+      const int t0 = DUAL ? (w == 0 ? 0 : (p.taps + 1) / 2) : 0;
+      const int t1 = DUAL ? (w == 0 ? (p.taps + 1) / 2 : p.taps) : p.taps;
+      const int r0 = t0 / p.S, s0 = t0 - r0 * p.S;
+      if (!mbar_wait(wbar, 0)) {
+        atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+        failed = true;
+      }
+      const uint32_t w0 = smem_u32(wts) + static_cast<uint32_t>(t0) * p.nblk * WBLOCK;
+      const uint32_t a_hi = umma_desc_hi(1024, static_cast<uint32_t>(UMMA_SWIZZLE_128B));
+      const uint32_t b_hi = umma_desc_hi(512, static_cast<uint32_t>(UMMA_SWIZZLE_128B_BASE32B));
+      const uint32_t b_step = static_cast<uint32_t>(p.nblk) * (WBLOCK >> 4);
+      const uint32_t row_step = static_cast<uint32_t>(p.Wp) * 8u;
+      const uint32_t a_first = static_cast<uint32_t>(r0) * row_step;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_DRAIN);
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (acc * NACC + w) * BN;
+        for (int slab = 0; slab < p.nslab; ++slab) {
+          if (!mbar_wait(&full[stage], phase)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * p.stage_bytes);
+          uint32_t a_row = umma_desc_lo(sA, 16) + a_first;
+          uint32_t b_lo = umma_desc_lo(w0 + static_cast<uint32_t>(slab) * WBLOCK, 4096);
+          uint32_t first = slab == 0 ? 0u : 1u;
+          for (int tap = t0, s = s0; tap < t1; ++tap) {
+            const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * 8u;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              umma_tf32_pair(d_tmem, umma_desc_pack(a_lo + kk * 2, a_hi),
+                             umma_desc_pack(b_lo + kk * 64, b_hi), idesc, first | (kk != 0));
+            }
+            first = 1u;
+            b_lo += b_step;
+            if (++s == p.S) {
+              s = 0;
+              a_row += row_step;
+            }
+          }
+          const uint32_t e = smem_u32(&empty[stage]);
+          tc_commit_pair(map_to_cta(e, 0));
+          tc_commit_pair(map_to_cta(e, 1));
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!failed) {
+          const uint32_t f = smem_u32(&acc_full[acc]);
+          tc_commit_pair(map_to_cta(f, 0));
+          tc_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    // --------------------------- epilogue (both CTAs) --------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const bool vec_ok = (p.F % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0);
+    int local = 0;
+    for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase)) {
+        if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const long long q = static_cast<long long>(tile) * (2 * BM) + static_cast<long long>(rank) * BM +
+                          quad * 32 + lane;
+      const int img = static_cast<int>(q / plane);
+      const int rem = static_cast<int>(q - static_cast<long long>(img) * plane);
+      const int oh = rem / p.Wp;
+      const int ow = rem - oh * p.Wp;
+      const bool valid = q < p.Q && oh < p.OH && ow < p.OW;
+      float* dst = p.Y + ((static_cast<long long>(img) * p.OH + oh) * p.OW + ow) * p.F;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + lane_base + acc * NACC * BN + c * 32, r);
+        if (DUAL) {
+          uint32_t r2[32];
+          tmem_ld_32x32(tmem_base + lane_base + (acc * NACC + 1) * BN + c * 32, r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+        } else {
+          tmem_ld_wait();
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), p.relu_threshold));
+        }
+        if (valid) {
+          const int col0 = c * 32;
+          if (vec_ok && col0 + 32 <= p.F) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              reinterpret_cast<float4*>(dst + col0)[j] =
+                  make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                              __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.F) dst[col0 + i] = __uint_as_float(r[i]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+    }
+  }
+
+  if (failed) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  }
+  // both filter copies must have landed before either CTA's shared memory is released
+  if (warp == 0 && lane == 0 && leader && !failed) mbar_wait(wbar, 0);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace xtc

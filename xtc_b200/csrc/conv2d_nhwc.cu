@@ -6,7 +6,7 @@
 // tensor map's bounding box starts at -pad and out-of-bounds reads return 0),
 // relu into the epilogue.  Shapes TMA cannot address (C or F not a multiple of
 // 4) run on a direct CUDA-core kernel.
-#include "conv2d_halo.cuh"
+#include "conv2d_halo_pair.cuh"
 #include "gemm_tf32_pair.cuh"
 
 namespace xtc {
@@ -149,21 +149,25 @@ int launch_conv_tc(const ConvArgs& a) {
 // ---- resident weights + halo tiles (conv2d_halo.cuh) ------------------------------
 struct HaloPlan {
   bool ok = false;
-  int bn = 0, stages = 0, P = 0, stage_bytes = 0, nslab = 0, smem = 0;
+  int bn = 0, stages = 0, P = 0, stage_bytes = 0, nslab = 0, nblk = 0, slab = 32, smem = 0;
 };
 
 // Whether the halo kernel can run this convolution, and with what footprint.
-HaloPlan plan_halo(const ConvArgs& a) {
+// pair = the CTA-pair kernel, where each CTA keeps half of the filter columns.
+// slab = channels per pipeline stage (32, or 16 in the single-CTA kernel).
+HaloPlan plan_halo(const ConvArgs& a, bool pair = false, int slab = 32) {
   HaloPlan h;
+  h.slab = slab;
   if (a.sh != 1 || a.sw != 1 || a.F > 256) return h;
   const int64_t Wp = a.W + a.pl + a.pr;
   const int64_t P = BM + (a.R - 1) * Wp + (a.S - 1);
   if (P > 1024 || a.pl > 127 || a.pt > 127 || a.pr > 127 || a.pb > 127) return h;
   h.bn = a.F <= 64 ? 64 : (a.F <= 128 ? 128 : 256);
   h.P = static_cast<int>(P);
-  h.stage_bytes = static_cast<int>((P * 128 + 1023) / 1024 * 1024);
-  h.nslab = static_cast<int>((a.C + 31) / 32);
-  const int64_t wbytes = a.R * a.S * h.nslab * h.bn * 128;
+  h.stage_bytes = static_cast<int>((P * slab * 4 + 1023) / 1024 * 1024);
+  h.nslab = static_cast<int>((a.C + slab - 1) / slab);
+  h.nblk = static_cast<int>((a.C + 31) / 32);
+  const int64_t wbytes = a.R * a.S * h.nblk * (pair ? h.bn / 2 : h.bn) * 128;
   const int64_t budget = 232448 - 1024 - 1024;
   const int64_t stages = (budget - wbytes) / h.stage_bytes;
   if (stages < 2) return h;
@@ -173,7 +177,7 @@ HaloPlan plan_halo(const ConvArgs& a) {
   return h;
 }
 
-template <int BN>
+template <int BN, bool PAIR, int SLAB>
 int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
   encode_im2col_fn enc = get_encode_im2col();
   XTC_REQUIRE(enc != nullptr, "cuTensorMapEncodeIm2col is not available from this driver");
@@ -191,8 +195,9 @@ int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
   int upper[2] = {a.pr, a.pb};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.X), dims, strides,
-                   lower, upper, 32, static_cast<cuuint32_t>(h.P), estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   lower, upper, SLAB, static_cast<cuuint32_t>(h.P), estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   SLAB == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   XTC_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeIm2col (halo) failed (%d)", static_cast<int>(r));
   int rc;
@@ -206,43 +211,59 @@ int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
   p.status = device_status_word(dev);
   XTC_REQUIRE(p.status != nullptr, "conv2d: device status word unavailable");
   p.Q = a.B * Hp * Wp;
-  p.tiles = static_cast<int>((p.Q + BM - 1) / BM);
+  const int tile_positions = PAIR ? 2 * BM : BM;
+  p.tiles = static_cast<int>((p.Q + tile_positions - 1) / tile_positions);
   p.Hp = static_cast<int>(Hp);
   p.Wp = static_cast<int>(Wp);
   p.OH = static_cast<int>(a.OH);
   p.OW = static_cast<int>(a.OW);
   p.F = static_cast<int>(a.F);
   p.nslab = h.nslab;
+  p.nblk = h.nblk;
   p.C = static_cast<int>(a.C);
   p.taps = static_cast<int>(a.R * a.S);
   p.S = static_cast<int>(a.S);
   p.pad_left = a.pl;
   p.pad_top = a.pt;
   p.stage_bytes = h.stage_bytes;
-  p.stage_tx = h.P * 128;
+  p.stage_tx = h.P * SLAB * 4;
   p.stages = a.stages >= 2 && a.stages < h.stages ? a.stages : h.stages;
   p.relu = a.relu;
   p.relu_threshold = a.thr;
 
-  auto kernel = conv2d_halo_kernel<BN>;
-  static thread_local int configured_dev = -1;
-  static thread_local int configured_smem = 0;
-  if (configured_dev != dev || configured_smem < h.smem) {
+  // two issuing threads whenever both accumulators fit in TMEM and there are taps to share
+  constexpr bool CAN_DUAL = BN <= 128;
+  const bool dual = CAN_DUAL && p.taps >= 2;
+  static_assert(!PAIR || SLAB == 32, "the CTA-pair kernel has 32-channel slabs only");
+  auto kernel = PAIR ? (dual ? conv2d_halo_pair_kernel<BN, CAN_DUAL> : conv2d_halo_pair_kernel<BN, false>)
+                     : (dual ? conv2d_halo_kernel<BN, CAN_DUAL, SLAB>
+                             : conv2d_halo_kernel<BN, false, SLAB>);
+  static thread_local int configured_dev[2] = {-1, -1};
+  static thread_local int configured_smem[2] = {0, 0};
+  const int which = dual ? 1 : 0;
+  if (configured_dev[which] != dev || configured_smem[which] < h.smem) {
     XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem));
-    configured_dev = dev;
-    configured_smem = h.smem;
+    configured_dev[which] = dev;
+    configured_smem[which] = h.smem;
   }
-  const int grid = p.tiles < sm_count(dev) ? p.tiles : sm_count(dev);
-  kernel<<<grid, NUM_THREADS, h.smem, a.stream>>>(tmX, tmW, p);
+  const int slots = PAIR ? sm_count(dev) / 2 : sm_count(dev);
+  const int grid = (p.tiles < slots ? p.tiles : slots) * (PAIR ? 2 : 1);
+  kernel<<<grid, HALO_THREADS, h.smem, a.stream>>>(tmX, tmW, p);
   XTC_CUDA_CHECK(cudaGetLastError());
   return XTC_CUDA_OK;
 }
 
-int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
+template <int BN>
+int dispatch_conv_halo_bn(const ConvArgs& a, const HaloPlan& h, bool pair) {
+  if (pair) return launch_conv_halo<BN, true, 32>(a, h);
+  return h.slab == 16 ? launch_conv_halo<BN, false, 16>(a, h) : launch_conv_halo<BN, false, 32>(a, h);
+}
+
+int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h, bool pair) {
   switch (h.bn) {
-    case 64: return launch_conv_halo<64>(a, h);
-    case 128: return launch_conv_halo<128>(a, h);
-    default: return launch_conv_halo<256>(a, h);
+    case 64: return dispatch_conv_halo_bn<64>(a, h, pair);
+    case 128: return dispatch_conv_halo_bn<128>(a, h, pair);
+    default: return dispatch_conv_halo_bn<256>(a, h, pair);
   }
 }
 
@@ -402,9 +423,19 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
   if (c.variant != 1) {
     // Resident weights + halo tiles: chosen when asked for, and by default when
     // the caller named no im2col-kernel parameter (pixel tile, K per stage).
-    const HaloPlan h = plan_halo(a);
+    // One CTA per tile: 32-channel slabs unless two stages of them do not fit next to
+    // the filter bank (measured on 32x56x56x64 -> 64, 3x3: five 16-channel stages are
+    // no faster than two 32-channel ones, 24.1 vs 23.4 us).  tile_k = 16 or 32 forces it.
+    HaloPlan h1 = plan_halo(a, false, 32);
+    const HaloPlan h16 = plan_halo(a, false, 16);
+    const bool narrow = c.tile_k == 16 || (c.tile_k != 32 && !h1.ok);
+    if (narrow && h16.ok) h1 = h16;
+    const HaloPlan h2 = plan_halo(a, true, 32);
+    // the pair kernel when asked for (tile_m = 256) or when only half a filter bank fits
+    const bool pair = c.tile_m == 2 * BM || (c.tile_m == 0 && !h1.ok && h2.ok);
+    const HaloPlan& h = pair ? h2 : h1;
     const bool wanted = c.variant == 2 || (c.tile_m == 0 && c.tile_k == 0);
-    if (h.ok && wanted) return dispatch_conv_halo(a, h);
+    if (h.ok && wanted) return dispatch_conv_halo(a, h, pair);
     if (c.variant == 2) {
       set_error("conv2d: the resident-weights variant needs stride 1 and a filter bank of at most "
                 "%d bytes next to two halo stages (R*S*C*F too large here)", 232448 - 2048);
