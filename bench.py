@@ -264,6 +264,42 @@ def bench_graph_device(torch, dev, name: str, steps: int, warmup: int, precision
     return info
 
 
+def measure_e2e(torch, dev, handle, cfg, workload: str, steps: int) -> dict:
+    """The same steps through host buffers: every step copies its inputs from pinned
+    host memory to the device and its result back.  Returns seconds per step of the
+    pipelined executor and of the synchronous call, and the bytes moved per step."""
+    from xtc_b200 import configs
+
+    host_ins = [pinned_like(dev, h) for h in configs.inputs(workload)]
+    host_out = pinned_like(dev, np.zeros(cfg.output_shape, np.float32))
+    e2e_steps = max(3, min(steps, 20))
+    for _ in range(2):
+        handle.run_host(host_ins + [host_out])
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        handle.run_host(host_ins + [host_out])  # H2D inputs, run, D2H result, synchronise
+    e2e_sync_sec = (time.perf_counter() - t0) / e2e_steps
+    # the same steps through the pipelined executor: every step still copies all of its
+    # inputs in and its result out, but step i+1's input copy and step i-1's output copy
+    # overlap step i's kernels
+    pipe = handle.pipeline(depth=3)
+    host_outs = [host_out] + [pinned_like(dev, host_out) for _ in range(2)]
+    for i in range(3):
+        pipe.submit(host_ins + [host_outs[i % 3]])
+    pipe.wait()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        pipe.submit(host_ins + [host_outs[i % 3]])
+    pipe.wait()
+    e2e_sec = (time.perf_counter() - t0) / e2e_steps
+    pipe.close()
+    h2d = int(sum(h.nbytes for h in host_ins))
+    d2h = int(host_out.nbytes)
+
+    return {"sec": e2e_sec, "sync_sec": e2e_sync_sec, "h2d": h2d, "d2h": d2h, "steps": e2e_steps}
+
+
 def roofline_of(cfg, seconds: float, peaks: dict, workload: str, sustained: bool) -> dict:
     if cfg.bound == "hbm":
         achieved = cfg.bytes / seconds / 1e9
@@ -296,40 +332,14 @@ def run_single(args) -> None:
     sampler.start()
     info = bench_graph_device(torch, dev, workload, args.steps, args.warmup,
                               precision=args.precision,
-                              fuse_transpose=True if args.fuse_transpose else None)
+                              fuse_transpose=False if args.unfused_transpose else None)
     clocks = sampler.stop()
     cfg, plan = info["cfg"], info["plan"]
     sec = info["seconds"]
     launches_per_step = len(plan.steps) + (2 if args.precision == "3xtf32" else 0)
 
     # ---- end to end through host buffers ("e2e") ------------------------------
-    host_ins = [pinned_like(dev, h) for h in configs.inputs(workload)]
-    host_out = pinned_like(dev, np.zeros(cfg.output_shape, np.float32))
-    handle = info["handle"]
-    e2e_steps = max(3, min(args.steps, 20))
-    for _ in range(2):
-        handle.run_host(host_ins + [host_out])
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        handle.run_host(host_ins + [host_out])  # H2D inputs, run, D2H result, synchronise
-    e2e_sync_sec = (time.perf_counter() - t0) / e2e_steps
-    # the same steps through the pipelined executor: every step still copies all of its
-    # inputs in and its result out, but step i+1's input copy and step i-1's output copy
-    # overlap step i's kernels
-    pipe = handle.pipeline(depth=3)
-    host_outs = [host_out] + [pinned_like(dev, host_out) for _ in range(2)]
-    for i in range(3):
-        pipe.submit(host_ins + [host_outs[i % 3]])
-    pipe.wait()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        pipe.submit(host_ins + [host_outs[i % 3]])
-    pipe.wait()
-    e2e_sec = (time.perf_counter() - t0) / e2e_steps
-    pipe.close()
-    h2d = int(sum(h.nbytes for h in host_ins))
-    d2h = int(host_out.nbytes)
+    e2e = None if args.no_e2e else measure_e2e(torch, dev, info["handle"], cfg, workload, args.steps)
 
     unit_work = cfg.flops if cfg.flops else cfg.bytes
     scale = 1e12 if cfg.flops else 1e9
@@ -345,11 +355,12 @@ def run_single(args) -> None:
                          f"{info['set_bytes'] / 1e6:.0f} MB (> 126 MB L2 in total)"},
         "roofline": roofline_of(cfg, statistics.median(info["per_step"]), peaks, workload,
                                 sustained=sec * args.steps > 1.0),
-        "e2e": {"value": unit_work / e2e_sec / scale, "unit": unit, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
-                "api": "xtc_cuda_pipeline_submit/wait, depth 3 (pinned host buffers)",
-                "synchronous_ms_per_step": e2e_sync_sec * 1e3,
-                "synchronous_api": "xtc_cuda_plan_run_host"},
+        "e2e": None if e2e is None else {
+            "value": unit_work / e2e["sec"] / scale, "unit": unit, "h2d_bytes_per_step": e2e["h2d"],
+            "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e["sec"] * 1e3, "steps": e2e["steps"],
+            "api": "xtc_cuda_pipeline_submit/wait, depth 3 (pinned host buffers)",
+            "synchronous_ms_per_step": e2e["sync_sec"] * 1e3,
+            "synchronous_api": "xtc_cuda_plan_run_host"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
@@ -543,12 +554,15 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
-    ap.add_argument("--fuse-transpose", action="store_true")
+    ap.add_argument("--unfused-transpose", action="store_true",
+                    help="c4: run the transpose as its own kernel instead of reading A transposed")
     ap.add_argument("--chunks", type=int, default=1, help="row chunks overlapped with the exchange (N>1)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="c5 at N>1: fused peer stores in the GEMM epilogue, or an NCCL all-gather")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
+    ap.add_argument("--no-e2e", action="store_true",
+                    help="skip the host-buffer leg (for profiler runs; the line then has e2e null)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     world = int(os.environ.get("WORLD_SIZE", "1"))

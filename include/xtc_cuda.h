@@ -82,7 +82,7 @@ enum {
  * the reference records the same directives in
  * src/xtc/backends/mlir/MlirNodeScheduler.py:84-170. */
 typedef struct xtc_cuda_gemm_config {
-  int32_t tile_m;    /* CTA tile rows     : 128                                   */
+  int32_t tile_m;    /* CTA tile rows     : 128, or 256 = one tile per CTA pair    */
   int32_t tile_n;    /* CTA tile columns  : 64, 128 or 256                        */
   int32_t tile_k;    /* K per pipeline stage: 32 or 64                            */
   int32_t stages;    /* shared-memory ring depth (0 = as many as fit)             */
@@ -93,7 +93,11 @@ typedef struct xtc_cuda_gemm_config {
   int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off (the
                         default: it did not pay on the shapes measured).  Needs the
                         workspace of xtc_cuda_gemm_workspace_bytes, zeroed before its
-                        first use (the kernel leaves its counters zero again)        */
+                        first use (the kernel leaves its counters zero again).
+                        With tile_m = 256: 0 = when the last round of tiles would leave
+                        CTA pairs idle, share the K blocks of the last tiles out evenly
+                        (same workspace rule; without a workspace the tiles simply go
+                        round-robin); 1 = never                                      */
 } xtc_cuda_gemm_config;
 
 /* C[M,N] = A[M,K] * B[K,N]  (+ optional relu).  Replaces the loop nest the

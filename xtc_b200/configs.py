@@ -74,8 +74,12 @@ def inputs(name: str, scale: int = 1, batch: int | None = None) -> list[np.ndarr
 
 
 def _gemm_schedule(tile_n: int, tile_k: int, stages: int = 0, tma_store: bool = True,
-                   tile_m: int = 128):
+                   tile_m: int = 128, fuse_a: bool = False):
     def apply(sch: Any) -> None:
+        if fuse_a:
+            # read the transposed operand in place (column-major A tiles) instead of
+            # materialising the transpose: on c4, 193 us against 293 us
+            sch.fuse_producer_at("i", 0)
         sch.tile("i", {"i1": tile_m})  # 256 rows = the CTA-pair kernel
         sch.tile("j", {"j1": tile_n})
         sch.tile("k", {"k1": tile_k})
@@ -145,7 +149,7 @@ def build(name: str, scale: int = 1, batch: int | None = None, rows: int | None 
             O.matmul(t, w, name="mm")
         return Config(name, gb.graph, "mm", [(n, n), (n, j)], (n, j), 2 * n * n * j,
                       4 * (n * n + n * j + n * j) + 8 * n * n, "tensor", "",
-                      _gemm_schedule(256, 64, tile_m=256))
+                      _gemm_schedule(256, 64, tile_m=256, fuse_a=True))
     if name == "c5":
         k = _scaled(8192, s)
         m = rows if rows is not None else _scaled(65536, s)

@@ -89,7 +89,18 @@ struct LaunchArgs {
   int split_k = 1;        // CTAs per output tile along K (needs partials + counters)
   float* partials = nullptr;
   int* counters = nullptr;
+  // CTA-pair kernel: zeroed workspace for the split tail (pair_tail_bytes), or NULL
+  void* pair_tail = nullptr;
 };
+
+// Workspace of the pair kernel's split tail: at most `pairs` parked pieces, each
+// with 8 flags and one 256 x tile_n raw accumulator.
+size_t pair_tail_flag_bytes(int pairs) {
+  return (static_cast<size_t>(pairs) * 8 * sizeof(int) + 255) & ~static_cast<size_t>(255);
+}
+size_t pair_tail_bytes(int pairs, int tile_n) {
+  return pair_tail_flag_bytes(pairs) + static_cast<size_t>(pairs) * 256 * tile_n * sizeof(float);
+}
 
 template <int BN, int KSPANS, int A_MODE, bool B_MN, bool SPLIT3, bool TMA_STORE>
 int launch_tc(const LaunchArgs& a) {
@@ -240,6 +251,19 @@ int launch_pair(const LaunchArgs& a) {
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  // Split tail: the tiles of a last round that would leave at least half of the
+  // pairs idle are cut along K, one piece per pair (see gemm_tf32_pair.cuh).
+  const int rem = tiles % pairs;
+  const int split = rem > 0 ? pairs / rem : 0;
+  if (a.pair_tail != nullptr && tiles > pairs && split >= 2 && pairs <= sm_count(dev) / 2) {
+    p.tail_split = split < p.k_blocks ? split : p.k_blocks;
+    p.tail_tiles = rem;
+    p.tail_first = tiles - rem;
+    p.sk_flags = static_cast<int*>(a.pair_tail);
+    p.sk_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a.pair_tail) +
+                                             pair_tail_flag_bytes(sm_count(dev) / 2));
+    if (p.tail_split < 2) p.tail_split = 0;
+  }
   kernel<<<2 * pairs, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmC, p, stages);
   XTC_CUDA_CHECK(cudaGetLastError());
   return XTC_CUDA_OK;
@@ -383,10 +407,15 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
     *bytes = 2 * align256(static_cast<size_t>(M) * K * 4) + 2 * align256(static_cast<size_t>(K) * N * 4);
     return XTC_CUDA_OK;
   }
+  int dev = 0;
+  int sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
+  if (c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m == 2 * BM && c.split_k != 1) {
+    // the CTA-pair kernel's split tail (split_k = 1 turns it off)
+    *bytes = pair_tail_bytes(sms / 2, c.tile_n ? c.tile_n : 256);
+    return XTC_CUDA_OK;
+  }
   if (c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m != 2 * BM) {
-    int dev = 0;
-    int sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
     const TfShape s = resolve_tf32_shape(M, N, K, c, sms);
     if (s.split_k > 1)  // tile counters, then the partial tiles [split][tile][128][tile_n]
       *bytes = align256(static_cast<size_t>(s.tiles) * 4) +
@@ -451,7 +480,12 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   if (c.tile_m == 2 * BM) {
     XTC_REQUIRE(c.precision == XTC_CUDA_PRECISION_TF32, "gemm: tile_m=256 is a TF32-only configuration");
     XTC_REQUIRE(tma_addressable(C, ldc), "gemm: tile_m=256 needs a 16-byte aligned C with ldc %% 4 == 0");
-    return dispatch_pair(a, c.tile_n ? c.tile_n : 256, c.tile_k ? c.tile_k : 32);
+    const int tn = c.tile_n ? c.tile_n : 256;
+    // the split tail is an optimisation: without a (zeroed) workspace the tiles go round-robin
+    if (c.split_k != 1 && workspace != nullptr &&
+        workspace_bytes >= pair_tail_bytes(sm_count(dev) / 2, tn))
+      a.pair_tail = workspace;
+    return dispatch_pair(a, tn, c.tile_k ? c.tile_k : 32);
   }
   const TfShape shp = resolve_tf32_shape(M, N, K, c, sm_count(dev));
   int tile_n = c.tile_n ? c.tile_n : shp.tile_n;

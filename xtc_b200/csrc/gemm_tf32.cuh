@@ -59,6 +59,14 @@ struct GemmParams {
   int split_kblocks;
   float* partials;
   int* tile_counters;
+  // Split tail of the CTA-pair kernel (gemm_tf32_pair.cuh): the tail_tiles tiles of
+  // the last, partly idle round are each cut into tail_split pieces along K, one
+  // piece per pair.  tail_split = 0 turns it off.
+  int tail_first;      // index of the first tail tile (= tiles - tail_tiles)
+  int tail_tiles;
+  int tail_split;
+  int* sk_flags;       // [tail tile][piece - 1][8 slabs]: "parked" flags (zeroed once)
+  float* sk_partials;  // [tail tile][piece - 1][8 slabs][32 x BN] raw accumulators
 };
 
 template <int BN, int KSPANS, bool SPLIT3>

@@ -11,10 +11,76 @@
 //   empty[s]     one per CTA.  The leader commits to both after the MMAs of a stage.
 //   acc_full[a]  one per CTA.  The leader commits to both after the last MMA of a tile.
 //   acc_empty[a] leader only, 8 arrivals: the 4 epilogue warps of both CTAs.
+//
+// Split tail.  With T tiles on P pairs the last of ceil(T/P) rounds is partly idle
+// (4096^3: 256 tiles on 74 pairs, 3.46 rounds of work in 4).  When the launcher
+// provides a workspace and the rem = T mod P tiles of the last round number at
+// most P/2, each of them is cut into S = floor(P/rem) pieces along K and every
+// piece goes to a pair of its own, so the last round lasts 1/S as long.  Pieces
+// 1..S-1 park their raw accumulators in the workspace; the pair that holds piece
+// 0 waits for them, adds them to its own in piece order (so the result does not
+// depend on timing) and stores the tile.  All pieces of a round start together,
+// so tiles that share an operand panel still stream it in step and L2 serves the
+// re-reads; cutting K into contiguous per-pair ranges instead (stream-K) was
+// measured slower than no split at all for that reason (4096^3: 210 us against
+// 198 us; 8192x1024x8192: 278 us against 190 us).
 #pragma once
 #include "gemm_tf32.cuh"
 
 namespace xtc {
+
+struct PairWork {
+  int tile, kb0, kb1;
+  int piece;  // 0 = this pair stores the tile; > 0 = it parks its accumulator
+  int split;  // pieces the tile is cut into (1 = whole tile)
+  int tail;   // index of the tile among the tail tiles
+};
+
+// The sequence of work items of one pair; the producer, the MMA issuer and the
+// epilogue warps each walk their own copy.
+struct PairWorkIter {
+  int next_tile, stride, pair;
+  bool tail_done;
+  __device__ PairWorkIter(int pair_, int num_pairs)
+      : next_tile(pair_), stride(num_pairs), pair(pair_), tail_done(false) {}
+  __device__ bool next(const GemmParams& p, PairWork& w) {
+    const int whole = p.tail_split > 0 ? p.tail_first : p.tiles_m * p.tiles_n;
+    if (next_tile < whole) {
+      w.tile = next_tile;
+      w.kb0 = 0;
+      w.kb1 = p.k_blocks;
+      w.piece = 0;
+      w.split = 1;
+      w.tail = 0;
+      next_tile += stride;
+      return true;
+    }
+    if (p.tail_split > 0 && !tail_done && pair < p.tail_tiles * p.tail_split) {
+      tail_done = true;
+      w.tail = pair / p.tail_split;
+      w.piece = pair - w.tail * p.tail_split;
+      w.split = p.tail_split;
+      w.tile = p.tail_first + w.tail;
+      w.kb0 = static_cast<int>(static_cast<long long>(p.k_blocks) * w.piece / p.tail_split);
+      w.kb1 = static_cast<int>(static_cast<long long>(p.k_blocks) * (w.piece + 1) / p.tail_split);
+      return true;
+    }
+    return false;
+  }
+};
+
+// Bounded wait (about 2 s) for a flag in global memory that another CTA sets.
+__device__ __forceinline__ bool wait_flag_set(int* flag) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (atomicAdd(flag, 0) != 0) return true;
+    if ((it & 0xff) == 0xff) {
+      const uint64_t now = dev::globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) return false;
+    }
+  }
+}
 
 template <int BN, int KSPANS>
 struct PairSmem {
@@ -86,7 +152,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x BN
   bool failed = false;
 
   if (warp == 0) {
@@ -94,9 +159,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
+      PairWorkIter work(pair, num_pairs);
+      PairWork w;
+      while (!failed && work.next(p, w)) {
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(w.tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
         const int n0 = tn * BN + static_cast<int>(rank) * HALF;
         int img = 0, ih0 = 0, iw0 = 0;  // input pixel under the filter origin of row m0
@@ -107,7 +174,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           ih0 = oh * p.conv_stride_h - p.conv_pad_top;
           iw0 = (rem - oh * p.conv_ow) * p.conv_stride_w - p.conv_pad_left;
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
             failed = true;
@@ -160,7 +227,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
-      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local) {
+      PairWorkIter work(pair, num_pairs);
+      PairWork w;
+      for (; !failed && work.next(p, w); ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
@@ -170,7 +239,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase)) {
             atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
             failed = true;
@@ -185,7 +254,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                                      : umma_desc_hi(1024, (uint32_t)UMMA_SWIZZLE_128B);
           const uint32_t a_lo = umma_desc_lo(sA, A_MN ? BK * 128 : 16);
           const uint32_t b_lo = umma_desc_lo(sB, B_MN ? BK * 128 : 16);
-          const uint32_t first = kb != 0 ? 1u : 0u;
+          const uint32_t first = kb != w.kb0 ? 1u : 0u;
 #pragma unroll
           for (int kk = 0; kk < BK / 8; ++kk) {
             const uint32_t aoff = (A_MN ? kk * 1024 : (kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
@@ -218,9 +287,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     int local = 0;
     int buf = 0;
-    for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local) {
+    PairWorkIter work(pair, num_pairs);
+    PairWork w;
+    for (; !failed && work.next(p, w); ++local) {
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, tm, tn);
       const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
       const int n0 = tn * BN;
       const int acc = local & 1;
@@ -231,11 +302,50 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         break;
       }
       tc_fence_after();
+      // A tail tile cut along K: this warp's 32 x BN slab is either parked for the
+      // pair that holds piece 0, or (piece 0) completed with the parked slabs.
+      const size_t my_slab = rank * 4 + quad;
+      const size_t tail_base = static_cast<size_t>(w.tail) * (p.tail_split > 1 ? p.tail_split - 1 : 1);
+      if (w.split > 1 && w.piece == 0) {
+        int ok = 1;
+        if (lane == 0)
+          for (int j = 0; j < w.split - 1 && ok; ++j)
+            ok = wait_flag_set(p.sk_flags + (tail_base + j) * 8 + my_slab) ? 1 : 0;
+        if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
+          if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+          failed = true;
+          break;
+        }
+        __threadfence();
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + lane_base + acc * BN + c * 32, r);
         tmem_ld_wait();
+        if (w.piece > 0) {
+          // lane-interleaved layout: each store instruction writes 512 contiguous bytes
+          float4* parked = reinterpret_cast<float4*>(
+              p.sk_partials + ((tail_base + w.piece - 1) * 8 + my_slab) * (32 * BN));
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            parked[(c * 8 + j) * 32 + lane] =
+                make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          continue;
+        }
+        for (int piece = 1; piece < w.split; ++piece) {
+          const float4* parked = reinterpret_cast<const float4*>(
+              p.sk_partials + ((tail_base + piece - 1) * 8 + my_slab) * (32 * BN));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = __ldcg(&parked[(c * 8 + j) * 32 + lane]);
+            r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+            r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+            r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+            r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+          }
+        }
         if (p.relu) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -274,6 +384,15 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           }
         }
         buf ^= 1;
+      }
+      if (w.piece > 0) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicExch(p.sk_flags + (tail_base + w.piece - 1) * 8 + my_slab, 1);
+      } else if (w.split > 1) {
+        __syncwarp();
+        if (lane == 0)  // leave the flags as the next launch expects them
+          for (int j = 0; j < w.split - 1; ++j) p.sk_flags[(tail_base + j) * 8 + my_slab] = 0;
       }
       tc_fence_before();
       __syncwarp();
