@@ -39,7 +39,7 @@ sys.path.insert(0, str(ROOT))
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes per launch of the dominant kernel from one ncu capture each
 # (dram__bytes_read.sum + dram__bytes_write.sum, see profiles/); None = not captured.
-NCU_TRAFFIC = {"c1": None, "c2": 395.1e6, "c3": 25.9e6, "c4": None, "c5": None}
+NCU_TRAFFIC = {"c1": None, "c2": 395.1e6, "c3": 25.9e6, "c4": None, "c4a": 488.7e6, "c5": None}
 
 
 def measured_peaks() -> dict:
@@ -143,7 +143,8 @@ def time_cpu(workload: str, steps: int, warmup: int) -> dict:
         cb.run_config(workload, ins)
         times.append(time.perf_counter() - t0)
     t = min(times)
-    return {"value": cfg.flops * frac / t / 1e12, "unit": "TFLOP/s", "cores": cb.threads(),
+    work, unit = (cfg.flops / 1e12, "TFLOP/s") if cfg.flops else (cfg.bytes / 1e9, "GB/s")
+    return {"value": work * frac / t, "unit": unit, "cores": cb.threads(),
             "kind": "port", "sample": f"{desc}; best of {len(times)} runs, {t * 1e3:.1f} ms each",
             "seconds_per_sample": t}
 
@@ -158,12 +159,12 @@ def run_reference(args, rank: int, world: int) -> None:
     t = base.pop("seconds_per_sample")
     line = {
         "impl": "reference", "metric": "graph_throughput", "value": base["value"],
-        "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warm,
+        "unit": base["unit"], "n_gpus": world, "steps": steps, "warmup": warm,
         "ms_per_step": t * 1e3, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": workload_name(workload)},
         "cpu_baseline": base,
-        "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+        "e2e": {"value": base["value"], "unit": base["unit"], "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "note": ("the reference's MLIR llvmir backend cannot be built on this box (no MLIR/LLVM "
                  "toolchain); this is its loop nest restated in C, OpenMP over the host cores"),
@@ -177,6 +178,7 @@ def workload_name(w: str) -> str:
         "c2": "c2: matmul 4096^3 + relu f32 (configs[1])",
         "c3": "c3: pad + conv2d 3x3 + relu, NHWC 32x56x56x64 -> 64 f32",
         "c4": "c4: transpose 8192^2 + matmul 8192x8192x1024 f32",
+        "c4a": "c4a: transpose 8192^2 f32 alone",
         "c5": "c5: row-sharded matmul 65536x8192x8192 f32 + all-gather",
     }[w]
 
@@ -348,7 +350,8 @@ def run_single(args) -> None:
         "metric": "graph_throughput", "value": unit_work / sec / scale, "unit": unit,
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "tf32" if args.precision == "tf32" else args.precision, "data": "synthetic",
+        "dtype": ("f32" if not cfg.flops else "tf32" if args.precision == "tf32" else args.precision),
+        "data": "synthetic",
         "config": {"workload": workload_name(workload), "precision": args.precision,
                    "kernel_config": plan.steps[-1].config, "fused": [list(s.fused) for s in plan.steps],
                    "l2": f"inputs rotate over {info['n_sets']} buffer sets of "
@@ -552,7 +555,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default=None, choices=["c1", "c2", "c3", "c4", "c4a", "c5"])
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
     ap.add_argument("--unfused-transpose", action="store_true",
                     help="c4: run the transpose as its own kernel instead of reading A transposed")

@@ -90,7 +90,9 @@ def transpose2d(x: np.ndarray) -> np.ndarray:
 
 
 def run_config(name: str, inputs) -> np.ndarray:
-    """The five benchmark graphs on the CPU loop nests."""
+    """The benchmark graphs on the CPU loop nests."""
+    if name == "c4a":
+        return transpose2d(inputs[0])
     a, b = inputs
     if name == "c1":
         return matmul(a, b)

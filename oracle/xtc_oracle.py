@@ -221,6 +221,8 @@ def config_inputs(name: str, scale: int = 1) -> list[np.ndarray]:
         n = 8192 // s
         return [rng.uniform(-1, 1, (n, n)).astype(np.float32),
                 rng.normal(0, 0.02, (n, 1024 // s)).astype(np.float32)]
+    if name == "c4a":
+        return config_inputs("c4", s)[:1]
     if name == "c5":
         rng = np.random.default_rng(4)
         k = 8192 // s
@@ -231,6 +233,8 @@ def config_inputs(name: str, scale: int = 1) -> list[np.ndarray]:
 
 def config_forward(name: str, inputs: Sequence[np.ndarray]) -> np.ndarray:
     """Output of configuration `name` on `inputs` in the dtype of the inputs."""
+    if name == "c4a":
+        return transpose(inputs[0], (1, 0))
     a, b = inputs
     if name == "c1":
         return matmul(a, b)

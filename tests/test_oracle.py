@@ -96,7 +96,7 @@ def test_cpu_loopnest_matches_oracle():
     """The C loop nests (the timed CPU baseline) agree with the NumPy oracle."""
     from oracle import cpu_baseline as cb
 
-    for name, scale in [("c1", 4), ("c2", 32), ("c3", 32), ("c4", 64), ("c5", 128)]:
+    for name, scale in [("c1", 4), ("c2", 32), ("c3", 32), ("c4", 64), ("c4a", 64), ("c5", 128)]:
         ins = xo.config_inputs(name, scale)
         y64 = xo.config_forward(name, [x.astype(np.float64) for x in ins])
         got = cb.run_config(name, ins)

@@ -79,6 +79,39 @@ def test_exploration_csv_and_resume(tmp_path, monkeypatch):
     assert len(list(csv.DictReader(open(out)))) == 9
 
 
+def test_graph_file_and_named_operations(tmp_path, monkeypatch, capsys):
+    """``--graph-file`` explores a graph saved as YAML (the reference's
+    tests/graphs/*.graph.yaml format); ``--op-name`` takes the dims of a registered
+    operation; ``--op-name-list`` prints the registry."""
+    from xtc_b200 import artifacts
+    from xtc_b200.search import explore
+
+    path = tmp_path / "mm_relu.graph.yaml"
+    matmul_graph(384, 640, 256, relu=True).dump(path)
+    exp = Exploration(ExplorationConfig(graph_file=str(path), peak_flops=1e15))
+    assert [n.operation.name for n in exp.graph.nodes.values()] == ["matmul", "relu"]
+    assert exp.fma_count() == 384 * 640 * 256
+    assert exp.strategy._node.operation.name == "matmul"
+
+    named = Exploration(ExplorationConfig(operator="conv2d", op_name="c3_conv", peak_flops=1e15))
+    assert named.fma_count() == 32 * 56 * 56 * 64 * 3 * 3 * 64
+    with pytest.raises(ValueError):
+        Exploration(ExplorationConfig(operator="matmul", op_name="no_such_layer"))
+    artifacts.register_operation("matmul", "tiny", {"i": 128, "j": 64, "k": 32})
+    assert Exploration(ExplorationConfig(operator="matmul", op_name="Tiny", peak_flops=1e15)).fma_count() == 128 * 64 * 32
+
+    assert explore.main(["--op-name-list"]) == 0
+    listed = capsys.readouterr().out.split("\n")
+    assert "conv2d c3_conv" in listed and "matmul_relu c2" in listed
+
+    seen = []
+    monkeypatch.setattr(Exploration, "evaluate_one",
+                        lambda self, module, sample: (seen.append(sample) or (sample, 0, 1e-6, "cuda")))
+    rc = explore.main(["--graph-file", str(path), "--opt-level", "2", "--peak-flops", "1e15",
+                       "--output", str(tmp_path / "r.csv"), "--explore-dir", str(tmp_path / "x")])
+    assert rc == 0 and len(seen) == 1
+
+
 @pytest.mark.gpu
 def test_exhaustive_search_on_gpu(tmp_path):
     out = tmp_path / "res.csv"

@@ -183,7 +183,25 @@ class CudaEvaluator:
         self._rtol = kwargs.get("rtol", 1e-5)
         self._atol = kwargs.get("atol", 1e-8)
         device = kwargs.get("device", kwargs.get("runtime"))
+        if device is None:
+            device = self._graph_device(module.graph)
         self._device = device if isinstance(device, CudaDevice) else CudaDevice(int(device or 0))
+
+    @staticmethod
+    def _graph_device(graph: Any) -> CudaDevice | None:
+        """The device a graph's tensors were declared on with ``O.tensor(..., device=gpu)`` /
+        ``O.matmul(..., device=gpu)`` (the reference's offload tensors,
+        ``tests/filecheck/backends/target_gpu/test_matmul_mlir_offload_tensor.py:8-19``): every
+        tensor lives in device memory here anyway, so the declaration only picks the GPU."""
+        if graph is None:
+            return None
+        types = list(getattr(graph, "inputs_types", None) or []) + list(
+            getattr(graph, "outputs_types", None) or [])
+        for t in types:
+            dev = getattr(t, "device", None)
+            if isinstance(dev, CudaDevice):
+                return dev
+        return None
 
     @property
     def module(self) -> CudaModule:

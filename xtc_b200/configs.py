@@ -22,7 +22,7 @@ import numpy as np
 
 from .graphs.xtc import op as O
 
-NAMES = ("c1", "c2", "c3", "c4", "c5")
+NAMES = ("c1", "c2", "c3", "c4", "c4a", "c5")
 
 
 @dataclass
@@ -65,6 +65,8 @@ def inputs(name: str, scale: int = 1, batch: int | None = None) -> list[np.ndarr
         n = _scaled(8192, s)
         return [rng.uniform(-1, 1, (n, n)).astype(np.float32),
                 rng.normal(0, 0.02, (n, _scaled(1024, s))).astype(np.float32)]
+    if name == "c4a":
+        return inputs("c4", s)[:1]
     if name == "c5":
         rng = np.random.default_rng(4)
         k = _scaled(8192, s)
@@ -150,6 +152,13 @@ def build(name: str, scale: int = 1, batch: int | None = None, rows: int | None 
         return Config(name, gb.graph, "mm", [(n, n), (n, j)], (n, j), 2 * n * n * j,
                       4 * (n * n + n * j + n * j) + 8 * n * n, "tensor", "",
                       _gemm_schedule(256, 64, tile_m=256, fuse_a=True))
+    if name == "c4a":  # the transpose of c4 alone: a pure data-movement graph
+        n = _scaled(8192, s)
+        x = O.tensor((n, n), "float32", name="X")
+        with O.graph(name="c4a_transpose") as gb:
+            O.transpose(x, axes=(1, 0), name="xt")
+        return Config(name, gb.graph, "xt", [(n, n)], (n, n), 0, 8 * n * n, "hbm", "",
+                      lambda sch: None)
     if name == "c5":
         k = _scaled(8192, s)
         m = rows if rows is not None else _scaled(65536, s)

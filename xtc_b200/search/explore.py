@@ -68,6 +68,8 @@ class ExplorationConfig:
     operator: str = "matmul"
     dims: list[int] | None = None
     graph: Any = None               # an already built graph overrides operator/dims
+    graph_file: str | None = None   # a graph saved with Graph.dump (YAML) overrides operator/dims
+    op_name: str | None = None      # dims of a registered operation (xtc_b200.artifacts)
     strategy: str | None = None
     search: str = "random"          # random | exhaustive
     trials: int = 20
@@ -93,9 +95,16 @@ class Exploration:
         self.config = config
         if config.graph is not None:
             self.graph = config.graph
+        elif config.graph_file is not None:
+            self.graph = self.load_graph(config.graph_file)
         else:
             spec = OPERATORS[config.operator]
             dims = config.dims or spec["default_dims"]
+            if config.op_name:
+                from .. import artifacts
+
+                named = artifacts.get_operation(config.operator, config.op_name)["dims"]
+                dims = [named[d] for d in spec["dims"]]
             assert len(dims) == len(spec["dims"]), (
                 f"{config.operator} takes dims {spec['dims']}, got {dims}")
             if config.operator == "conv2d":
@@ -106,6 +115,14 @@ class Exploration:
         self.strategy = Strategies.create(name, self.graph, **config.strategy_options)
         self.results: list[tuple[list[int], int, float, str]] = []
         self._peak_time: float | None = None
+
+    @staticmethod
+    def load_graph(graph_file: str) -> Any:
+        """A graph written by ``Graph.dump`` (the reference's ``--graph-file``,
+        ``search/explore.py:211-217``)."""
+        with O.graph() as gb:
+            gb.load(graph_file)
+        return gb.graph
 
     # -- peak -----------------------------------------------------------------------
     def fma_count(self) -> int:
@@ -216,6 +233,9 @@ def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(prog="loop-explore (cuda)", description=__doc__.split("\n")[0])
     ap.add_argument("--operator", default="matmul", choices=sorted(OPERATORS))
     ap.add_argument("--dims", nargs="+", type=int, help="dimensions, default to the operator's default")
+    ap.add_argument("--graph-file", default=None, help="explore a graph saved as YAML instead of an operator")
+    ap.add_argument("--op-name", default=None, help="dims of a registered operation, see --op-name-list")
+    ap.add_argument("--op-name-list", action="store_true", help="list the registered operations and exit")
     ap.add_argument("--strategy", default=None, choices=Strategies.names())
     ap.add_argument("--search", default="random", choices=["random", "exhaustive"])
     ap.add_argument("--backends", nargs="+", default=["cuda"], choices=["cuda"])
@@ -237,7 +257,14 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--debug", action="store_true")
     args = ap.parse_args(argv)
     logging.basicConfig(level=logging.DEBUG if args.debug else logging.INFO)
+    if args.op_name_list:
+        from .. import artifacts
+
+        for operator, name in artifacts.list_operations():
+            print(f"{operator} {name}")
+        return 0
     cfg = ExplorationConfig(
+        graph_file=args.graph_file, op_name=args.op_name,
         operator=args.operator, dims=args.dims, strategy=args.strategy, search=args.search,
         trials=args.trials, seed=args.seed, opt_level=args.opt_level, output=args.output,
         resume=args.resume, repeat=args.repeat, number=args.number,
