@@ -56,6 +56,10 @@ typedef CUresult (*encode_im2col_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32
 encode_tiled_fn get_encode_tiled();
 encode_im2col_fn get_encode_im2col();
 
+// Rank-4 fp32 map without swizzle: dims / box innermost first, strides (in floats) of dims 1..3.
+// Returns false (no error recorded) when the driver rejects the geometry.
+bool make_tmap_4d_plain(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                        const uint64_t strides[3], const uint32_t box[4]);
 // 2-D fp32 tiled map over a row-major [rows, cols] matrix with leading
 // dimension ld (elements).  box = {box_cols, box_rows}.
 int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
@@ -175,6 +179,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
                    reinterpret_cast<uint64_t>(m)),
                "r"(smem_u32(src)), "r"(x), "r"(y)
                : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");

@@ -140,6 +140,107 @@ transpose_tile_kernel(const float* __restrict__ x, float* __restrict__ y, Tile2D
   }
 }
 
+// The same tile transpose with the global traffic handed to TMA: a persistent CTA
+// keeps three 64x64 input tiles in flight (bulk tensor loads, zero-filled at the
+// edges) and two output tiles draining (bulk tensor stores, clipped at the edges),
+// and its threads only move data between the two shared-memory tiles.  Both tiles
+// are dense, so lane l of a warp walks a diagonal of its 32x32 block: element
+// (l, (l+i) mod 32) in step i, whose bank is (l+i) mod 32 on the read side and l on
+// the write side; no padding, no conflicts.
+constexpr int TT = 64;
+constexpr int TT_STAGES = 3;
+constexpr int TT_TILE_BYTES = TT * TT * 4;
+constexpr int TT_SMEM = 1024 + (TT_STAGES + 2) * TT_TILE_BYTES + 64;
+
+struct TmaTransposeParams {
+  long long tiles_c, tiles_r, b0;  // tile grid: along the input's inner axis, its row axis, first batch axis
+  long long total;                 // tiles_c * tiles_r * b0 * b1
+  int* status;
+};
+
+__global__ void __launch_bounds__(256, 2)
+transpose_tma_kernel(const __grid_constant__ CUtensorMap tmIn,
+                     const __grid_constant__ CUtensorMap tmOut, const TmaTransposeParams p) {
+  using namespace dev;
+  extern __shared__ uint8_t tt_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tt_smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  float* in_tiles = reinterpret_cast<float*>(smem);
+  float* out_tiles = reinterpret_cast<float*>(smem + TT_STAGES * TT_TILE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (TT_STAGES + 2) * TT_TILE_BYTES);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  auto coords = [&](long long t, int& c0, int& r0, int& i0, int& i1) {
+    const long long tc = t % p.tiles_c; t /= p.tiles_c;
+    const long long tr = t % p.tiles_r; t /= p.tiles_r;
+    c0 = static_cast<int>(tc) * TT;
+    r0 = static_cast<int>(tr) * TT;
+    i0 = static_cast<int>(t % p.b0);
+    i1 = static_cast<int>(t / p.b0);
+  };
+  auto load = [&](long long t, int stage) {
+    int c0, r0, i0, i1;
+    coords(t, c0, r0, i0, i1);
+    mbar_arrive_expect_tx(&full[stage], TT_TILE_BYTES);
+    tma_load_4d(in_tiles + stage * (TT * TT), &tmIn, &full[stage], c0, r0, i0, i1);
+  };
+
+  if (tid == 0) {
+    prefetch_tmap(&tmIn);
+    prefetch_tmap(&tmOut);
+    for (int s = 0; s < TT_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const long long first = blockIdx.x, step = gridDim.x;
+  if (tid == 0)
+    for (int s = 0; s < TT_STAGES; ++s)
+      if (first + s * step < p.total) load(first + s * step, s);
+
+  const int blk = warp & 3;                 // which 32x32 block of the tile
+  const int br = (blk >> 1) * 32, bc = (blk & 1) * 32;
+  const int i_lo = (warp >> 2) * 16;        // which half of the 32 diagonal steps
+  int stage = 0, o = 0;
+  uint32_t phase = 0;
+  bool gave_up = false;
+  for (long long t = first; t < p.total; t += step) {
+    int failed = mbar_wait(&full[stage], phase) ? 0 : 1;
+    if (tid == 0) tma_store_wait_read<1>();  // the store issued two tiles ago has read out_tiles[o]
+    if (__syncthreads_or(failed)) {
+      if (tid == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+      gave_up = true;
+      break;
+    }
+    const float* src = in_tiles + stage * (TT * TT);
+    float* dst = out_tiles + o * (TT * TT);
+    const int r = br + lane;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int c = bc + ((lane + i_lo + i) & 31);
+      dst[c * TT + r] = src[r * TT + c];
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+      int c0, r0, i0, i1;
+      coords(t, c0, r0, i0, i1);
+      tma_store_4d(&tmOut, dst, r0, c0, i0, i1);
+      tma_store_commit();
+      const long long next = t + TT_STAGES * step;
+      if (next < p.total) load(next, stage);
+    }
+    if (++stage == TT_STAGES) {
+      stage = 0;
+      phase ^= 1;
+    }
+    o ^= 1;
+  }
+  if (gave_up) {  // let copies still in flight land before the shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  }
+  if (tid == 0) tma_store_wait_all<0>();
+}
+
 // Permutation that keeps the innermost axis: rows of `inner` contiguous floats
 // are copied whole; `vec` floats (4 or 1) per thread.
 struct RowCopyParams {
@@ -349,6 +450,46 @@ extern "C" int xtc_cuda_transpose_f32(const float* X, float* Y, int ndim, const 
   }
   p.vec_in = vin;
   p.vec_out = vout;
+  // TMA path: both sides addressable by a rank-4 tensor map (16-byte aligned base and
+  // pitches, at most two batch axes); anything else runs the load/store kernel below.
+  if (vin && vout && p.nbatch_dims <= 2 && p.R < (1ll << 31) && p.C < (1ll << 31)) {
+    const uint64_t b0 = p.nbatch_dims > 0 ? p.batch_shape[p.nbatch_dims - 1] : 1;
+    const uint64_t b1 = p.nbatch_dims > 1 ? p.batch_shape[0] : 1;
+    const uint64_t span = static_cast<uint64_t>(total + 3) & ~3ull;  // pitch of an absent axis
+    auto bstride = [&](const int64_t* st, int which) -> uint64_t {
+      if (which == 0) return p.nbatch_dims > 0 ? st[p.nbatch_dims - 1] : span;
+      return p.nbatch_dims > 1 ? st[0] : span;
+    };
+    const uint64_t in_dims[4] = {static_cast<uint64_t>(p.C), static_cast<uint64_t>(p.R), b0, b1};
+    const uint64_t in_st[3] = {static_cast<uint64_t>(p.in_r_stride), bstride(p.batch_in_stride, 0),
+                               bstride(p.batch_in_stride, 1)};
+    const uint64_t out_dims[4] = {static_cast<uint64_t>(p.R), static_cast<uint64_t>(p.C), b0, b1};
+    const uint64_t out_st[3] = {static_cast<uint64_t>(p.out_c_stride), bstride(p.batch_out_stride, 0),
+                                bstride(p.batch_out_stride, 1)};
+    const uint32_t box[4] = {TT, TT, 1, 1};
+    CUtensorMap tmIn, tmOut;
+    int* status = device_status_word(dev);
+    if (status != nullptr && make_tmap_4d_plain(&tmIn, X, in_dims, in_st, box) &&
+        make_tmap_4d_plain(&tmOut, Y, out_dims, out_st, box)) {
+      TmaTransposeParams tp;
+      tp.tiles_c = p.tiles_c;
+      tp.tiles_r = p.tiles_r;
+      tp.b0 = static_cast<long long>(b0);
+      tp.total = p.tiles_c * p.tiles_r * static_cast<long long>(b0 * b1);
+      tp.status = status;
+      static thread_local int configured_dev = -1;
+      if (configured_dev != dev) {
+        XTC_CUDA_CHECK(cudaFuncSetAttribute(transpose_tma_kernel,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, TT_SMEM));
+        configured_dev = dev;
+      }
+      const long long slots = 2ll * sm_count(dev);
+      const unsigned grid = static_cast<unsigned>(tp.total < slots ? tp.total : slots);
+      transpose_tma_kernel<<<grid, 256, TT_SMEM, s>>>(tmIn, tmOut, tp);
+      XTC_CUDA_CHECK(cudaGetLastError());
+      return XTC_CUDA_OK;
+    }
+  }
   const int64_t blocks = nbatch * p.tiles_r * p.tiles_c;
   XTC_REQUIRE(blocks < (1ll << 31), "transpose: too many tiles");
   transpose_tile_kernel<TILE><<<static_cast<unsigned>(blocks), 256, 0, s>>>(X, Y, p);

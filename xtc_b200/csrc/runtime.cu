@@ -70,6 +70,19 @@ encode_im2col_fn get_encode_im2col() {
   return fn;
 }
 
+bool make_tmap_4d_plain(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                        const uint64_t strides[3], const uint32_t box[4]) {
+  encode_tiled_fn enc = get_encode_tiled();
+  if (!enc) return false;
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t st[3] = {strides[0] * sizeof(float), strides[1] * sizeof(float), strides[2] * sizeof(float)};
+  cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), d, st, b, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
   encode_tiled_fn enc = get_encode_tiled();
