@@ -2,7 +2,7 @@
 
 Run where the reference source tree is available:
 
-    python tests/golden/make_golden.py /path/to/xtc            (default /root/reference)
+    python tests/golden/make_golden.py /path/to/xtc
 
 It imports the reference's ``xtc.graphs.xtc`` (pure Python + NumPy), builds each
 case's graph with the reference DSL, evaluates ``graph.forward`` on float32
@@ -146,7 +146,9 @@ def jsonable(obj):
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py /path/to/the/reference/source/tree")
+    root = sys.argv[1]
     O, T = import_reference(root)
     arrays = {}
     meta = {}
