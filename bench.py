@@ -317,6 +317,24 @@ def roofline_of(cfg, seconds: float, peaks: dict, workload: str, sustained: bool
                            + ("sustained" if sustained else "burst") + ")"}
 
 
+NVLINK_PEER_GBS = 770.0  # measured peer copy bandwidth per direction per GPU on this pool
+
+
+def fused_roofline(flops_per_rank: float, exchange_bytes_per_rank: float, seconds: float,
+                   peaks: dict) -> dict:
+    """Roofline of a kernel that computes and exchanges at once: the target time is the
+    slower of (FLOPs / measured TF32 GEMM peak) and (bytes each GPU must send over NVLink /
+    measured link bandwidth); `frac` = target / measured."""
+    compute = flops_per_rank / (peaks["bf16_tflops_sustained"] / 2.0 * 1e12)
+    link = exchange_bytes_per_rank / (NVLINK_PEER_GBS * 1e9)
+    target = max(compute, link)
+    return {"bound": "tensor" if compute >= link else "nvlink", "compute_ms": compute * 1e3,
+            "nvlink_ms": link * 1e3, "target_ms": target * 1e3, "measured_ms": seconds * 1e3,
+            "frac": target / seconds,
+            "peaks": f"TF32 {peaks['bf16_tflops_sustained'] / 2.0:.0f} TFLOP/s (measured bf16 / 2, "
+                     f"sustained), NVLink {NVLINK_PEER_GBS:.0f} GB/s per direction (measured peer copy)"}
+
+
 def run_single(args) -> None:
     import torch
 
@@ -456,6 +474,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         h2d = a_blk.numel() * 4
         d2h = rows * N * 4
         launches = 1 if (args.chunks <= 1 or args.exchange == "peer") else args.chunks
+        exchange_bytes = rows * N * 4 * (world - 1)  # the rank's block of C, to every other rank
     elif workload == "c3":
         sh = BatchSharded(32, world, rank)
         cfg = configs.build("c3", batch=sh.local_batch)
@@ -473,6 +492,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         h2d = x.numel() * 4 + w.numel() * 4
         d2h = ys[0].numel() * 4
         launches = 1
+        exchange_bytes = 0
         sharding = f"batch of 32 split over {world} ranks, no collective"
     else:
         raise SystemExit(f"workload {workload} does not shard; run it with --gpus 1")
@@ -537,6 +557,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
                              if workload == "c5" else "inputs rotate over 8 buffer sets"},
             "roofline": roofline_of(local_cfg, kernel_sec, peaks, workload, sustained=True),
             "compute_only_ms": kernel_sec * 1e3,
+            "fused_roofline": fused_roofline(total_flops / world, exchange_bytes, sec, peaks),
             "e2e": {"value": total_flops / e2e_sec / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
