@@ -107,6 +107,23 @@ def test_illegal_tiles_snap_or_raise():
         strict.schedule()
 
 
+def test_precision_modes_snap_the_benchmark_schedules():
+    """The 3xTF32 and fp32 modes cannot use every TF32 tile: CTA-pair rows, 256 columns and
+    (at 128 columns) 64 of K per stage are snapped to what the single-CTA 3xTF32 kernel runs."""
+    from xtc_b200 import capi, configs
+
+    for name in ("c2", "c4", "c5"):
+        cfg = configs.build(name, 8)
+        step = configs.compile_config(cfg, precision="3xtf32").plan.steps[-1]
+        assert step.config["precision"] == capi.PRECISION_3XTF32
+        assert step.config["tile_m"] == 128 and step.config["tile_n"] == 128
+        assert step.config["tile_k"] == 32
+        tf32 = configs.compile_config(cfg).plan.steps[-1].config
+        assert tf32["tile_m"] == 256 and tf32["tile_n"] == 256
+    c1 = configs.compile_config(configs.build("c1"), precision="3xtf32").plan.steps[-1].config
+    assert (c1["tile_n"], c1["tile_k"]) == (64, 64)  # two stages of it do fit
+
+
 def test_default_node_is_the_contraction():
     a = O.tensor((64, 64), "float32")
     b = O.tensor((64, 64), "float32")

@@ -247,6 +247,11 @@ def lower(graph: Any, node_configs: dict[str, dict] | None = None,
             if cfg["precision"] == capi.PRECISION_3XTF32 and cfg.get("tile_n", 0) > 128:
                 # the 3xTF32 epilogue sums a tile row in registers: at most 128 columns
                 cfg["tile_n"] = 128
+            if (cfg["precision"] == capi.PRECISION_3XTF32 and cfg.get("tile_k", 0) > 32
+                    and cfg.get("tile_n", 128) > 64):
+                # a 3xTF32 stage holds hi and lo parts of both operands: at 128 columns and 64
+                # of K per stage only one stage would fit
+                cfg["tile_k"] = 32
             if cfg["precision"] != capi.PRECISION_TF32 and cfg.get("tile_m", 0) > 128:
                 cfg["tile_m"] = 128  # the CTA-pair kernel is a TF32-only configuration
             out_uid, flags, thr = n.uid, 0, 0.0
