@@ -119,7 +119,10 @@ int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int flags,
  * xtc_cuda_ipc_import.  This fuses the all-gather of a row-sharded matmul into
  * the GEMM: rank r passes C = its own full-size buffer + r's row offset and the
  * peers' buffers + the same offset.  Stores to peers are plain 128-bit stores
- * over NVLink; the caller orders them against readers on the other GPUs (a
+ * over NVLink, issued (CTA-pair kernel, cfg.variant != 1) by four copier warps
+ * per CTA that read finished tiles back from the local C, so the tensor pipeline
+ * never waits for the link, or (cfg.variant = 1, and the one-CTA kernel) by the
+ * epilogue warps themselves; the caller orders them against readers on the other GPUs (a
  * stream-ordered collective or barrier after the call).  The reference has no
  * multi-GPU execution (its GPU runtime is pinned to device 0,
  * src/xtc/runtimes/accelerator/gpu/GPUDevice.py:95-97); this implements the

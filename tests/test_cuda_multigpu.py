@@ -86,16 +86,26 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         assert np.array_equal(c_full.cpu().numpy(), single)
 
         # ---- fused peer stores -----------------------------------------------------
-        op = PeerStoreMatmul(dev, a_blk.data_ptr(), b_dev.data_ptr(), m, n, k, world, rank,
-                             config=dict(module.plan.steps[-1].config))
-        for _ in range(2):
-            op.step(stream)
-        torch.cuda.synchronize()
-        dist.barrier()
-        got = op.result()
-        assert np.array_equal(got, single), "every rank must hold the full product"
-        op.close()
-        assert dev.status() == 0
+        pair_cfg = dict(module.plan.steps[-1].config)
+        variants = [
+            pair_cfg,                                     # CTA pairs, peers written by copier warps
+            dict(pair_cfg, variant=1),                    # CTA pairs, peers written by the epilogue
+            dict(tile_m=128, tile_n=128, tile_k=32, epilogue=2),  # one CTA per tile
+        ]
+        for cfg in variants:
+            op = PeerStoreMatmul(dev, a_blk.data_ptr(), b_dev.data_ptr(), m, n, k, world, rank,
+                                 config=cfg)
+            for _ in range(2):
+                op.step(stream)
+            torch.cuda.synchronize()
+            dist.barrier()
+            got = op.result()
+            if cfg.get("tile_m") == pair_cfg.get("tile_m"):
+                assert np.array_equal(got, single), "every rank must hold the full product"
+            else:
+                assert xo.rel_err(got, y64) <= TF32_TOL
+            op.close()
+            assert dev.status() == 0
         Path(out_dir, f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()

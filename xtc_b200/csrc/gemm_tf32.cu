@@ -86,6 +86,7 @@ struct LaunchArgs {
   int* status = nullptr;  // status word to use instead of the per-device one
   int n_extra = 0;        // further copies of C to write (broadcast epilogue)
   float* extra[7] = {};
+  bool copier_warps = true;  // CTA-pair kernel: peers written by copier warps, not by the epilogue
   int split_k = 1;        // CTAs per output tile along K (needs partials + counters)
   float* partials = nullptr;
   int* counters = nullptr;
@@ -264,7 +265,8 @@ int launch_pair(const LaunchArgs& a) {
                                              pair_tail_flag_bytes(sm_count(dev) / 2));
     if (p.tail_split < 2) p.tail_split = 0;
   }
-  kernel<<<2 * pairs, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmC, p, stages);
+  const int threads = (p.n_extra > 0 && a.copier_warps) ? PAIR_THREADS_BCAST : PAIR_THREADS;
+  kernel<<<2 * pairs, threads, smem, a.stream>>>(tmA, tmB, tmC, p, stages);
   XTC_CUDA_CHECK(cudaGetLastError());
   return XTC_CUDA_OK;
 }
@@ -459,6 +461,7 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
     XTC_REQUIRE(tma_ok && tma_addressable(C, ldc) && c.precision != XTC_CUDA_PRECISION_FP32_SIMT,
                 "gemm_bcast: operands and C must be 16-byte aligned with pitches that are multiples of 4");
     a.n_extra = n_extra;
+    a.copier_warps = c.variant != 1;
     for (int d = 0; d < n_extra; ++d) {
       XTC_REQUIRE(tma_addressable(extra[d], ldc), "gemm_bcast: destination %d is NULL or misaligned", d);
       a.extra[d] = extra[d];

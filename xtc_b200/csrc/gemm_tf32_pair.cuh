@@ -97,8 +97,13 @@ struct PairSmem {
   static constexpr int total(int stages) { return 1024 + BAR_BYTES + EPI_BYTES + stages * STAGE_BYTES; }
 };
 
+// Threads per CTA: the six warps of gemm_tf32.cuh, plus four copier warps when the
+// output is also broadcast to peer GPUs (launched only then).
+constexpr int PAIR_THREADS = NUM_THREADS;
+constexpr int PAIR_THREADS_BCAST = NUM_THREADS + 4 * 32;
+
 template <int BN, int KSPANS, int A_MODE, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS_BCAST, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const GemmParams p,
@@ -120,13 +125,20 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* acc_full = bars + 16;
   uint64_t* acc_empty = bars + 18;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  // tiles stored so far by the epilogue warp of each TMEM quadrant (read by its copier warp)
+  volatile uint32_t* stored = reinterpret_cast<volatile uint32_t*>(bars + 24);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
+  // Broadcast with copier warps: the epilogue only stores the tile locally and counts
+  // it; warps 6..9 copy finished tiles from the local C to the peers, so the tensor
+  // pipeline never waits for NVLink.
+  const bool copiers = p.n_extra > 0 && blockDim.x > PAIR_THREADS;
 
   if (threadIdx.x == 0) {
+    for (int q = 0; q < 4; ++q) stored[q] = 0;
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
     prefetch_tmap(&tmC);
@@ -279,7 +291,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
     }
-  } else {
+  } else if (warp < 2 + EPI_WARPS) {
     // ------------------------- epilogue (both CTAs) ---------------------------
     const int quad = warp & 3;
     const int epi_id = warp - 2;
@@ -367,7 +379,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M)
           tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
         if (lane == 0) tma_store_commit();
-        if (p.n_extra > 0) {
+        if (p.n_extra > 0 && !copiers) {
           const int chunk = lane & 7;
           const int gcol = col0 + chunk * 4;
 #pragma unroll
@@ -397,8 +409,76 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      if (copiers && w.piece == 0 && lane == 0) {
+        tma_store_wait_all<0>();  // this warp's 32 rows of the tile are in the local C
+        __threadfence();
+        stored[quad] = stored[quad] + 1;
+      }
     }
     tma_store_wait_all<0>();
+  } else if (copiers) {
+    // ------------------- copier warps (broadcast to the peers) -------------------
+    // Warp q copies the 32 rows that the epilogue warp of quadrant q stored, once that
+    // warp has counted the tile: read from the local C (L2), 128-bit stores over NVLink.
+    const int q = warp - (2 + EPI_WARPS);
+    constexpr int V = BN / 4;             // float4 per tile row
+    constexpr int JT = (V + 31) / 32;     // float4 per lane and row
+    uint32_t seen = 0;
+    PairWorkIter work(pair, num_pairs);
+    PairWork w;
+    while (!failed && work.next(p, w)) {
+      if (w.piece != 0) continue;  // another pair stores this tile
+      ++seen;
+      int ok = 1;
+      if (lane == 0) {
+        uint64_t t0 = 0;
+        for (uint32_t it = 0; stored[q] < seen; ++it) {
+          if ((it & 0xff) == 0xff) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) { ok = 0; break; }
+          }
+        }
+      }
+      if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
+        if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+        failed = true;
+        break;
+      }
+      __threadfence();
+      int tm, tn;
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int row0 = tm * (2 * BM) + static_cast<int>(rank) * BM + q * 32;
+      const int n0 = tn * BN;
+#pragma unroll 1
+      for (int r = 0; r < 32; r += 4) {
+        float4 v[4][JT];
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          const int row = row0 + r + rr;
+#pragma unroll
+          for (int j = 0; j < JT; ++j) {
+            const int idx = j * 32 + lane;
+            const int col = n0 + idx * 4;
+            if (idx < V && row < p.M && col < p.N)
+              v[rr][j] = __ldcg(reinterpret_cast<const float4*>(p.C + static_cast<int64_t>(row) * p.ldc + col));
+          }
+        }
+        for (int d = 0; d < p.n_extra; ++d) {
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int row = row0 + r + rr;
+#pragma unroll
+            for (int j = 0; j < JT; ++j) {
+              const int idx = j * 32 + lane;
+              const int col = n0 + idx * 4;
+              if (idx < V && row < p.M && col < p.N)
+                *reinterpret_cast<float4*>(p.extra_dst[d] + static_cast<int64_t>(row) * p.ldc + col) = v[rr][j];
+            }
+          }
+        }
+      }
+    }
   }
 
   if (failed) {
