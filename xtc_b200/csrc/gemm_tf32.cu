@@ -412,7 +412,11 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
   int dev = 0;
   int sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
-  if (c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m == 2 * BM && c.split_k != 1) {
+  // the library's own choice for large problems is the CTA-pair kernel (see gemm_impl)
+  const bool default_pair = c.tile_m == 0 && c.tile_n == 0 &&
+                            ((M + 255) / 256) * ((N + 255) / 256) >= sms / 2;
+  if (c.precision == XTC_CUDA_PRECISION_TF32 && (c.tile_m == 2 * BM || default_pair) &&
+      c.split_k != 1) {
     // the CTA-pair kernel's split tail (split_k = 1 turns it off)
     *bytes = pair_tail_bytes(sms / 2, c.tile_n ? c.tile_n : 256);
     return XTC_CUDA_OK;
