@@ -362,6 +362,55 @@ static int default_tile_n(int64_t M, int64_t N, int sms) {
   return tm * ((N + 127) / 128) >= sms / 2 ? 128 : 64;
 }
 
+// Kernel and tile for a TF32 problem whose caller named nothing (all of tile_m, tile_n,
+// tile_k, split_k zero): the candidate with the smallest modelled time.  The model is the
+// shared-memory / tensor-pipe cost of one K step of 8 per tile (measured: 128 clocks for a
+// 256x256 pair tile, 128 for 128x128, 192 for 128x256, 96 for 256x128 and 128x64), times
+// the K steps, times the rounds of tiles over the SMs (the split tail of the pair kernel
+// shortens a last round that is at most half full), plus a fixed 6 us; single-CTA
+// candidates with few tiles may split K, which costs 3 us + 1.15 us per split for the
+// reduction pass (measured on 512x256x1024).
+struct AutoChoice {
+  int tile_m, tile_n, tile_k, split_k;
+};
+static AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok) {
+  struct Cand { int tm, tn; double clk; };
+  // on a tie the earlier candidate wins: one CTA per tile before CTA pairs
+  static const Cand cands[] = {{128, 64, 96.0}, {128, 128, 128.0}, {128, 256, 192.0},
+                               {256, 128, 96.0}, {256, 256, 128.0}};
+  const double clk_per_us = 1900.0, fixed = 6.0 * clk_per_us;
+  const double ksteps = static_cast<double>((K + 7) / 8);
+  AutoChoice best{128, 128, 32, 1};
+  double best_t = 1e300;
+  for (const Cand& c : cands) {
+    if (c.tm == 256 && !pair_ok) continue;
+    const int64_t tiles = ((M + c.tm - 1) / c.tm) * ((N + c.tn - 1) / c.tn);
+    const int64_t slots = c.tm == 256 ? sms / 2 : sms;
+    const int64_t full = tiles / slots, rem = tiles % slots;
+    double rounds = static_cast<double>(full);
+    if (rem) rounds += (c.tm == 256 && full >= 1 && rem * 2 <= slots) ? 1.0 / static_cast<double>(slots / rem) : 1.0;
+    const int tile_k = c.tm == 256 ? (K >= 128 ? 64 : 32) : (c.tn == 64 && K >= 128 ? 64 : 32);
+    double t = rounds * ksteps * c.clk + fixed;
+    int split = 1;
+    if (c.tm == 128 && tiles * 2 <= slots) {
+      const int64_t kblocks = (K + tile_k - 1) / tile_k;
+      for (int s = 2; s <= 16 && tiles * s <= slots && s <= kblocks; s *= 2) {
+        const double ts = ksteps * c.clk / s + fixed + (3.0 + 1.15 * s) * clk_per_us;
+        if (ts < t) { t = ts; split = s; }
+      }
+    }
+    if (t < best_t) {
+      best_t = t;
+      best = {c.tm, c.tn, tile_k, split};
+    }
+  }
+  return best;
+}
+static bool is_full_auto(const xtc_cuda_gemm_config& c) {
+  return c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m == 0 && c.tile_n == 0 && c.tile_k == 0 &&
+         c.split_k == 0;
+}
+
 // What the single-CTA TF32 kernel will run with for a problem and a request:
 // tile shape and the split-K factor (1 = none).  Used by the launcher and by the
 // workspace query so that both agree.
@@ -412,11 +461,14 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
   int dev = 0;
   int sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
-  // the library's own choice for large problems is the CTA-pair kernel (see gemm_impl)
-  const bool default_pair = c.tile_m == 0 && c.tile_n == 0 &&
-                            ((M + 255) / 256) * ((N + 255) / 256) >= sms / 2;
-  if (c.precision == XTC_CUDA_PRECISION_TF32 && (c.tile_m == 2 * BM || default_pair) &&
-      c.split_k != 1) {
+  if (is_full_auto(c)) {  // size for what the library would pick itself (see gemm_impl)
+    const AutoChoice pick = choose_tf32_default(M, N, K, sms, true);
+    c.tile_m = pick.tile_m;
+    c.tile_n = pick.tile_n;
+    c.tile_k = pick.tile_k;
+    c.split_k = pick.tile_m == 2 * BM ? 0 : pick.split_k;
+  }
+  if (c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m == 2 * BM && c.split_k != 1) {
     // the CTA-pair kernel's split tail (split_k = 1 turns it off)
     *bytes = pair_tail_bytes(sms / 2, c.tile_n ? c.tile_n : 256);
     return XTC_CUDA_OK;
@@ -473,14 +525,14 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   }
   if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
 
-  // Library default for large problems: 256x256 tiles on CTA pairs (at least one
-  // tile per pair of SMs), which halves the shared-memory traffic for B per SM.
-  if (c.tile_m == 0 && c.tile_n == 0 && c.precision == XTC_CUDA_PRECISION_TF32 &&
-      tma_addressable(C, ldc) &&
-      ((M + 255) / 256) * ((N + 255) / 256) >= sm_count(dev) / 2) {
-    c.tile_m = 2 * BM;
-    c.tile_n = 256;
-    if (c.tile_k == 0) c.tile_k = 32;
+  // Nothing named by the caller: the library picks kernel, tile and split itself.
+  const bool full_auto = is_full_auto(c);
+  if (full_auto) {
+    const AutoChoice pick = choose_tf32_default(M, N, K, sm_count(dev), tma_addressable(C, ldc));
+    c.tile_m = pick.tile_m;
+    c.tile_n = pick.tile_n;
+    c.tile_k = pick.tile_k;
+    c.split_k = pick.tile_m == 2 * BM ? 0 : pick.split_k;
   }
   XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM || c.tile_m == 2 * BM,
               "gemm: tile_m=%d unsupported (128, or 256 for the CTA-pair kernel)", c.tile_m);
@@ -507,8 +559,9 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
       a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counters);
     } else {
       // automatic split-K is an optimisation: without a workspace run unsplit
-      XTC_REQUIRE(c.split_k == 0, "gemm: split_k=%d needs %zu bytes of zeroed workspace, got %zu",
-                  c.split_k, need, workspace ? workspace_bytes : static_cast<size_t>(0));
+      XTC_REQUIRE(full_auto || c.split_k == 0,
+                  "gemm: split_k=%d needs %zu bytes of zeroed workspace, got %zu", c.split_k, need,
+                  workspace ? workspace_bytes : static_cast<size_t>(0));
     }
   }
   // the broadcast epilogue reads the tile back from the store staging buffers
