@@ -67,6 +67,14 @@ int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t col
 
 int sm_count(int dev);
 
+// Kernel, tile and split-K factor the library picks for a TF32 contraction M x N x K
+// whose caller named none of them (cost model in gemm_tf32.cu).
+struct AutoChoice {
+  int tile_m, tile_n, tile_k, split_k;
+};
+AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
+                               bool split_ok);
+
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------
 // Device side

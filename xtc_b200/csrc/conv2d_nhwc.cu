@@ -66,8 +66,13 @@ int make_tmap_im2col(CUtensorMap* map, const ConvArgs& a, uint32_t pixels) {
                            static_cast<cuuint64_t>(a.H * a.W * a.C) * 4};
   // Base pixels (the input pixel under filter tap (0,0)) range over
   // [-pad, extent + pad - (filter - 1)) in each of W and H.
+  // With a stride that does not divide the padded extent the last few input
+  // columns / rows are never under tap (0,0): the box ends at the last base pixel,
+  // so that it holds exactly OW x OH base pixels whatever the stride.
+  const int rem_w = static_cast<int>((a.W + a.pl + a.pr - a.S) % a.sw);
+  const int rem_h = static_cast<int>((a.H + a.pt + a.pb - a.R) % a.sh);
   int lower[2] = {-a.pl, -a.pt};
-  int upper[2] = {a.pr - static_cast<int>(a.S - 1), a.pb - static_cast<int>(a.R - 1)};
+  int upper[2] = {a.pr - static_cast<int>(a.S - 1) - rem_w, a.pb - static_cast<int>(a.R - 1) - rem_h};
   cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(a.sw), static_cast<cuuint32_t>(a.sh), 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.X), dims, strides,
                    lower, upper, 32, pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -397,15 +402,18 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
   XTC_CUDA_CHECK(cudaGetDevice(&dev));
 
   auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  // A 1x1 filter with unit stride and no padding is a plain matrix product
+  // [B*H*W, C] x [C, F]: the GEMM entry point picks kernel and tile for it.
+  if (R == 1 && S == 1 && stride_h == 1 && stride_w == 1 && pad_top + pad_bottom + pad_left + pad_right == 0 &&
+      c.variant == 0 && c.precision != XTC_CUDA_PRECISION_3XTF32)
+    return xtc_cuda_gemm_f32(X, Wt, Y, M, F, C, C, F, F, flags & XTC_CUDA_FUSE_RELU, relu_threshold,
+                             &c, workspace, workspace_bytes, stream);
   // The tensor-core path needs TMA-addressable operands, a unit or small
-  // traversal stride, corner offsets within the im2col descriptor's range, and
-  // the tiles of the bounding box to line up with the output pixel grid.
-  const bool exact_h = (H + pad_top + pad_bottom - R) % stride_h == 0;
-  const bool exact_w = (W + pad_left + pad_right - S) % stride_w == 0;
+  // traversal stride, and corner offsets within the im2col descriptor's range.
   const bool tc_ok = c.precision == XTC_CUDA_PRECISION_TF32 && C % 4 == 0 && F % 4 == 0 &&
                      a16(X) && a16(Wt) && stride_h <= 8 && stride_w <= 8 && pad_top <= 127 &&
-                     pad_left <= 127 && S <= 128 && R <= 128 && exact_h && exact_w &&
-                     W <= 65535 && H <= 65535;
+                     pad_left <= 127 && pad_right <= 127 && pad_bottom <= 127 && S <= 120 &&
+                     R <= 120 && W <= 65535 && H <= 65535;
   if (!tc_ok) {
     XTC_REQUIRE(c.precision != XTC_CUDA_PRECISION_3XTF32,
                 "conv2d: the 3xTF32 mode is not available for convolutions");
@@ -444,10 +452,17 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
   }
   XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM || c.tile_m == 2 * BM,
               "conv2d: tile_m=%d unsupported (128, or 256 for the CTA-pair kernel)", c.tile_m);
-  int tile_n = c.tile_n;
+  int tile_m = c.tile_m, tile_n = c.tile_n;
+  if (tile_m == 0 && tile_n == 0 && c.tile_k == 0) {
+    // nothing named: the GEMM cost model on M = pixels, N = filters, K = taps x padded channels
+    const AutoChoice pick = choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sm_count(dev),
+                                                a16(Y), false);
+    tile_m = pick.tile_m;
+    tile_n = pick.tile_n;
+  }
   if (tile_n == 0) tile_n = F <= 64 ? 64 : (F <= 128 ? 128 : 256);
   int tile_k = c.tile_k ? c.tile_k : (C % 64 == 0 ? 64 : 32);
   const bool tma_store = c.epilogue == 2 && a16(Y);
-  if (c.tile_m == 2 * BM && a16(Y)) return dispatch_conv_pair(a, tile_n, tile_k);
+  if (tile_m == 2 * BM && a16(Y)) return dispatch_conv_pair(a, tile_n, tile_k);
   return tma_store ? dispatch_conv<true>(a, tile_n, tile_k) : dispatch_conv<false>(a, tile_n, tile_k);
 }

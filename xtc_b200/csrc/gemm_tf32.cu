@@ -370,10 +370,8 @@ static int default_tile_n(int64_t M, int64_t N, int sms) {
 // shortens a last round that is at most half full), plus a fixed 6 us; single-CTA
 // candidates with few tiles may split K, which costs 3 us + 1.15 us per split for the
 // reduction pass (measured on 512x256x1024).
-struct AutoChoice {
-  int tile_m, tile_n, tile_k, split_k;
-};
-static AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok) {
+AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
+                               bool split_ok) {
   struct Cand { int tm, tn; double clk; };
   // on a tie the earlier candidate wins: one CTA per tile before CTA pairs
   static const Cand cands[] = {{128, 64, 96.0}, {128, 128, 128.0}, {128, 256, 192.0},
@@ -392,7 +390,7 @@ static AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, 
     const int tile_k = c.tm == 256 ? (K >= 128 ? 64 : 32) : (c.tn == 64 && K >= 128 ? 64 : 32);
     double t = rounds * ksteps * c.clk + fixed;
     int split = 1;
-    if (c.tm == 128 && tiles * 2 <= slots) {
+    if (split_ok && c.tm == 128 && tiles * 2 <= slots) {
       const int64_t kblocks = (K + tile_k - 1) / tile_k;
       for (int s = 2; s <= 16 && tiles * s <= slots && s <= kblocks; s *= 2) {
         const double ts = ksteps * c.clk / s + fixed + (3.0 + 1.15 * s) * clk_per_us;
@@ -462,7 +460,7 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
   int sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
   if (is_full_auto(c)) {  // size for what the library would pick itself (see gemm_impl)
-    const AutoChoice pick = choose_tf32_default(M, N, K, sms, true);
+    const AutoChoice pick = choose_tf32_default(M, N, K, sms, true, true);
     c.tile_m = pick.tile_m;
     c.tile_n = pick.tile_n;
     c.tile_k = pick.tile_k;
@@ -528,7 +526,7 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   // Nothing named by the caller: the library picks kernel, tile and split itself.
   const bool full_auto = is_full_auto(c);
   if (full_auto) {
-    const AutoChoice pick = choose_tf32_default(M, N, K, sm_count(dev), tma_addressable(C, ldc));
+    const AutoChoice pick = choose_tf32_default(M, N, K, sm_count(dev), tma_addressable(C, ldc), true);
     c.tile_m = pick.tile_m;
     c.tile_n = pick.tile_n;
     c.tile_k = pick.tile_k;
