@@ -21,6 +21,9 @@ struct ConvArgs {
   float thr;
   int stages;
   cudaStream_t stream;
+  int split_k = 1;            // im2col kernel, one CTA per tile: CTAs sharing a tile along K
+  float* partials = nullptr;  // [split][tile][128][tile_n]
+  int* counters = nullptr;    // [tile], zeroed once
 };
 
 __global__ void __launch_bounds__(256)
@@ -120,8 +123,12 @@ int launch_conv_tc(const ConvArgs& a) {
   p.conv_cblocks = static_cast<int>((a.C + BK - 1) / BK);
   p.k_blocks = static_cast<int>(a.R * a.S) * p.conv_cblocks;
   p.chunk_kblocks = p.k_blocks;
-  p.split_k = 1;
-  p.split_kblocks = p.k_blocks;
+  const int want_split = (a.partials && a.counters) ? a.split_k : 1;
+  p.split_kblocks = (p.k_blocks + want_split - 1) / want_split;
+  p.split_k = (p.k_blocks + p.split_kblocks - 1) / p.split_kblocks;
+  p.partials = a.partials;
+  p.tile_counters = a.counters;
+  if (p.split_k > 1) p.chunk_kblocks = p.split_kblocks;
   p.relu = a.relu;
   p.relu_threshold = a.thr;
   p.status = device_status_word(dev);
@@ -144,7 +151,7 @@ int launch_conv_tc(const ConvArgs& a) {
     configured_dev = dev;
     configured_smem = smem;
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.split_k;
   const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
   kernel<<<grid, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmZ, tmZ, tmC, p, stages);
   XTC_CUDA_CHECK(cudaGetLastError());
@@ -359,11 +366,51 @@ int dispatch_conv(const ConvArgs& a, int tile_n, int tile_k) {
 
 using namespace xtc;
 
-extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t,
-                                               int64_t, int64_t, int, int, int, int, int, int,
-                                               const xtc_cuda_gemm_config*, size_t* bytes) {
+// Split-K workspace of the im2col kernel for a layer whose caller named nothing:
+// tile counters, then split x tiles partial tiles of 128 x tile_n floats.
+static size_t conv_split_bytes(int64_t M, int64_t F, const AutoChoice& pick) {
+  if (pick.tile_m != BM || pick.split_k <= 1) return 0;
+  const size_t tiles = static_cast<size_t>((M + BM - 1) / BM) * ((F + pick.tile_n - 1) / pick.tile_n);
+  return ((tiles * 4 + 255) & ~static_cast<size_t>(255)) +
+         static_cast<size_t>(pick.split_k) * tiles * BM * pick.tile_n * 4;
+}
+static bool conv_names_nothing(const xtc_cuda_gemm_config& c) {
+  return c.precision == XTC_CUDA_PRECISION_TF32 && c.variant == 0 && c.tile_m == 0 && c.tile_n == 0 &&
+         c.tile_k == 0 && c.split_k == 0;
+}
+
+extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, int64_t C, int64_t R,
+                                               int64_t S, int64_t F, int stride_h, int stride_w,
+                                               int pad_top, int pad_bottom, int pad_left,
+                                               int pad_right, const xtc_cuda_gemm_config* cfg,
+                                               size_t* bytes) {
   XTC_REQUIRE(bytes != nullptr, "conv2d_workspace_bytes: bytes is NULL");
   *bytes = 0;
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || R <= 0 || S <= 0 || F <= 0 || stride_h <= 0 ||
+      stride_w <= 0 || H + pad_top + pad_bottom < R || W + pad_left + pad_right < S)
+    return XTC_CUDA_OK;  // the convolution itself reports what is wrong
+  xtc_cuda_gemm_config c;
+  memset(&c, 0, sizeof(c));
+  if (cfg) c = *cfg;
+  const int64_t OH = (H + pad_top + pad_bottom - R) / stride_h + 1;
+  const int64_t OW = (W + pad_left + pad_right - S) / stride_w + 1;
+  const int64_t M = B * OH * OW;
+  if (R == 1 && S == 1 && stride_h == 1 && stride_w == 1 &&
+      pad_top + pad_bottom + pad_left + pad_right == 0 && c.variant == 0 &&
+      c.precision != XTC_CUDA_PRECISION_3XTF32)
+    return xtc_cuda_gemm_workspace_bytes(M, F, C, 0, &c, bytes);
+  if (!conv_names_nothing(c)) return XTC_CUDA_OK;
+  ConvArgs a;
+  memset(&a, 0, sizeof(a));
+  a.B = B; a.H = H; a.W = W; a.C = C; a.R = R; a.S = S; a.F = F;
+  a.sh = stride_h; a.sw = stride_w;
+  a.pt = pad_top; a.pb = pad_bottom; a.pl = pad_left; a.pr = pad_right;
+  a.OH = OH; a.OW = OW;
+  if (plan_halo(a, false, 32).ok || plan_halo(a, false, 16).ok || plan_halo(a, true, 32).ok)
+    return XTC_CUDA_OK;  // resident weights: no workspace
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
+  *bytes = conv_split_bytes(M, F, choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sms, true, true));
   return XTC_CUDA_OK;
 }
 
@@ -373,8 +420,6 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
                                         int pad_bottom, int pad_left, int pad_right, int flags,
                                         float relu_threshold, const xtc_cuda_gemm_config* cfg,
                                         void* workspace, size_t workspace_bytes, void* stream) {
-  (void)workspace;
-  (void)workspace_bytes;
   XTC_REQUIRE(X && Wt && Y, "conv2d: NULL operand");
   XTC_REQUIRE(B > 0 && H > 0 && W > 0 && C > 0 && R > 0 && S > 0 && F > 0, "conv2d: empty extent");
   XTC_REQUIRE(stride_h > 0 && stride_w > 0, "conv2d: stride must be positive");
@@ -455,8 +500,19 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
   int tile_m = c.tile_m, tile_n = c.tile_n;
   if (tile_m == 0 && tile_n == 0 && c.tile_k == 0) {
     // nothing named: the GEMM cost model on M = pixels, N = filters, K = taps x padded channels
-    const AutoChoice pick = choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sm_count(dev),
-                                                a16(Y), false);
+    // (split-K only with the zeroed workspace xtc_cuda_conv2d_workspace_bytes asks for)
+    const int64_t kpad = R * S * ((C + 31) / 32 * 32);
+    AutoChoice pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), true);
+    const size_t need = conv_split_bytes(M, F, pick);
+    if (need > 0 && c.split_k == 0 && workspace != nullptr && workspace_bytes >= need) {
+      const size_t tiles = static_cast<size_t>((M + BM - 1) / BM) * ((F + pick.tile_n - 1) / pick.tile_n);
+      a.split_k = pick.split_k;
+      a.counters = static_cast<int*>(workspace);
+      a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
+                                            ((tiles * 4 + 255) & ~static_cast<size_t>(255)));
+    } else if (need > 0) {
+      pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), false);
+    }
     tile_m = pick.tile_m;
     tile_n = pick.tile_n;
   }

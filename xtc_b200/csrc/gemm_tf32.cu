@@ -256,8 +256,13 @@ int launch_pair(const LaunchArgs& a) {
   // pairs idle are cut along K, one piece per pair (see gemm_tf32_pair.cuh).
   const int rem = tiles % pairs;
   const int split = rem > 0 ? pairs / rem : 0;
-  if (a.pair_tail != nullptr && tiles > pairs && split >= 2 && pairs <= sm_count(dev) / 2) {
-    p.tail_split = split < p.k_blocks ? split : p.k_blocks;
+  // (each piece keeps at least 1024 of K: parking and re-reading a 256 x BN accumulator
+  // costs more than a shorter piece saves)
+  const int max_split = static_cast<int>(a.K / 1024);
+  if (a.pair_tail != nullptr && tiles > pairs && split >= 2 && max_split >= 2 &&
+      pairs <= sm_count(dev) / 2) {
+    p.tail_split = split < max_split ? split : max_split;
+    if (p.tail_split > p.k_blocks) p.tail_split = p.k_blocks;
     p.tail_tiles = rem;
     p.tail_first = tiles - rem;
     p.sk_flags = static_cast<int*>(a.pair_tail);
@@ -393,7 +398,8 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
     if (split_ok && c.tm == 128 && tiles * 2 <= slots) {
       const int64_t kblocks = (K + tile_k - 1) / tile_k;
       for (int s = 2; s <= 16 && tiles * s <= slots && s <= kblocks; s *= 2) {
-        const double ts = ksteps * c.clk / s + fixed + (3.0 + 1.15 * s) * clk_per_us;
+        // the reducing CTA reads s partial tiles of 128 x tn floats (calibrated at tn = 64)
+        const double ts = ksteps * c.clk / s + fixed + (3.0 + 1.15 * s * (c.tn / 64.0)) * clk_per_us;
         if (ts < t) { t = ts; split = s; }
       }
     }
