@@ -390,7 +390,7 @@ def run_single(args) -> None:
         extra = {}
         for name in ("c1", "c3", "c4"):
             try:
-                r = bench_graph_device(torch, dev, name, max(args.steps, 20), args.warmup)
+                r = bench_graph_device(torch, dev, name, max(args.steps, 200), args.warmup)
                 c = r["cfg"]
                 extra[name] = {"tflops": c.flops / r["seconds"] / 1e12, "us": r["seconds"] * 1e6,
                                "frac_of_tf32_peak": c.flops / r["seconds"] / 1e12 / (peaks["bf16_tflops"] / 2)}

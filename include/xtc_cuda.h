@@ -258,7 +258,10 @@ int xtc_cuda_plan_destroy(xtc_cuda_plan* plan);
  * io pointers is seen and replayed with one graph launch afterwards (the
  * reference pays a host call per node instead, evaluate_perf.c:99-103). */
 int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* stream);
-/* enabled = 0 turns graph replay off (every run issues its launches directly). */
+/* enabled = 0 turns graph replay off (every run issues its launches directly);
+ * 1 turns it on.  Default: on for plans of two or more launches, off for a plan
+ * that is a single kernel (its runs then overlap back to back through programmatic
+ * dependent launch, which graph launches do not). */
 int xtc_cuda_plan_set_graph_mode(xtc_cuda_plan* plan, int enabled);
 /* io: HOST pointers.  Copies inputs to the device, runs, copies outputs back,
  * synchronises: the call the per-module payload makes, equivalent to calling

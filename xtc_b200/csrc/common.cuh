@@ -142,6 +142,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// ---- programmatic dependent launch ------------------------------------------
+// A kernel launched with launch_overlapped() may start while the previous kernel
+// of its stream is still finishing; its CTAs run their prologue (barriers, TMEM,
+// descriptor prefetch) and then wait here until that kernel's memory is complete.
+// Without the launch attribute both calls do nothing.
+__device__ __forceinline__ void grid_dependency_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- TMA -----------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -373,6 +383,26 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, bool a_mn, 
 }
 
 }  // namespace dev
+
+// Launch with programmatic stream serialisation: the kernel may begin before its
+// predecessor in the stream has drained (see dev::grid_dependency_sync).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  lc.gridDim = dim3(grid, 1, 1);
+  lc.blockDim = dim3(block, 1, 1);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = &attr;
+  lc.numAttrs = 1;
+  return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
+}
 #endif  // __CUDACC__
 
 }  // namespace xtc

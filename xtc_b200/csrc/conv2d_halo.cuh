@@ -116,6 +116,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_sync();
   const uint32_t tmem_base = *tmem_slot;
   const int plane = p.Hp * p.Wp;
   bool failed = false;

@@ -70,6 +70,7 @@ conv2d_halo_pair_kernel(const __grid_constant__ CUtensorMap tmX,
   __syncthreads();
   cluster_sync_all();
   tc_fence_after();
+  grid_dependency_sync();
   const uint32_t tmem_base = *tmem_slot;
   const int plane = p.Hp * p.Wp;
   const int pair = blockIdx.x >> 1;

@@ -153,8 +153,8 @@ int launch_conv_tc(const ConvArgs& a) {
   }
   const int tiles = p.tiles_m * p.tiles_n * p.split_k;
   const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
-  kernel<<<grid, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmZ, tmZ, tmC, p, stages);
-  XTC_CUDA_CHECK(cudaGetLastError());
+  XTC_CUDA_CHECK(launch_overlapped(kernel, grid, NUM_THREADS, smem, a.stream, tmA, tmB, tmZ, tmZ, tmC,
+                                   p, stages));
   return XTC_CUDA_OK;
 }
 
@@ -260,8 +260,7 @@ int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
   }
   const int slots = PAIR ? sm_count(dev) / 2 : sm_count(dev);
   const int grid = (p.tiles < slots ? p.tiles : slots) * (PAIR ? 2 : 1);
-  kernel<<<grid, HALO_THREADS, h.smem, a.stream>>>(tmX, tmW, p);
-  XTC_CUDA_CHECK(cudaGetLastError());
+  XTC_CUDA_CHECK(launch_overlapped(kernel, grid, HALO_THREADS, h.smem, a.stream, tmX, tmW, p));
   return XTC_CUDA_OK;
 }
 
@@ -333,8 +332,8 @@ int launch_conv_pair(const ConvArgs& a) {
   const int tiles = p.tiles_m * p.tiles_n;
   const int max_pairs = sm_count(dev) / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kernel<<<2 * pairs, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmC, p, stages);
-  XTC_CUDA_CHECK(cudaGetLastError());
+  XTC_CUDA_CHECK(launch_overlapped(kernel, 2 * pairs, NUM_THREADS, smem, a.stream, tmA, tmB, tmC, p,
+                                   stages));
   return XTC_CUDA_OK;
 }
 

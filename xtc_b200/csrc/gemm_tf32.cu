@@ -177,8 +177,8 @@ int launch_tc(const LaunchArgs& a) {
   }
   const int tiles = p.tiles_m * p.tiles_n * p.split_k;
   const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
-  kernel<<<grid, NUM_THREADS, smem, a.stream>>>(tmA, tmB, tmAlo, tmBlo, tmC, p, stages);
-  XTC_CUDA_CHECK(cudaGetLastError());
+  XTC_CUDA_CHECK(launch_overlapped(kernel, grid, NUM_THREADS, smem, a.stream, tmA, tmB, tmAlo, tmBlo,
+                                   tmC, p, stages));
   return XTC_CUDA_OK;
 }
 
@@ -271,8 +271,7 @@ int launch_pair(const LaunchArgs& a) {
     if (p.tail_split < 2) p.tail_split = 0;
   }
   const int threads = (p.n_extra > 0 && a.copier_warps) ? PAIR_THREADS_BCAST : PAIR_THREADS;
-  kernel<<<2 * pairs, threads, smem, a.stream>>>(tmA, tmB, tmC, p, stages);
-  XTC_CUDA_CHECK(cudaGetLastError());
+  XTC_CUDA_CHECK(launch_overlapped(kernel, 2 * pairs, threads, smem, a.stream, tmA, tmB, tmC, p, stages));
   return XTC_CUDA_OK;
 }
 

@@ -155,6 +155,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_sync();
   const uint32_t tmem_base = *tmem_slot;
 
   // Work items: (tile, K split).  Without split-K there is one item per tile.

@@ -160,6 +160,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   __syncthreads();
   cluster_sync_all();  // the other CTA's barriers exist before anything signals them
   tc_fence_after();
+  grid_dependency_sync();
   const uint32_t tmem_base = *tmem_slot;
 
   const int pair = blockIdx.x >> 1;
