@@ -192,6 +192,7 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap tmIn,
     fence_barrier_init();
   }
   __syncthreads();
+  grid_dependency_sync();
   const long long first = blockIdx.x, step = gridDim.x;
   if (tid == 0)
     for (int s = 0; s < TT_STAGES; ++s)
@@ -485,8 +486,7 @@ extern "C" int xtc_cuda_transpose_f32(const float* X, float* Y, int ndim, const 
       }
       const long long slots = 2ll * sm_count(dev);
       const unsigned grid = static_cast<unsigned>(tp.total < slots ? tp.total : slots);
-      transpose_tma_kernel<<<grid, 256, TT_SMEM, s>>>(tmIn, tmOut, tp);
-      XTC_CUDA_CHECK(cudaGetLastError());
+      XTC_CUDA_CHECK(launch_overlapped(transpose_tma_kernel, grid, 256, TT_SMEM, s, tmIn, tmOut, tp));
       return XTC_CUDA_OK;
     }
   }
