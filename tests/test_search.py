@@ -126,3 +126,124 @@ def test_exhaustive_search_on_gpu(tmp_path):
     assert len(rows) == len(results)
     assert all(0 < float(r["peak"]) <= 1.5 for r in rows)
     assert exp.best() is not None
+
+
+@pytest.mark.gpu
+def test_iterative_search_and_database_on_gpu(tmp_path):
+    from xtc_b200.search import read_db
+
+    cfg = ExplorationConfig(operator="matmul", dims=[1024, 1024, 1024], search="iterative", trials=8,
+                            batch=4, optimizer="random-forest-default", output=str(tmp_path / "it.csv"),
+                            db_file=str(tmp_path / "db.jsonl"), repeat=2, number=3, min_repeat_ms=1,
+                            validate=True, explore_dir=str(tmp_path / "x"))
+    exp = Exploration(cfg)
+    results = exp.run()
+    assert len(results) == 8 and all(code == 0 for _, code, _, _ in results)
+    recs = read_db(cfg.db_file, graph=exp.graph, backend="cuda")
+    assert len(recs) == 8 and all(r["results"][0] == 0 and r["results"][1][0] > 0 for r in recs)
+    assert "B200" in recs[0]["compiler"][2]
+    # the table of this run drives a data search
+    replay = Exploration(ExplorationConfig(**{**cfg.__dict__, "search": "data", "data": cfg.output,
+                                              "output": str(tmp_path / "replay.csv"), "db_file": None}))
+    assert [r[0] for r in replay.run()] == [r[0] for r in results]
+
+
+def _fake_timer(monkeypatch, calls=None):
+    """Replaces compile and execute by a cost model: time falls with the tile area."""
+    def fake_eval(self, module, sample):
+        if calls is not None:
+            calls.append(list(sample))
+        if sample[3] == 6:  # pretend the deepest pipeline fails to run
+            return (list(sample), 7, float("inf"), "cuda")
+        return (list(sample), 0, 1.0 / (sample[0] * sample[1] * (1 + sample[4])), "cuda")
+
+    monkeypatch.setattr(Exploration, "compile_one", lambda self, ident, sample, d: None)
+    monkeypatch.setattr(Exploration, "evaluate_one", fake_eval)
+
+
+def test_callbacks_write_table_database_and_manifest(tmp_path, monkeypatch):
+    import csv
+    import json
+
+    from xtc_b200.search import DBCallback, read_db
+    from xtc_b200.search.explore import matmul_graph
+
+    _fake_timer(monkeypatch)
+    out = tmp_path / "t.csv"
+    cfg = ExplorationConfig(operator="matmul", dims=[512, 512, 512], search="exhaustive", trials=0,
+                            output=str(out), peak_flops=1e15)
+    exp = Exploration(cfg)
+    results = exp.run()
+    space = list(exp.strategy.exhaustive())
+    assert [r[0] for r in results] == space
+    failed = [r for r in results if r[1] != 0]
+    assert failed and all(r[0][3] == 6 for r in failed)
+    rows = list(csv.DictReader(open(out)))
+    assert len(rows) == len(space) - len(failed)  # failures stay out of the table
+    assert list(rows[0])[-4:] == ["X", "time", "peak", "backend"]
+    assert float(rows[0]["peak"]) == pytest.approx(exp.peak_time() / float(rows[0]["time"]))
+    meta = json.load(open(f"{out}.meta.json"))
+    assert meta["sampleNames"] == exp.strategy.sample_names and meta["args"]["search"] == "exhaustive"
+
+    # append adds rows without a second header; a data search replays the table's X column
+    cfg_data = ExplorationConfig(**{**cfg.__dict__, "search": "data", "data": str(out),
+                                    "output": str(tmp_path / "replay.csv")})
+    replay = Exploration(cfg_data)
+    assert replay.samples() == [r[0] for r in results if r[1] == 0]
+    cfg_app = ExplorationConfig(**{**cfg.__dict__, "append": True, "search": "random", "trials": 2})
+    added = sum(r[1] == 0 for r in Exploration(cfg_app).run())
+    lines = open(out).read().strip().splitlines()
+    assert len(lines) == 1 + len(rows) + added and sum(l.startswith("tile_m") for l in lines) == 1
+
+    # the results database: one JSON line per sample, failures with time 0, matched by graph digest
+    graph = matmul_graph(512, 512, 512)
+    db = DBCallback(str(tmp_path / "db.jsonl"), "NVIDIA B200", 1, "cuda_gemm")
+    db.set_graph(graph)
+    for r in results[:5] + failed[:1]:
+        db(r)
+    recs = read_db(str(tmp_path / "db.jsonl"), graph=matmul_graph(512, 512, 512, name="other_name"),
+                   target="NVIDIA B200", backend="cuda")
+    assert len(recs) == 6 and recs[-1]["results"] == [7, [0.0]]
+    assert recs[0]["compiler"][:1] == ["xtc"] and recs[0]["compiler"][2:] == ["NVIDIA B200", 1, "cuda"]
+    assert recs[0]["schedule"] == results[0][0] and recs[0]["operator"][0] == "xtc.graph"
+    assert read_db(str(tmp_path / "db.jsonl"), graph=matmul_graph(512, 512, 256)) == []
+
+
+@pytest.mark.parametrize("optimizer", ["random", "random-forest-default", "random-forest-aggressive"])
+def test_iterative_search_with_optimizers(tmp_path, monkeypatch, optimizer):
+    from xtc_b200.search import Optimizers
+
+    calls: list[list[int]] = []
+    _fake_timer(monkeypatch, calls)
+    cfg = ExplorationConfig(operator="matmul", dims=[1024, 1024, 1024], search="iterative", trials=24,
+                            batch=6, optimizer=optimizer, output=str(tmp_path / "it.csv"),
+                            peak_flops=1e15, seed=3)
+    exp = Exploration(cfg)
+    results = exp.run()
+    assert len(results) == 24 and len(calls) == 24
+    assert len({tuple(c) for c in calls}) == 24  # nothing is measured twice while unseen samples remain
+    assert all(exp.strategy.is_legal(c) for c in calls)
+    best = exp.best()
+    assert best is not None
+    if optimizer != "random":  # the surrogate finds the widest tile with the TMA epilogue
+        assert best[0][0] * best[0][1] == 256 * 256 and best[0][4] == 1
+    with pytest.raises(ValueError):
+        Optimizers.create("no-such-optimizer", exp.strategy.sample, 4, 0)
+
+
+def test_optimizer_refit_schedule_and_config_file(tmp_path):
+    from xtc_b200.search import Optimizers
+    from xtc_b200.search.explore import matmul_graph
+
+    strategy = Strategies.create("cuda_gemm", matmul_graph(512, 512, 512))
+    cfgfile = tmp_path / "opt.yaml"
+    cfgfile.write_text("n_estimators: 10\nupdate_first: 8\nupdate_period: 4\nbeta: 1.0\n")
+    opt = Optimizers.create("random-forest-explore", strategy.sample, 4, 0, str(cfgfile))
+    assert opt.forest.n_estimators == 10 and opt.beta0 == 1.0 and opt.alpha == 0.6
+    for step in range(4):
+        batch = opt.suggest()
+        assert len(batch) == 4
+        opt.observe(batch, [s[0] * s[1] / 65536 for s in batch])
+        assert opt.fitted_on == (0 if step == 0 else 8 + (4 * (step + 1) - 8) // 4 * 4)
+    assert opt.beta() == pytest.approx(max(0.05, 1.0 / 16 ** 0.6))
+    assert opt.best_y == max(opt.y)
