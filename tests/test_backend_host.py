@@ -122,6 +122,9 @@ def test_precision_modes_snap_the_benchmark_schedules():
         assert tf32["tile_m"] == 256 and tf32["tile_n"] == 256
     c1 = configs.compile_config(configs.build("c1"), precision="3xtf32").plan.steps[-1].config
     assert (c1["tile_n"], c1["tile_k"]) == (64, 64)  # two stages of it do fit
+    # convolutions have no operand-split mode: a 3xTF32 graph runs them in fp32 FMA
+    c3 = configs.compile_config(configs.build("c3", 8), precision="3xtf32").plan.steps[-1]
+    assert c3.kind == "conv2d" and c3.config["precision"] == capi.PRECISION_FP32_SIMT
 
 
 def test_default_node_is_the_contraction():

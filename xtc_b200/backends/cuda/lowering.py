@@ -244,6 +244,10 @@ def lower(graph: Any, node_configs: dict[str, dict] | None = None,
         fused: list[str] = []
         if op.name in ("matmul", "conv2d"):
             cfg.setdefault("precision", PRECISIONS[precision])
+            if op.name == "conv2d" and cfg["precision"] == capi.PRECISION_3XTF32:
+                # the convolution kernels have no operand-split mode: a graph compiled for
+                # 3xTF32 runs its convolutions in fp32 FMA, which is at least as accurate
+                cfg["precision"] = capi.PRECISION_FP32_SIMT
             if cfg["precision"] == capi.PRECISION_3XTF32 and cfg.get("tile_n", 0) > 128:
                 # the 3xTF32 epilogue sums a tile row in registers: at most 128 columns
                 cfg["tile_n"] = 128
