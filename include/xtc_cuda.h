@@ -90,9 +90,14 @@ typedef struct xtc_cuda_gemm_config {
   int32_t epilogue;  /* 0 = default; 1 = direct global stores; 2 = TMA stores     */
   int32_t variant;   /* conv2d: 0 = auto; 1 = im2col fetch per filter tap;
                         2 = resident weights + halo tiles (stride 1 only)          */
-  int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off (the
-                        default: it did not pay on the shapes measured).  Needs the
-                        workspace of xtc_cuda_gemm_workspace_bytes, zeroed before its
+  int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off unless
+                        the whole config is zero, when the library decides.  2, 4 or 8
+                        pieces of a tile at most 128 columns wide, N a multiple of 4, C
+                        16-byte aligned, all clusters resident at once: the pieces are
+                        the CTAs of one thread-block cluster and are summed through
+                        distributed shared memory, no workspace (variant = 1 opts out).
+                        Any other split needs the workspace of
+                        xtc_cuda_gemm_workspace_bytes, zeroed before its
                         first use (the kernel leaves its counters zero again).
                         With tile_m = 256: 0 = when the last round of tiles would leave
                         CTA pairs idle, share the K blocks of the last tiles out evenly

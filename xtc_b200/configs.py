@@ -76,8 +76,13 @@ def inputs(name: str, scale: int = 1, batch: int | None = None) -> list[np.ndarr
 
 
 def _gemm_schedule(tile_n: int, tile_k: int, stages: int = 0, tma_store: bool = True,
-                   tile_m: int = 128, fuse_a: bool = False):
+                   tile_m: int = 128, fuse_a: bool = False, split: tuple[int, int] | None = None):
     def apply(sch: Any) -> None:
+        if split is not None:
+            # (pieces, K): the reduction cut into equal segments that run concurrently, one
+            # CTA of a thread-block cluster each; on c1, 7.6 us against 10.0 us unsplit
+            pieces, k_extent = split
+            sch.split("k", {f"k_s{i}": i * (k_extent // pieces) for i in range(pieces)})
         if fuse_a:
             # read the transposed operand in place (column-major A tiles) instead of
             # materialising the transpose: on c4, 193 us against 293 us
@@ -120,7 +125,8 @@ def build(name: str, scale: int = 1, batch: int | None = None, rows: int | None 
         with O.graph(name="c1_matmul") as gb:
             O.matmul(a, b, name="C")
         return Config(name, gb.graph, "C", [(m, k), (k, n)], (m, n), 2 * m * n * k,
-                      4 * (m * k + k * n + m * n), "tensor", "", _gemm_schedule(64, 64))
+                      4 * (m * k + k * n + m * n), "tensor", "",
+                      _gemm_schedule(64, 64, split=(4, k) if k % 256 == 0 else None))
     if name == "c2":
         n = _scaled(4096, s)
         a = O.tensor((n, n), "float32", name="A")

@@ -72,8 +72,11 @@ int sm_count(int dev);
 struct AutoChoice {
   int tile_m, tile_n, tile_k, split_k;
 };
+// `cluster_cap[s]` (s = 2, 4, 8; indexable to 8) = clusters of s single-CTA GEMM blocks the
+// device runs at once (cluster_capacity), NULL = do not consider a split inside a cluster.
 AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
-                               bool split_ok);
+                               bool split_ok, const int* cluster_cap = nullptr);
+int cluster_capacity(int dev, int size);
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------
@@ -276,6 +279,14 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
+__device__ __forceinline__ float4 ld_shared_cluster_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
                    : "memory");
@@ -387,21 +398,32 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, bool a_mn, 
 // Launch with programmatic stream serialisation: the kernel may begin before its
 // predecessor in the stream has drained (see dev::grid_dependency_sync).
 template <typename... KArgs, typename... Args>
-cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
-                              cudaStream_t stream, Args&&... args) {
+cudaError_t launch_overlapped_clustered(void (*kernel)(KArgs...), unsigned grid, unsigned cluster,
+                                        unsigned block, size_t smem, cudaStream_t stream,
+                                        Args&&... args) {
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
   lc.gridDim = dim3(grid, 1, 1);
   lc.blockDim = dim3(block, 1, 1);
   lc.dynamicSmemBytes = smem;
   lc.stream = stream;
-  cudaLaunchAttribute attr;
-  memset(&attr, 0, sizeof(attr));
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  lc.attrs = &attr;
-  lc.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  memset(attr, 0, sizeof(attr));
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;  // `cluster` consecutive CTAs form a cluster
+  attr[1].val.clusterDim.x = cluster;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = cluster > 1 ? 2 : 1;
   return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  return launch_overlapped_clustered(kernel, grid, 1u, block, smem, stream,
+                                     static_cast<Args&&>(args)...);
 }
 #endif  // __CUDACC__
 

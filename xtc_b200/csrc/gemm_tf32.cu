@@ -90,6 +90,7 @@ struct LaunchArgs {
   int split_k = 1;        // CTAs per output tile along K (needs partials + counters)
   float* partials = nullptr;
   int* counters = nullptr;
+  bool cluster_k = false; // split-K reduced inside a thread-block cluster (no workspace)
   // CTA-pair kernel: zeroed workspace for the split tail (pair_tail_bytes), or NULL
   void* pair_tail = nullptr;
 };
@@ -159,12 +160,17 @@ int launch_tc(const LaunchArgs& a) {
   XTC_REQUIRE(p.status != nullptr, "gemm: device status word unavailable");
   p.n_extra = TMA_STORE ? a.n_extra : 0;
   for (int d = 0; d < p.n_extra; ++d) p.extra_dst[d] = a.extra[d];
-  const int want_split = (SPLIT3 || a.partials == nullptr || a.counters == nullptr) ? 1 : a.split_k;
+  const bool in_cluster = !SPLIT3 && a.cluster_k && BN <= 128;
+  const int want_split =
+      SPLIT3 ? 1 : (in_cluster || (a.partials != nullptr && a.counters != nullptr)) ? a.split_k : 1;
   p.split_kblocks = (p.k_blocks + want_split - 1) / want_split;
   p.split_k = (p.k_blocks + p.split_kblocks - 1) / p.split_kblocks;
   p.partials = a.partials;
   p.tile_counters = a.counters;
   if (p.split_k > 1) p.chunk_kblocks = p.split_kblocks;
+  p.cluster_k = in_cluster && (p.split_k == 2 || p.split_k == 4 || p.split_k == 8);
+  XTC_REQUIRE(p.cluster_k || !in_cluster || p.split_k == 1,
+              "gemm: the cluster split needs 2, 4 or 8 pieces, got %d", p.split_k);
 
   auto kernel = gemm_tf32_kernel<BN, KSPANS, A_MODE, B_MN, SPLIT3, TMA_STORE>;
   const int smem = L::total(stages, TMA_STORE);
@@ -176,9 +182,10 @@ int launch_tc(const LaunchArgs& a) {
     configured_smem = smem;
   }
   const int tiles = p.tiles_m * p.tiles_n * p.split_k;
-  const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
-  XTC_CUDA_CHECK(launch_overlapped(kernel, grid, NUM_THREADS, smem, a.stream, tmA, tmB, tmAlo, tmBlo,
-                                   tmC, p, stages));
+  // cluster split: one work item per CTA, the pieces of a tile in consecutive CTAs
+  const int grid = p.cluster_k ? tiles : (tiles < sm_count(dev) ? tiles : sm_count(dev));
+  XTC_CUDA_CHECK(launch_overlapped_clustered(kernel, grid, p.cluster_k ? p.split_k : 1, NUM_THREADS,
+                                             smem, a.stream, tmA, tmB, tmAlo, tmBlo, tmC, p, stages));
   return XTC_CUDA_OK;
 }
 
@@ -366,16 +373,59 @@ static int default_tile_n(int64_t M, int64_t N, int sms) {
   return tm * ((N + 127) / 128) >= sms / 2 ? 128 : 64;
 }
 
+// How many clusters of `size` CTAs of the single-CTA GEMM kernel the device runs at once
+// (the kernel takes a whole SM, and a cluster must sit inside one GPC).  Asked of the
+// runtime once per device and size; a split whose clusters do not all fit runs in waves
+// and loses what it was meant to gain.
+int cluster_capacity(int dev, int size) {
+  if (size <= 1) return sm_count(dev);
+  static std::mutex mu;
+  static int cache[16][9];  // 0 = not asked yet
+  if (dev < 0 || dev >= 16 || size > 8) return sm_count(dev) / (size * 2);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev][size] == 0) {
+    using L = SmemLayout<64, 2, false>;
+    auto kernel = gemm_tf32_kernel<64, 2, A_KMAJOR, true, false, false>;
+    const int smem = L::total(L::max_stages(false), false);
+    int n = 0;
+    cudaLaunchConfig_t lc;
+    memset(&lc, 0, sizeof(lc));
+    lc.gridDim = dim3(static_cast<unsigned>(size) * 64u, 1, 1);
+    lc.blockDim = dim3(NUM_THREADS, 1, 1);
+    lc.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    memset(&attr, 0, sizeof(attr));
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = static_cast<unsigned>(size);
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    lc.attrs = &attr;
+    lc.numAttrs = 1;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, kernel, &lc) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count(dev) / (size * 2);  // a guess on the safe side
+    }
+    cache[dev][size] = n;
+  }
+  return cache[dev][size];
+}
+
 // Kernel and tile for a TF32 problem whose caller named nothing (all of tile_m, tile_n,
 // tile_k, split_k zero): the candidate with the smallest modelled time.  The model is the
 // shared-memory / tensor-pipe cost of one K step of 8 per tile (measured: 128 clocks for a
 // 256x256 pair tile, 128 for 128x128, 192 for 128x256, 96 for 256x128 and 128x64), times
 // the K steps, times the rounds of tiles over the SMs (the split tail of the pair kernel
 // shortens a last round that is at most half full), plus a fixed 6 us; single-CTA
-// candidates with few tiles may split K, which costs 3 us + 1.15 us per split for the
-// reduction pass (measured on 512x256x1024).
+// candidates with few tiles may split K.  Tiles up to 128 columns wide split into 2, 4 or
+// 8 pieces inside a thread-block cluster while all clusters fit on the device at once
+// (`cluster_cap[s]`, NULL = no cluster split): 1 us + 1 us per 64 tile columns + 0.1 us per
+// piece for the reduction through distributed shared memory (512x256x1024: 10.0 us
+// unsplit, 7.6 us in 4 pieces; 256x256x4096: 29.1 us unsplit, 9.6 us in 8 pieces).
+// Other splits go through a workspace (`split_ok`), which costs 3 us + 1.15 us per piece
+// for the reduction pass.
 AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
-                               bool split_ok) {
+                               bool split_ok, const int* cluster_cap) {
   struct Cand { int tm, tn; double clk; };
   // on a tie the earlier candidate wins: one CTA per tile before CTA pairs
   static const Cand cands[] = {{128, 64, 96.0}, {128, 128, 128.0}, {128, 256, 192.0},
@@ -394,8 +444,14 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
     const int tile_k = c.tm == 256 ? (K >= 128 ? 64 : 32) : (c.tn == 64 && K >= 128 ? 64 : 32);
     double t = rounds * ksteps * c.clk + fixed;
     int split = 1;
-    if (split_ok && c.tm == 128 && tiles * 2 <= slots) {
-      const int64_t kblocks = (K + tile_k - 1) / tile_k;
+    const int64_t kblocks = (K + tile_k - 1) / tile_k;
+    if (cluster_cap != nullptr && c.tm == 128 && c.tn <= 128 && N % 4 == 0) {
+      for (int s = 2; s <= 8 && tiles <= cluster_cap[s] && tiles * s <= slots && s <= kblocks; s *= 2) {
+        const double ts = ksteps * c.clk / s + fixed + (1.0 + c.tn / 64.0 + 0.1 * s) * clk_per_us;
+        if (ts < t) { t = ts; split = s; }
+      }
+    }
+    if (split == 1 && split_ok && c.tm == 128 && tiles * 2 <= slots) {
       for (int s = 2; s <= 16 && tiles * s <= slots && s <= kblocks; s *= 2) {
         // the reducing CTA reads s partial tiles of 128 x tn floats (calibrated at tn = 64)
         const double ts = ksteps * c.clk / s + fixed + (3.0 + 1.15 * s * (c.tn / 64.0)) * clk_per_us;
@@ -465,7 +521,9 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
   int sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
   if (is_full_auto(c)) {  // size for what the library would pick itself (see gemm_impl)
-    const AutoChoice pick = choose_tf32_default(M, N, K, sms, true, true);
+    int caps[9] = {};
+    for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+    const AutoChoice pick = choose_tf32_default(M, N, K, sms, true, true, caps);
     c.tile_m = pick.tile_m;
     c.tile_n = pick.tile_n;
     c.tile_k = pick.tile_k;
@@ -478,7 +536,11 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
   }
   if (c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m != 2 * BM) {
     const TfShape s = resolve_tf32_shape(M, N, K, c, sms);
-    if (s.split_k > 1)  // tile counters, then the partial tiles [split][tile][128][tile_n]
+    // a split the launcher reduces inside a cluster needs nothing (assuming, as the launcher
+    // checks, a 16-byte aligned C with a pitch that is a multiple of 4)
+    const bool in_cluster = c.variant != 1 && (s.split_k == 2 || s.split_k == 4 || s.split_k == 8) &&
+                            s.tile_n <= 128 && N % 4 == 0 && s.tiles <= cluster_capacity(dev, s.split_k);
+    if (s.split_k > 1 && !in_cluster)  // tile counters, then the partial tiles [split][tile][128][tile_n]
       *bytes = align256(static_cast<size_t>(s.tiles) * 4) +
                static_cast<size_t>(s.split_k) * s.tiles * BM * s.tile_n * 4;
   }
@@ -531,7 +593,10 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   // Nothing named by the caller: the library picks kernel, tile and split itself.
   const bool full_auto = is_full_auto(c);
   if (full_auto) {
-    const AutoChoice pick = choose_tf32_default(M, N, K, sm_count(dev), tma_addressable(C, ldc), true);
+    int caps[9] = {};
+    for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+    const AutoChoice pick = choose_tf32_default(M, N, K, sm_count(dev), tma_addressable(C, ldc), true,
+                                                tma_addressable(C, ldc) && n_extra == 0 ? caps : nullptr);
     c.tile_m = pick.tile_m;
     c.tile_n = pick.tile_n;
     c.tile_k = pick.tile_k;
@@ -553,7 +618,17 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   int tile_n = c.tile_n ? c.tile_n : shp.tile_n;
   if (c.precision == XTC_CUDA_PRECISION_3XTF32 && c.tile_n == 0 && tile_n > 128) tile_n = 128;
   const int tile_k = c.tile_k ? c.tile_k : 32;
-  if (shp.split_k > 1 && n_extra == 0) {
+  // 2, 4 or 8 pieces of tiles up to 128 columns wide are reduced inside a thread-block cluster
+  // (variant = 1 keeps the workspace form)
+  const bool cluster_split = shp.split_k > 1 && n_extra == 0 && c.variant != 1 &&
+                             (shp.split_k == 2 || shp.split_k == 4 || shp.split_k == 8) &&
+                             shp.tile_n <= 128 && tma_addressable(C, ldc) && N % 4 == 0 &&
+                             c.precision == XTC_CUDA_PRECISION_TF32 &&
+                             shp.tiles <= cluster_capacity(dev, shp.split_k);
+  if (cluster_split) {
+    a.split_k = shp.split_k;
+    a.cluster_k = true;
+  } else if (shp.split_k > 1 && n_extra == 0) {
     const size_t counters = align256(static_cast<size_t>(shp.tiles) * 4);
     const size_t need = counters + static_cast<size_t>(shp.split_k) * shp.tiles * BM * shp.tile_n * 4;
     if (workspace != nullptr && workspace_bytes >= need) {

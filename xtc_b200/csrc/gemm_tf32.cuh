@@ -59,6 +59,12 @@ struct GemmParams {
   int split_kblocks;
   float* partials;
   int* tile_counters;
+  // Split-K inside a thread-block cluster (cluster_k = 1; split_k is the cluster size,
+  // 2, 4 or 8; one work item per CTA): the CTAs of a cluster hold the K pieces of one
+  // tile, park their accumulators in their own shared memory (the operand ring is free
+  // by then) and each sums 128 / split_k rows of the tile over all pieces through
+  // distributed shared memory, in piece order.  No workspace, no pass through L2.
+  int cluster_k;
   // Split tail of the CTA-pair kernel (gemm_tf32_pair.cuh): the tail_tiles tiles of
   // the last, partly idle round are each cut into tail_split pieces along K, one
   // piece per pair.  tail_split = 0 turns it off.
@@ -433,6 +439,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tmem_ld_wait();
             if (!split) {
               store_block(r, m0, n0 + c * 32);
+            } else if (p.cluster_k) {
+              // float4 (row, q) of the tile lives at [q][row]: a warp writes 512 contiguous bytes
+              float4* red4 = reinterpret_cast<float4*>(ring);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                red4[(c * 8 + j) * BM + quad * 32 + lane] =
+                    make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
             } else {
 #pragma unroll
               for (int j = 0; j < 8; ++j)
@@ -456,7 +470,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           store_block(r, m0, n0 + c * 32);
         }
       }
-      if (split && !failed) {
+      if (split && !p.cluster_k && !failed) {
         // Publish the partial, count arrivals; the CTA that completes the tile reduces.
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -497,6 +511,41 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     if (TMA_STORE) tma_store_wait_all<0>();
+  }
+
+  if (p.cluster_k) {
+    // Every thread of the cluster meets here twice, whatever its role did before (the
+    // role loops above are bounded, so a CTA whose wait gave up still arrives).
+    __syncwarp();
+    cluster_sync_all();  // all pieces of the tile are parked in their CTAs' shared memory
+    if (warp >= 2) {
+      const int tile = static_cast<int>(blockIdx.x) / p.split_k;
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int rows_own = BM / p.split_k;
+      const int rank = static_cast<int>(cluster_ctarank());  // = this CTA's piece
+      const uint32_t red_base = smem_u32(ring);
+      for (int i = (warp - 2) * 32 + lane; i < rows_own * (BN / 4); i += EPI_WARPS * 32) {
+        const int q = i / rows_own;
+        const int row = rank * rows_own + (i - q * rows_own);
+        const uint32_t offset = static_cast<uint32_t>(q * BM + row) * 16u;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int piece = 0; piece < p.split_k; ++piece) {  // fixed order: bit-reproducible
+          const float4 v = ld_shared_cluster_f4(map_to_cta(red_base + offset, piece));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (p.relu) {
+          acc.x = fmaxf(acc.x, p.relu_threshold); acc.y = fmaxf(acc.y, p.relu_threshold);
+          acc.z = fmaxf(acc.z, p.relu_threshold); acc.w = fmaxf(acc.w, p.relu_threshold);
+        }
+        const int grow = m0 + row, gcol = n0 + 4 * q;
+        if (grow < p.M && gcol < p.N)  // N is a multiple of 4 in this mode
+          *reinterpret_cast<float4*>(p.C + static_cast<size_t>(grow) * p.ldc + gcol) = acc;
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // no CTA leaves while the others still read its shared memory
   }
 
   if (failed) {
