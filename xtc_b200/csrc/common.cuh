@@ -77,6 +77,17 @@ struct AutoChoice {
 AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
                                bool split_ok, const int* cluster_cap = nullptr);
 int cluster_capacity(int dev, int size);
+// Pieces (8, 4, 2, or 1 = do not split) a cluster split of `k_blocks` K stages runs with when
+// `want` were asked for: the largest power of two not above `want` whose pieces, of
+// ceil(k_blocks / pieces) stages each, are all non-empty.
+inline int cluster_pieces(int k_blocks, int want) {
+  for (int s = 8; s >= 2; s >>= 1) {
+    if (s > want) continue;
+    const int per = (k_blocks + s - 1) / s;
+    if ((s - 1) * per < k_blocks) return s;
+  }
+  return 1;
+}
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------

@@ -24,6 +24,7 @@ struct ConvArgs {
   int split_k = 1;            // im2col kernel, one CTA per tile: CTAs sharing a tile along K
   float* partials = nullptr;  // [split][tile][128][tile_n]
   int* counters = nullptr;    // [tile], zeroed once
+  bool cluster_k = false;     // 2, 4 or 8 pieces summed inside a thread-block cluster (no workspace)
 };
 
 __global__ void __launch_bounds__(256)
@@ -123,12 +124,17 @@ int launch_conv_tc(const ConvArgs& a) {
   p.conv_cblocks = static_cast<int>((a.C + BK - 1) / BK);
   p.k_blocks = static_cast<int>(a.R * a.S) * p.conv_cblocks;
   p.chunk_kblocks = p.k_blocks;
-  const int want_split = (a.partials && a.counters) ? a.split_k : 1;
+  const bool in_cluster = a.cluster_k && BN <= 128;
+  const int want_split = in_cluster ? cluster_pieces(p.k_blocks, a.split_k)
+                                    : (a.partials && a.counters) ? a.split_k : 1;
   p.split_kblocks = (p.k_blocks + want_split - 1) / want_split;
   p.split_k = (p.k_blocks + p.split_kblocks - 1) / p.split_kblocks;
   p.partials = a.partials;
   p.tile_counters = a.counters;
   if (p.split_k > 1) p.chunk_kblocks = p.split_kblocks;
+  p.cluster_k = in_cluster && (p.split_k == 2 || p.split_k == 4 || p.split_k == 8);
+  XTC_REQUIRE(p.cluster_k || !in_cluster || p.split_k == 1,
+              "conv2d: the cluster split needs 2, 4 or 8 pieces, got %d", p.split_k);
   p.relu = a.relu;
   p.relu_threshold = a.thr;
   p.status = device_status_word(dev);
@@ -152,9 +158,10 @@ int launch_conv_tc(const ConvArgs& a) {
     configured_smem = smem;
   }
   const int tiles = p.tiles_m * p.tiles_n * p.split_k;
-  const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
-  XTC_CUDA_CHECK(launch_overlapped(kernel, grid, NUM_THREADS, smem, a.stream, tmA, tmB, tmZ, tmZ, tmC,
-                                   p, stages));
+  // cluster split: one work item per CTA, the pieces of a tile in consecutive CTAs
+  const int grid = p.cluster_k ? tiles : (tiles < sm_count(dev) ? tiles : sm_count(dev));
+  XTC_CUDA_CHECK(launch_overlapped_clustered(kernel, grid, p.cluster_k ? p.split_k : 1, NUM_THREADS,
+                                             smem, a.stream, tmA, tmB, tmZ, tmZ, tmC, p, stages));
   return XTC_CUDA_OK;
 }
 
@@ -373,6 +380,14 @@ static size_t conv_split_bytes(int64_t M, int64_t F, const AutoChoice& pick) {
   return ((tiles * 4 + 255) & ~static_cast<size_t>(255)) +
          static_cast<size_t>(pick.split_k) * tiles * BM * pick.tile_n * 4;
 }
+// A split the im2col launcher reduces inside a thread-block cluster (no workspace): 2, 4 or
+// 8 pieces of a tile at most 128 filters wide, with every cluster resident at once.
+static bool conv_split_in_cluster(int64_t M, int64_t F, const AutoChoice& pick, int dev) {
+  if (pick.tile_m != BM || pick.tile_n > 128 || F % 4 != 0) return false;
+  if (pick.split_k != 2 && pick.split_k != 4 && pick.split_k != 8) return false;
+  const int64_t tiles = ((M + BM - 1) / BM) * ((F + pick.tile_n - 1) / pick.tile_n);
+  return tiles <= cluster_capacity(dev, pick.split_k);
+}
 static bool conv_names_nothing(const xtc_cuda_gemm_config& c) {
   return c.precision == XTC_CUDA_PRECISION_TF32 && c.variant == 0 && c.tile_m == 0 && c.tile_n == 0 &&
          c.tile_k == 0 && c.split_k == 0;
@@ -409,7 +424,11 @@ extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, 
     return XTC_CUDA_OK;  // resident weights: no workspace
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
-  *bytes = conv_split_bytes(M, F, choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sms, true, true));
+  int caps[9] = {};
+  for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+  const AutoChoice pick =
+      choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sms, true, true, F % 4 == 0 ? caps : nullptr);
+  *bytes = conv_split_in_cluster(M, F, pick, dev) ? 0 : conv_split_bytes(M, F, pick);
   return XTC_CUDA_OK;
 }
 
@@ -501,9 +520,15 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     // nothing named: the GEMM cost model on M = pixels, N = filters, K = taps x padded channels
     // (split-K only with the zeroed workspace xtc_cuda_conv2d_workspace_bytes asks for)
     const int64_t kpad = R * S * ((C + 31) / 32 * 32);
-    AutoChoice pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), true);
+    int caps[9] = {};
+    for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+    AutoChoice pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), true,
+                                          a16(Y) && F % 4 == 0 ? caps : nullptr);
     const size_t need = conv_split_bytes(M, F, pick);
-    if (need > 0 && c.split_k == 0 && workspace != nullptr && workspace_bytes >= need) {
+    if (need > 0 && c.split_k == 0 && a16(Y) && conv_split_in_cluster(M, F, pick, dev)) {
+      a.split_k = pick.split_k;
+      a.cluster_k = true;
+    } else if (need > 0 && c.split_k == 0 && workspace != nullptr && workspace_bytes >= need) {
       const size_t tiles = static_cast<size_t>((M + BM - 1) / BM) * ((F + pick.tile_n - 1) / pick.tile_n);
       a.split_k = pick.split_k;
       a.counters = static_cast<int*>(workspace);

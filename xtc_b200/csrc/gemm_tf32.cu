@@ -162,7 +162,8 @@ int launch_tc(const LaunchArgs& a) {
   for (int d = 0; d < p.n_extra; ++d) p.extra_dst[d] = a.extra[d];
   const bool in_cluster = !SPLIT3 && a.cluster_k && BN <= 128;
   const int want_split =
-      SPLIT3 ? 1 : (in_cluster || (a.partials != nullptr && a.counters != nullptr)) ? a.split_k : 1;
+      SPLIT3 ? 1 : in_cluster ? cluster_pieces(p.k_blocks, a.split_k)
+                              : (a.partials != nullptr && a.counters != nullptr) ? a.split_k : 1;
   p.split_kblocks = (p.k_blocks + want_split - 1) / want_split;
   p.split_k = (p.k_blocks + p.split_kblocks - 1) / p.split_kblocks;
   p.partials = a.partials;
