@@ -435,8 +435,13 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
   const double ksteps = static_cast<double>((K + 7) / 8);
   AutoChoice best{128, 128, 32, 1};
   double best_t = 1e300;
+  // Short K under a narrow N (1x1 convolutions as GEMMs): a tile is one or two K stages, the
+  // step is the epilogue and HBM, and the per-tile hand-offs of a CTA pair only cost
+  // (100352x256x64: 33 us with pairs, 26 us with 128x256 tiles, at the HBM floor of 20 us;
+  // 100352x64x256: 29 - 31 us against 24 us).
+  const bool skinny = K <= 256 && N <= 256;
   for (const Cand& c : cands) {
-    if (c.tm == 256 && !pair_ok) continue;
+    if (c.tm == 256 && (!pair_ok || skinny)) continue;
     const int64_t tiles = ((M + c.tm - 1) / c.tm) * ((N + c.tn - 1) / c.tn);
     const int64_t slots = c.tm == 256 ? sms / 2 : sms;
     const int64_t full = tiles / slots, rem = tiles % slots;
@@ -602,6 +607,9 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
     c.tile_n = pick.tile_n;
     c.tile_k = pick.tile_k;
     c.split_k = pick.tile_m == 2 * BM ? 0 : pick.split_k;
+    // bulk tensor stores for the one-CTA kernel too: with one or two K stages per tile the
+    // epilogue is the step, and direct stores take 39 us where TMA stores take 26
+    if (pick.tile_m == BM && c.epilogue == 0 && tma_addressable(C, ldc)) c.epilogue = 2;
   }
   XTC_REQUIRE(c.tile_m == 0 || c.tile_m == BM || c.tile_m == 2 * BM,
               "gemm: tile_m=%d unsupported (128, or 256 for the CTA-pair kernel)", c.tile_m);
