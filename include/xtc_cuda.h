@@ -99,6 +99,8 @@ typedef struct xtc_cuda_gemm_config {
                         Any other split needs the workspace of
                         xtc_cuda_gemm_workspace_bytes, zeroed before its
                         first use (the kernel leaves its counters zero again).
+                        conv2d (im2col kernels, tile_m = 128): 2, 4 or 8 = the cluster
+                        form under the same conditions, else the layer runs unsplit.
                         With tile_m = 256: 0 = when the last round of tiles would leave
                         CTA pairs idle, share the K blocks of the last tiles out evenly
                         (same workspace rule; without a workspace the tiles simply go

@@ -541,6 +541,14 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     tile_n = pick.tile_n;
   }
   if (tile_n == 0) tile_n = F <= 64 ? 64 : (F <= 128 ? 128 : 256);
+  if (c.split_k > 1 && tile_m != 2 * BM && a16(Y)) {
+    // a split the caller asked for runs where the cluster form applies, else the layer runs unsplit
+    const AutoChoice asked{BM, tile_n, 0, c.split_k};
+    if (conv_split_in_cluster(M, F, asked, dev)) {
+      a.split_k = c.split_k;
+      a.cluster_k = true;
+    }
+  }
   int tile_k = c.tile_k ? c.tile_k : (C % 64 == 0 ? 64 : 32);
   const bool tma_store = c.epilogue == 2 && a16(Y);
   if (tile_m == 2 * BM && a16(Y)) return dispatch_conv_pair(a, tile_n, tile_k);
