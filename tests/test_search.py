@@ -15,7 +15,7 @@ def test_strategy_space_is_legal_and_maps_one_to_one():
     strat = Strategies.create("cuda_gemm", graph)
     space = list(strat.exhaustive())
     assert len(space) == len({tuple(s) for s in space}) > 40
-    assert strat.sample_names == ["tile_m", "tile_n", "tile_k", "stages", "tma_store"]
+    assert strat.sample_names == ["tile_m", "tile_n", "tile_k", "stages", "tma_store", "split_k"]
     for s in space:
         assert strat.is_legal(s)
         sch = Backend(graph).get_scheduler(strict=True)  # strict: an illegal point would raise
@@ -23,9 +23,13 @@ def test_strategy_space_is_legal_and_maps_one_to_one():
         cfg = sch.schedule().node_configs()["C"]
         assert (cfg["tile_m"], cfg["tile_n"], cfg["tile_k"]) == tuple(s[:3])
         assert cfg.get("stages", 0) == s[3] and cfg.get("epilogue", 0) == (2 if s[4] else 0)
+        assert cfg.get("split_k", 1) == s[5]
     # the shared-memory filter: 128x256x64 leaves room for 2 stages, not for 3
-    assert strat.is_legal([128, 256, 64, 2, 0]) and not strat.is_legal([128, 256, 64, 3, 0])
-    assert not strat.is_legal([128, 96, 32, 0, 0])
+    assert strat.is_legal([128, 256, 64, 2, 0, 1]) and not strat.is_legal([128, 256, 64, 3, 0, 1])
+    assert not strat.is_legal([128, 96, 32, 0, 0, 1])
+    # pieces of the reduction: one CTA per tile, at most 128 columns, K divisible
+    assert strat.is_legal([128, 128, 64, 0, 1, 8]) and not strat.is_legal([256, 128, 64, 0, 1, 2])
+    assert not strat.is_legal([128, 256, 32, 0, 1, 2]) and not strat.is_legal([128, 64, 32, 0, 0, 3])
     assert strat.sample(5, seed=1) == strat.sample(5, seed=1) and len(strat.sample(5, 1)) == 5
     for level in range(4):
         assert strat.is_legal(strat.default_schedule(level))
@@ -36,14 +40,19 @@ def test_strategy_targets_the_contraction_of_a_fused_graph():
     strat = Strategies.create("cuda_gemm", graph)
     assert strat.node_name == "C"
     sch = Backend(graph).get_scheduler()
-    strat.generate(sch, [128, 128, 64, 3, 1])
+    strat.generate(sch, [128, 128, 64, 3, 1])  # a five-value sample of an older table still works
     assert sch.schedule().node_configs() == {
         "C": {"tile_m": 128, "tile_n": 128, "tile_k": 64, "stages": 3, "epilogue": 2}}
+    sch = Backend(graph).get_scheduler(strict=True)
+    strat.generate(sch, [128, 64, 64, 0, 1, 4])
+    assert sch.schedule().node_configs()["C"]["split_k"] == 4
+    assert "k_s3" in str(sch.schedule())
     conv = conv2d_graph(2, 8, 8, 64, 3, 3, 32, 1, 1)
     cs = Strategies.create("cuda_gemm", conv)
     assert {s[0] for s in cs.exhaustive()} == {128, 256}
     sch = Backend(conv).get_scheduler(strict=True)
-    cs.generate(sch, [128, 64, 64, 0, 0])
+    assert {s[5] for s in cs.exhaustive()} == {1}  # no split dimension for convolutions
+    cs.generate(sch, [128, 64, 64, 0, 0, 1])
     assert sch.schedule().node_configs()["O"] == {"tile_m": 128, "tile_n": 64, "tile_k": 64}
     with pytest.raises(KeyError):
         Strategies.create("nope", graph)
@@ -65,7 +74,7 @@ def test_exploration_csv_and_resume(tmp_path, monkeypatch):
     results = exp.run()
     assert len(results) == 6 and len(calls) == 6
     rows = list(csv.DictReader(open(out)))
-    assert list(rows[0].keys()) == ["tile_m", "tile_n", "tile_k", "stages", "tma_store", "X", "time",
+    assert list(rows[0].keys()) == ["tile_m", "tile_n", "tile_k", "stages", "tma_store", "split_k", "X", "time",
                                     "peak", "backend"]
     assert len(rows) == 6 and all(r["backend"] == "cuda" for r in rows)
     best_sample, best_time = exp.best()

@@ -11,7 +11,9 @@ width, register count, L1/L2 footprint; ``search/strategies.py:150-171,
 is the shared-memory budget of the pipeline.
 
 Sample layout of ``cuda_gemm`` (also used for conv2d):
-    [tile_m, tile_n, tile_k, stages, tma_store]
+    [tile_m, tile_n, tile_k, stages, tma_store, split_k]
+``split_k`` (1, 2, 4, 8) cuts a matmul's reduction into segments that run
+concurrently, one CTA of a thread-block cluster each (``scheduler.split``).
 """
 
 from __future__ import annotations
@@ -35,16 +37,18 @@ class StrategyCudaGemm:
     """Exhaustive / random search over CTA tile, K per stage, pipeline depth, epilogue."""
 
     name = "cuda_gemm"
-    sample_names = ["tile_m", "tile_n", "tile_k", "stages", "tma_store"]
+    sample_names = ["tile_m", "tile_n", "tile_k", "stages", "tma_store", "split_k"]
 
     TILE_M = (128, 256)
     TILE_N = (64, 128, 256)
     TILE_K = (32, 64)
     STAGES = (0, 2, 3, 4, 6)  # 0 = as deep as shared memory allows
+    SPLITS = (1, 2, 4, 8)     # pieces of the reduction (matmul, one CTA per tile, tile_n <= 128)
 
     def __init__(self, graph: Any, tile_m: tuple[int, ...] | None = None,
                  tile_n: tuple[int, ...] | None = None, tile_k: tuple[int, ...] | None = None,
-                 stages: tuple[int, ...] | None = None, **_ignored: Any) -> None:
+                 stages: tuple[int, ...] | None = None, splits: tuple[int, ...] | None = None,
+                 **_ignored: Any) -> None:
         self._graph = graph
         self._node = contraction_node(graph)
         self._op = self._node.operation
@@ -53,6 +57,8 @@ class StrategyCudaGemm:
         self.tile_n = tuple(tile_n or self.TILE_N)
         self.tile_k = tuple(tile_k or self.TILE_K)
         self.stages = tuple(stages or self.STAGES)
+        self.splits = tuple(splits or self.SPLITS) if not self._is_conv else (1,)
+        self._k_extent = 0 if self._is_conv else int(list(self._op.dims.values())[2])
 
     @property
     def graph(self) -> Any:
@@ -71,8 +77,13 @@ class StrategyCudaGemm:
         return (128 + tile_n) * tile_k * 4
 
     def is_legal(self, sample: list[int]) -> bool:
-        tm, tn, tk, st, tma = sample
+        tm, tn, tk, st, tma = sample[:5]
+        split = sample[5] if len(sample) > 5 else 1
         if tm not in self.TILE_M or tn not in self.TILE_N or tk not in self.TILE_K:
+            return False
+        if split not in self.SPLITS:
+            return False
+        if split > 1 and (self._is_conv or tm != 128 or tn > 128 or self._k_extent % (split * tk)):
             return False
         if tma not in (0, 1) or not (st == 0 or 2 <= st <= 8):
             return False
@@ -81,7 +92,8 @@ class StrategyCudaGemm:
         return depth * self.stage_bytes(tm, tn, tk) <= budget
 
     def exhaustive(self):
-        for s in itertools.product(self.tile_m, self.tile_n, self.tile_k, self.stages, (0, 1)):
+        for s in itertools.product(self.tile_m, self.tile_n, self.tile_k, self.stages, (0, 1),
+                                   self.splits):
             s = list(s)
             if self.is_legal(s):
                 yield s
@@ -95,16 +107,17 @@ class StrategyCudaGemm:
     def default_schedule(self, opt_level: int = 2) -> list[int]:
         """O0: smallest tiles, shallow pipeline; O3: the widest tile, deepest pipeline."""
         if opt_level <= 0:
-            return [128, 64, 32, 2, 0]
+            return [128, 64, 32, 2, 0, 1]
         if opt_level == 1:
-            return [128, 128, 32, 0, 0]
+            return [128, 128, 32, 0, 0, 1]
         if opt_level == 2 or self._is_conv:
-            return [128, 256 if not self._is_conv else 64, 32 if not self._is_conv else 64, 0, 1]
-        return [256, 256, 32, 0, 1]
+            return [128, 256 if not self._is_conv else 64, 32 if not self._is_conv else 64, 0, 1, 1]
+        return [256, 256, 32, 0, 1, 1]
 
     # -- sample -> scheduler calls ---------------------------------------------------
     def generate(self, scheduler: Any, sample: list[int]) -> None:
-        tm, tn, tk, st, tma = [int(v) for v in sample]
+        tm, tn, tk, st, tma = [int(v) for v in sample[:5]]
+        split = int(sample[5]) if len(sample) > 5 else 1
         dims = list(self._op.dims)
         target = scheduler.node(self.node_name) if hasattr(scheduler, "node") else scheduler
         if self._is_conv:
@@ -115,6 +128,9 @@ class StrategyCudaGemm:
             target.parallelize(dims[:3])
         else:
             row, col, red = dims
+            if split > 1:
+                piece = self._k_extent // split
+                target.split(red, {f"{red}_s{i}": i * piece for i in range(split)})
             target.tile(row, {f"{row}1": tm})
             target.tile(col, {f"{col}1": tn})
             target.tile(red, {f"{red}1": tk})
