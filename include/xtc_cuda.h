@@ -54,10 +54,25 @@ int xtc_cuda_stream_create(void** stream);
 int xtc_cuda_stream_destroy(void* stream);
 int xtc_cuda_stream_synchronize(void* stream);
 int xtc_cuda_device_synchronize(void);
-/* Reads and clears the per-device status word that kernels set when one of
- * their bounded waits gives up (0 = none).  Error reporting in the reference is
- * the (results, code, message) tuple of src/xtc/utils/evaluation.py:129-145. */
+/* Free and total device memory of the current device (cudaMemGetInfo).  The
+ * reference's device interface has no such query
+ * (src/xtc/runtimes/accelerator/gpu/GPUDevice.py:131-215); tests use it to show
+ * that an entry point allocates nothing. */
+int xtc_cuda_mem_info(size_t* free_bytes, size_t* total_bytes);
+/* Synchronises the device, then reads and clears the status words that kernels
+ * set when one of their bounded waits gives up (0 = none): the per-device word
+ * of the regular entry points and the word of xtc_cuda_gemm_f32_3xtf32_noalloc.
+ * Allocates nothing once the device has been used.  Error reporting in the
+ * reference is the (results, code, message) tuple of
+ * src/xtc/utils/evaluation.py:129-145. */
 int xtc_cuda_device_status(int* status);
+/* Self-test of the bounded waits: launches one CTA whose single waiting thread
+ * waits on a barrier that nothing completes, gives up after limit_ms
+ * (1..1000) exactly as the compute kernels do after their 2 s, records the
+ * give-up code in the device status word and returns normally.  The next
+ * xtc_cuda_device_status therefore reads a non-zero status and clears it.  No
+ * counterpart in the reference (its kernels have no in-kernel waits). */
+int xtc_cuda_selftest_bounded_wait(int limit_ms, void* stream);
 const char* xtc_cuda_last_error(void);
 
 /* ------------------------------------------------------------------------
@@ -158,11 +173,14 @@ int xtc_cuda_ipc_release(void* device_ptr);
  * the library image: every GPU that loads the library holds those 32 MiB until
  * the process exits.
  *
- * C[M,N] = A * B (+ relu), operands dense (lda = K or M, ldb = N or K, ldc = N),
- * 16-byte aligned, row lengths multiples of 4; flags as for xtc_cuda_gemm_f32.
+ * C[M,N] = A * B (+ relu), A, B and C dense (lda = K or M, ldb = N or K, ldc = N),
+ * 16-byte aligned, row lengths multiples of 4 (all three are checked); flags as
+ * for xtc_cuda_gemm_f32.
  * Limit: 2 * (round256(4*M*K) + round256(4*K*N)) <= 32 MiB, i.e. about
  * M*K + K*N <= 4 Mi elements; larger problems are refused with
- * XTC_CUDA_ERR_INVALID and a message that states both sizes.
+ * XTC_CUDA_ERR_INVALID and a message that states both sizes (the element
+ * counts are bounded before any byte count is formed, so no extent up to 2^31
+ * can wrap past the check).
  *
  * The call makes no cudaMalloc / cudaFree and calls no allocating library
  * routine.  The first call on each device looks up the device address of the
@@ -172,8 +190,10 @@ int xtc_cuda_ipc_release(void* device_ptr);
  * ordering between them) race on it; calls on one stream are safe.  The array
  * keeps the previous call's contents, which is harmless: every byte the GEMM
  * reads is rewritten by the split kernels of the same call first.  A bounded
- * wait that gives up inside this variant is recorded in a word of the library
- * image, not in the word xtc_cuda_device_status reads. */
+ * wait that gives up inside this variant is recorded in a second word of the
+ * library image; xtc_cuda_device_status reads and clears it together with the
+ * regular status word (with two cudaMemcpy calls on the cached address, no
+ * allocation). */
 int xtc_cuda_gemm_f32_3xtf32_noalloc(const float* A, const float* B, float* C, int64_t M,
                                      int64_t N, int64_t K, int flags, float relu_threshold,
                                      void* stream);
@@ -254,6 +274,17 @@ typedef struct xtc_cuda_step {
 
 typedef struct xtc_cuda_plan xtc_cuda_plan;
 
+/* Workspace of one step as xtc_cuda_plan_create allocates it: its size and how
+ * many leading bytes the plan clears once (split-K tile counters, one int per
+ * output tile whatever their number, and split-tail flags must read zero at the
+ * first launch; the kernels leave them zero again).  A caller that drives
+ * xtc_cuda_gemm_f32 / xtc_cuda_conv2d_nhwc_f32 directly clears the same bytes
+ * of the workspace it passes.  Needs no device.  The reference keeps no such
+ * scratch (its split reductions are sequential loops,
+ * src/xtc/backends/mlir/MlirNodeScheduler.py:139-160). */
+int xtc_cuda_step_workspace_bytes(const struct xtc_cuda_step* step, size_t* total_bytes,
+                                  size_t* zeroed_bytes);
+
 /* slot_bytes[n_slots] gives every slot's size.  The plan allocates the
  * intermediates and any kernel workspace on the current device.  Plays the role
  * of Compiler.compile -> Module, src/xtc/backends/mlir/MlirCompiler.py:67-110. */
@@ -298,8 +329,7 @@ int xtc_cuda_pipeline_destroy(xtc_cuda_pipeline* pipe);
  * a measurement lasts min_repeat_ms; results[r] = seconds per run. */
 int xtc_cuda_evaluate(xtc_cuda_plan* plan, void* const* io, int repeat, int number,
                       int min_repeat_ms, double* results);
-/* Device time of the kernels launched by the most recent xtc_cuda_evaluate
- * measurement, per step, in seconds per run (n_steps doubles). */
+/* Number of steps (kernel-level operations) of a plan. */
 int xtc_cuda_plan_step_count(const xtc_cuda_plan* plan, int* n_steps);
 
 /* Peak fused-multiply-add rate of the tensor pipe for "float32" (TF32 inputs),

@@ -250,6 +250,30 @@ def test_library_exports_every_declared_symbol(cuda_lib):
     assert cuda_lib.xtc_cuda_abi_version() == 1
 
 
+def test_plan_clears_every_split_k_counter(cuda_lib):
+    """A split-K step keeps one int per output tile at the start of its workspace.  With
+    more than 16384 tiles those counters pass 64 KiB: the bytes a plan clears must cover
+    all of them (needs no device: the sizes are host arithmetic)."""
+    from xtc_b200.backends.cuda.lowering import StepDesc
+
+    m, n, k = 128 * 130, 64 * 128, 96  # 130 x 128 = 16640 tiles of 128 x 64
+    step = StepDesc("gemm", "mm", 0, 1, 2, dims=(m, n, k, k, n, n),
+                    config={"tile_m": 128, "tile_n": 64, "tile_k": 32, "split_k": 3, "variant": 1}).to_c()
+    total, zeroed = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    capi.check(cuda_lib.xtc_cuda_step_workspace_bytes(ctypes.byref(step), ctypes.byref(total),
+                                                      ctypes.byref(zeroed)))
+    tiles = (m // 128) * (n // 64)
+    counters = (tiles * 4 + 255) // 256 * 256
+    assert counters > 65536
+    assert total.value == counters + 3 * tiles * 128 * 64 * 4
+    assert zeroed.value >= counters
+    # the 3xTF32 operand split is rewritten by every run: nothing to clear
+    step.cfg.precision = capi.PRECISION_3XTF32
+    capi.check(cuda_lib.xtc_cuda_step_workspace_bytes(ctypes.byref(step), ctypes.byref(total),
+                                                      ctypes.byref(zeroed)))
+    assert total.value > 0 and zeroed.value == 0
+
+
 def test_struct_layout_matches_the_header(cuda_lib):
     # sizeof(xtc_cuda_gemm_config) = 8 int32; sizeof(xtc_cuda_step) = 8*4 + 3*6*8 + 32
     assert ctypes.sizeof(capi.GemmConfig) == 32

@@ -91,7 +91,39 @@ def test_noalloc_gemm_matches_the_regular_entry_point_twice_in_a_row(cuda_lib):
         assert _rel_err(noalloc, regular.astype(np.float64)) <= FP32_TOL
         # same kernels, same arithmetic, same order: the bits agree as well
         assert np.array_equal(noalloc, regular)
+    # reads (and would clear) the status word of this entry point as well as the regular one
     assert dev.status() == 0
+
+
+def _free_bytes(dev):
+    free, total = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    capi.check(dev.lib.xtc_cuda_mem_info(byref(free), byref(total)))
+    return free.value
+
+
+def test_noalloc_gemm_leaves_free_device_memory_unchanged(cuda_lib):
+    """What the entry point is for: after the first call on the device (which resolves the
+    address of the built-in array), a call takes nothing from the device allocator."""
+    dev = CudaDevice(0)
+    assert dev.detect_accelerator(), "this test needs a CUDA device"
+    dev.activate()
+    M, K, N = 256, 512, 128
+    rng = np.random.default_rng(7)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    dA, dB, dC = _put(dev, A), _put(dev, B), dev.memory_allocate(M * N * 4)
+    lib = dev.lib
+    capi.check(lib.xtc_cuda_gemm_f32_3xtf32_noalloc(dA, dB, dC, M, N, K, 0, 0.0, None))  # warm-up
+    assert dev.status() == 0
+    before = _free_bytes(dev)
+    for _ in range(3):
+        capi.check(lib.xtc_cuda_gemm_f32_3xtf32_noalloc(dA, dB, dC, M, N, K, 0, 0.0, None))
+    assert dev.status() == 0  # synchronises, reads both status words: no allocation either
+    assert _free_bytes(dev) == before
+    y64 = A.astype(np.float64) @ B.astype(np.float64)
+    assert _rel_err(_get(dev, dC, (M, N)), y64) <= FP32_TOL
+    for d in (dA, dB, dC):
+        dev.memory_free(d)
 
 
 def test_noalloc_gemm_refuses_what_does_not_fit(cuda_lib):
@@ -103,6 +135,20 @@ def test_noalloc_gemm_refuses_what_does_not_fit(cuda_lib):
     assert rc == capi.ERR_INVALID
     msg = capi.last_error()
     assert "scratch" in msg and str(32 << 20) in msg
+    # just over the limit: 1024 x 2048 + 2048 x 1024 elements fill the 32 MiB exactly, one
+    # more row of A does not fit
+    big = dev.memory_allocate(4 * 1028 * 2048)
+    rc = dev.lib.xtc_cuda_gemm_f32_3xtf32_noalloc(big, big, big, 1028, 1024, 2048, 0, 0.0, None)
+    assert rc == capi.ERR_INVALID and "scratch" in capi.last_error()
+    # extents whose byte counts would wrap a 64-bit product must be refused, not wrapped
+    huge = (1 << 31) - 4
+    rc = dev.lib.xtc_cuda_gemm_f32_3xtf32_noalloc(big, big, big, huge, huge, huge, 0, 0.0, None)
+    assert rc == capi.ERR_INVALID and "scratch" in capi.last_error()
+    # a misaligned C is refused like a misaligned operand
+    rc = dev.lib.xtc_cuda_gemm_f32_3xtf32_noalloc(big, big, c_void_p(big.value + 4), 64, 64, 64, 0,
+                                                  0.0, None)
+    assert rc == capi.ERR_INVALID and "aligned" in capi.last_error()
     rc = dev.lib.xtc_cuda_gemm_f32_3xtf32_noalloc(None, p, p, 8, 8, 8, 0, 0.0, None)
     assert rc == capi.ERR_INVALID
+    dev.memory_free(big)
     dev.memory_free(p)

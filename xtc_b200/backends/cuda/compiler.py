@@ -118,6 +118,7 @@ def payload_source(plan: Plan) -> str:
     args = ", ".join(f"a{i}" for i in range(n_io))
     name = "".join(c if c.isalnum() or c == "_" else "_" for c in plan.name)
     return f"""/* generated by xtc_b200.backends.cuda: payload of graph {plan.name} */
+#include <pthread.h>
 #include <stdio.h>
 #include "xtc_cuda.h"
 static const xtc_cuda_step steps[] = {{
@@ -125,15 +126,23 @@ static const xtc_cuda_step steps[] = {{
 }};
 static const size_t slot_bytes[] = {_c_array(plan.slot_bytes, len(plan.slot_bytes))};
 static xtc_cuda_plan* plan;
+static pthread_once_t plan_once = PTHREAD_ONCE_INIT;
+static pthread_mutex_t run_lock = PTHREAD_MUTEX_INITIALIZER;
+static void create_plan(void) {{ /* once, whichever thread calls first */
+  if (xtc_cuda_plan_create(&plan, steps, {len(plan.steps)}, {plan.n_inputs}, {plan.n_outputs},
+                           {len(plan.slot_bytes)}, slot_bytes) != XTC_CUDA_OK) {{
+    fprintf(stderr, "{name}: %s\\n", xtc_cuda_last_error());
+    plan = NULL;
+  }}
+}}
 void {name}({params}) {{
   void* io[] = {{{args}}};
-  if (!plan && xtc_cuda_plan_create(&plan, steps, {len(plan.steps)}, {plan.n_inputs}, {plan.n_outputs},
-                                    {len(plan.slot_bytes)}, slot_bytes) != XTC_CUDA_OK) {{
-    fprintf(stderr, "{name}: %s\\n", xtc_cuda_last_error());
-    return;
-  }}
+  pthread_once(&plan_once, create_plan);
+  if (!plan) return;
+  pthread_mutex_lock(&run_lock); /* one plan, one set of staging buffers */
   if (xtc_cuda_plan_run_host(plan, io) != XTC_CUDA_OK)
     fprintf(stderr, "{name}: %s\\n", xtc_cuda_last_error());
+  pthread_mutex_unlock(&run_lock);
 }}
 """
 
@@ -145,7 +154,7 @@ def write_payload_library(plan: Plan, file_name: str) -> None:
     include = Path(__file__).resolve().parents[3] / "include"
     src = Path(file_name).with_suffix(".c")
     src.write_text(payload_source(plan))
-    cmd = ["cc", "-shared", "-fPIC", "-O1", "-I", str(include), str(src), "-o", file_name,
+    cmd = ["cc", "-shared", "-fPIC", "-O1", "-pthread", "-I", str(include), str(src), "-o", file_name,
            f"-L{lib.parent}", "-lxtc_cuda", f"-Wl,-rpath,{lib.parent}"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     src.unlink(missing_ok=True)

@@ -11,6 +11,7 @@ passes (``backends/mlir/MlirGraphBackend.py:96-148``,
   the convolution's operand fetch
 * a 2-D ``transpose`` feeding only a ``matmul`` -> folded into the GEMM as a
   transposed operand when the schedule asks for it (``fuse_producer_at``)
+* a ``reshape`` that is not a graph output -> no step: it shares its input's buffer
 * everything else -> its own bandwidth kernel (transpose, pad/crop, relu, copy)
 
 Only duck-typed graph attributes are read (``graph.nodes``, ``node.inputs``,
@@ -334,6 +335,9 @@ def lower(graph: Any, node_configs: dict[str, dict] | None = None,
                                   aux0=tuple(sign * lo for lo, _ in widths),
                                   aux1=tuple(sign * hi for _, hi in widths),
                                   bytes=nbytes(n.inputs[0]) + nbytes(n.uid)))
+        elif op.name == "reshape" and n.uid not in out_set:
+            # same bytes under another shape: the result shares its producer's buffer
+            slot_of[n.uid] = slot(n.inputs[0])
         elif op.name == "reshape":
             steps.append(StepDesc("copy", n.name, slot(n.inputs[0]), -1, slot(n.uid),
                                   dims=(_prod(shapes[n.uid]),), bytes=2 * nbytes(n.uid)))

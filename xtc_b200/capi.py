@@ -106,6 +106,9 @@ SIGNATURES: dict[str, tuple] = {
     "xtc_cuda_stream_synchronize": (c_int, [c_void_p]),
     "xtc_cuda_device_synchronize": (c_int, []),
     "xtc_cuda_device_status": (c_int, [POINTER(c_int)]),
+    "xtc_cuda_mem_info": (c_int, [POINTER(c_size_t), POINTER(c_size_t)]),
+    "xtc_cuda_selftest_bounded_wait": (c_int, [c_int, c_void_p]),
+    "xtc_cuda_step_workspace_bytes": (c_int, [POINTER(Step), POINTER(c_size_t), POINTER(c_size_t)]),
     "xtc_cuda_last_error": (c_char_p, []),
     "xtc_cuda_gemm_f32": (
         c_int,

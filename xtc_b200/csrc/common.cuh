@@ -40,6 +40,10 @@ const char* get_error();
 // Per-device word the kernels write when a bounded wait gives up.  Kernels never
 // trap; the host reads this word after synchronising (xtc_cuda_device_status).
 int* device_status_word(int dev);
+// The status word of the allocation-free GEMM (it lives in the library image, see
+// gemm_tf32.cu): reads it into *status and clears it when set.  0 when that entry point
+// has not been used on `dev` yet.  Allocates nothing.
+int noalloc_status_fetch_and_clear(int dev, int* status);
 
 // Tensor-map encoders resolved through cudaGetDriverEntryPoint, so that the
 // library has no link-time dependency on libcuda and loads on a machine
@@ -141,9 +145,9 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
-// Bounded wait: spins on the barrier phase for at most ~2 s of wall time, then
+// Bounded wait: spins on the barrier phase for at most `limit_ns` of wall time, then
 // gives up and returns false.  The caller records a status code and unwinds.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
@@ -151,9 +155,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if ((it & 0x3ff) == 0x3ff) {
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > 2000000000ull) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
+}
+// The limit every kernel of the library uses: about 2 s.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, 2000000000ull);
 }
 
 // ---- programmatic dependent launch ------------------------------------------

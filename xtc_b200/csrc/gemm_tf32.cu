@@ -739,6 +739,20 @@ std::mutex g_noalloc_mutex;
 NoallocDevice g_noalloc[64];
 }  // namespace
 
+int xtc::noalloc_status_fetch_and_clear(int dev, int* status) {
+  *status = 0;
+  if (dev < 0 || dev >= 64) return XTC_CUDA_OK;
+  int* word = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc[dev].ready) word = g_noalloc[dev].status;
+  }
+  if (word == nullptr) return XTC_CUDA_OK;  // the entry point has not run on this device
+  XTC_CUDA_CHECK(cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status != 0) XTC_CUDA_CHECK(cudaMemset(word, 0, sizeof(int)));
+  return XTC_CUDA_OK;
+}
+
 extern "C" int xtc_cuda_gemm_f32_3xtf32_noalloc(const float* A, const float* B, float* C,
                                                 int64_t M, int64_t N, int64_t K, int flags,
                                                 float relu_threshold, void* stream) {
@@ -748,15 +762,21 @@ extern "C" int xtc_cuda_gemm_f32_3xtf32_noalloc(const float* A, const float* B, 
   const bool a_t = flags & XTC_CUDA_GEMM_A_TRANSPOSED;
   const bool b_t = flags & XTC_CUDA_GEMM_B_TRANSPOSED;
   const int64_t lda = a_t ? M : K, ldb = b_t ? K : N, ldc = N;
-  XTC_REQUIRE(tma_addressable(A, lda) && tma_addressable(B, ldb),
-              "gemm_noalloc: operands must be 16-byte aligned with row lengths that are multiples of 4");
-  const size_t a_bytes = align256(static_cast<size_t>(M) * K * 4);
-  const size_t b_bytes = align256(static_cast<size_t>(K) * N * 4);
+  XTC_REQUIRE(tma_addressable(A, lda) && tma_addressable(B, ldb) && tma_addressable(C, ldc),
+              "gemm_noalloc: A, B and C must be 16-byte aligned with row lengths that are multiples of 4");
+  // Bound the element counts before any byte arithmetic: with M, N, K up to 2^31 the
+  // products below would wrap in size_t and pass the size check.
+  constexpr int64_t MAX_ELEMS = static_cast<int64_t>(NOALLOC_SCRATCH_BYTES / 8);  // hi + lo, 4 bytes each
+  const bool fits = M <= MAX_ELEMS / K && K <= MAX_ELEMS / N;  // M*K and K*N each within the scratch
+  const size_t a_bytes = fits ? align256(static_cast<size_t>(M) * K * 4) : 0;
+  const size_t b_bytes = fits ? align256(static_cast<size_t>(K) * N * 4) : 0;
   const size_t need = 2 * a_bytes + 2 * b_bytes;
-  XTC_REQUIRE(need <= NOALLOC_SCRATCH_BYTES,
-              "gemm_noalloc: M*K + K*N = %lld elements need %zu bytes of scratch, the built-in "
-              "scratch holds %zu (use xtc_cuda_gemm_f32 with a caller workspace for larger problems)",
-              (long long)(M * K + K * N), need, NOALLOC_SCRATCH_BYTES);
+  XTC_REQUIRE(fits && need <= NOALLOC_SCRATCH_BYTES,
+              "gemm_noalloc: A (%lld x %lld) and B (%lld x %lld) need %.0f bytes of scratch for the "
+              "operand split, the built-in scratch holds %zu (use xtc_cuda_gemm_f32 with a caller "
+              "workspace for larger problems)",
+              (long long)M, (long long)K, (long long)K, (long long)N,
+              8.0 * (static_cast<double>(M) * K + static_cast<double>(K) * N), NOALLOC_SCRATCH_BYTES);
   int dev = 0;
   XTC_CUDA_CHECK(cudaGetDevice(&dev));
   XTC_REQUIRE(dev >= 0 && dev < 64, "gemm_noalloc: device ordinal %d out of range", dev);

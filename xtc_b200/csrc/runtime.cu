@@ -214,10 +214,47 @@ extern "C" int xtc_cuda_device_status(int* status) {
   XTC_REQUIRE(word != nullptr, "device_status: status word unavailable");
   XTC_CUDA_CHECK(cudaDeviceSynchronize());
   XTC_CUDA_CHECK(cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*status != 0) {
-    XTC_CUDA_CHECK(cudaMemset(word, 0, sizeof(int)));
-    set_error("a kernel's bounded wait gave up (device status %d)", *status);
+  if (*status != 0) XTC_CUDA_CHECK(cudaMemset(word, 0, sizeof(int)));
+  // the allocation-free GEMM reports into a word of its own (it may not use the
+  // allocated one): read and clear that too
+  int noalloc = 0;
+  int rc = noalloc_status_fetch_and_clear(dev, &noalloc);
+  if (rc != XTC_CUDA_OK) return rc;
+  if (*status == 0) *status = noalloc;
+  if (*status != 0) set_error("a kernel's bounded wait gave up (device status %d)", *status);
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_mem_info(size_t* free_bytes, size_t* total_bytes) {
+  XTC_REQUIRE(free_bytes && total_bytes, "mem_info: NULL");
+  XTC_CUDA_CHECK(cudaMemGetInfo(free_bytes, total_bytes));
+  return XTC_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// self-test of the bounded wait
+// ---------------------------------------------------------------------------
+namespace xtc {
+// One thread waits, for at most limit_ns, on a barrier phase that nothing completes,
+// records the give-up code exactly as the compute kernels do and returns.
+__global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    dev::mbar_init(&bar, 1);
+    dev::fence_barrier_init();
+    if (!dev::mbar_wait_limit(&bar, 0, limit_ns)) atomicCAS(status, 0, dev::STATUS_WAIT_TIMEOUT_LOAD);
   }
+}
+}  // namespace xtc
+
+extern "C" int xtc_cuda_selftest_bounded_wait(int limit_ms, void* stream) {
+  XTC_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, "selftest_bounded_wait: limit %d ms not in [1, 1000]", limit_ms);
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  int* word = device_status_word(dev);
+  XTC_REQUIRE(word != nullptr, "selftest_bounded_wait: status word unavailable");
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint64_t>(limit_ms) * 1000000ull, word);
+  XTC_CUDA_CHECK(cudaGetLastError());
   return XTC_CUDA_OK;
 }
 
@@ -253,6 +290,22 @@ static int step_workspace(const xtc_cuda_step& s, size_t* bytes) {
                                            s.dims[5], s.aux0[0], (int)s.aux0[1], (int)s.aux0[2],
                                            (int)s.aux1[0], (int)s.aux1[1], (int)s.aux1[2],
                                            (int)s.aux1[3], &s.cfg, bytes);
+  return XTC_CUDA_OK;
+}
+
+extern "C" int xtc_cuda_step_workspace_bytes(const xtc_cuda_step* step, size_t* total_bytes,
+                                             size_t* zeroed_bytes) {
+  XTC_REQUIRE(step && total_bytes && zeroed_bytes, "step_workspace_bytes: NULL argument");
+  *zeroed_bytes = 0;
+  int rc = step_workspace(*step, total_bytes);
+  if (rc != XTC_CUDA_OK) return rc;
+  // The split-K tile counters (one int per output tile, however many tiles there are) and
+  // the split-tail flags sit at the start of the workspace and must read zero at the first
+  // launch; the partial tiles behind them are written before they are read.  The whole
+  // workspace is cleared: it is done once per plan.  The 3xTF32 operand split is rewritten
+  // by every run before it is read and needs no clearing.
+  const bool split3 = step->kind == XTC_CUDA_STEP_GEMM && step->cfg.precision == XTC_CUDA_PRECISION_3XTF32;
+  *zeroed_bytes = split3 ? 0 : *total_bytes;
   return XTC_CUDA_OK;
 }
 
@@ -295,13 +348,12 @@ extern "C" int xtc_cuda_plan_create(xtc_cuda_plan** plan, const xtc_cuda_step* s
   for (int s = n_inputs + n_outputs; s < n_slots && rc == XTC_CUDA_OK; ++s)
     rc = xtc_cuda_malloc(&p->owned[s], p->slot_bytes[s]);
   for (int i = 0; i < n_steps && rc == XTC_CUDA_OK; ++i) {
-    size_t need = 0;
-    rc = step_workspace(p->steps[i], &need);
+    size_t need = 0, zeroed = 0;
+    rc = xtc_cuda_step_workspace_bytes(&p->steps[i], &need, &zeroed);
     if (rc == XTC_CUDA_OK && need > 0) {
       rc = xtc_cuda_malloc(&p->workspace[i], need);
       p->workspace_bytes[i] = need;
-      // split-K tile counters live at the start of the workspace and must start at zero
-      if (rc == XTC_CUDA_OK && cudaMemset(p->workspace[i], 0, need < 65536 ? need : 65536) != cudaSuccess)
+      if (rc == XTC_CUDA_OK && zeroed > 0 && cudaMemset(p->workspace[i], 0, zeroed) != cudaSuccess)
         rc = XTC_CUDA_ERR_RUNTIME;
     }
   }

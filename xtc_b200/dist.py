@@ -171,6 +171,16 @@ class PeerStoreMatmul:
         self._flag = torch.zeros(1, device="cuda")
         self._dist = dist
 
+    def _on_stream(self, stream: int | None) -> Any:
+        """Context that makes `stream` (a raw cudaStream_t; None or 0 = the legacy default
+        stream) torch's current stream, so that a collective issued inside it is ordered
+        after the kernels this object launched on that stream."""
+        import torch
+
+        if not stream:
+            return torch.cuda.stream(torch.cuda.default_stream())
+        return torch.cuda.stream(torch.cuda.ExternalStream(int(stream)))
+
     def step(self, stream: int | None = None) -> None:
         from . import capi
 
@@ -180,7 +190,10 @@ class PeerStoreMatmul:
         if rc:
             capi.check(rc)
         if self.world > 1:
-            self._dist.all_reduce(self._flag, group=self.group)  # stream-ordered barrier
+            # the barrier that says "every peer's stores into my C have landed": it must
+            # follow the GEMM on the GEMM's own stream, whatever torch's current stream is
+            with self._on_stream(stream):
+                self._dist.all_reduce(self._flag, group=self.group)
 
     def result(self) -> Any:
         """The full C of this rank as a NumPy array (synchronises)."""
@@ -192,7 +205,10 @@ class PeerStoreMatmul:
 
     def close(self) -> None:
         if self.world > 1:
-            self._dist.barrier(group=self.group)  # nobody may still be storing into a freed C
+            # nobody may still be storing into a C that is about to be freed: every kernel of
+            # every stream of this device first, then all ranks meet
+            self.device.synchronize()
+            self._dist.barrier(group=self.group)
         for ptr in self.imported:
             self.lib.xtc_cuda_ipc_release(ptr)
         self.imported = []
