@@ -3,24 +3,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1..c5] [--impl reference]
 
-N == 1 (default workload c2, matmul 4096^3 + relu): one step = one run of the
-compiled graph.  N > 1 (launched by torchrun, default workload c5, the
-row-sharded 65536x8192x8192 matmul): one step = every rank computes its row
-block and the blocks are all-gathered; total work is fixed ("strong" scaling).
-Prints ONE JSON line on rank 0.
+Plain ``python bench.py`` (one GPU): workload c2, matmul 4096^3 + relu; one step =
+one run of the compiled graph ("weak": the work per GPU is the whole graph).
+Launched by torch.distributed.run (any world size, 1 included): workload c5, the
+row-sharded 65536x8192x8192 matmul; one step = every rank computes its row block and
+the blocks are exchanged; the total work is fixed ("strong"), so the values at
+1, 2, 4 and 8 ranks are one curve.  Prints ONE JSON line on rank 0.
 
   value     graph throughput with inputs resident in device memory
   e2e       the same through host buffers: pinned host -> device copies of the
             inputs and a device -> host copy of the result inside the timed region
   roofline  the dominant kernel's achieved rate against the measured peak
+  other_configs   the remaining graphs and the standalone bandwidth kernels, device-resident
   cpu_baseline / --impl reference
             the CPU loop-nest restatement of the reference's MLIR llvmir lowering
-            (oracle/cpu_loopnest.c) on the host cores
+            (oracle/cpu_loopnest.c) on all host cores, its tile sizes tuned first with
+            this repository's exploration driver
 """
 
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
 import math
 import os
@@ -51,6 +55,10 @@ def measured_peaks() -> dict:
                 "source": "MEASURED_PEAKS.json (of measured)"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
             "source": "recipe fallback (of fallback)"}
+
+
+def under_torchrun() -> bool:
+    return "TORCHELASTIC_RUN_ID" in os.environ or "LOCAL_RANK" in os.environ
 
 
 # --------------------------------------------------------------------------- #
@@ -114,45 +122,90 @@ class ClockSampler:
 # CPU baseline (the reference arm)
 # --------------------------------------------------------------------------- #
 def cpu_sample(workload: str) -> tuple:
-    """(inputs, description, fraction of the full workload) of the bounded CPU sample."""
+    """(sample graph, inputs, description, fraction of the full workload) of the bounded CPU
+    sample: the full graph, except for c5 where rows 0..1024 of A stand for all 65536."""
     from xtc_b200 import configs
 
     if workload == "c5":
-        rows = 1024  # 1/64 of the rows; time scales linearly with rows
-        rng = np.random.default_rng(4)
-        a = rng.uniform(-1, 1, (rows, 8192)).astype(np.float32)
-        b = rng.normal(0, 1 / np.sqrt(8192), (8192, 8192)).astype(np.float32)
-        return [a, b], f"rows 0..{rows} of A (1/64 of the work), all of B", rows / 65536
-    if workload == "c4":
-        return configs.inputs("c4"), "the full graph (transpose + matmul)", 1.0
-    return configs.inputs(workload), "the full workload", 1.0
+        rows = 1024  # 1/64 of the rows; the time scales linearly with the rows
+        cfg = configs.build("c5", rows=rows)
+        return cfg, configs.input_rows("c5", 0, rows), f"rows 0..{rows} of A (1/64 of the work), all of B", rows / 65536
+    return configs.build(workload), configs.inputs(workload), "the full workload", 1.0
 
 
-def time_cpu(workload: str, steps: int, warmup: int) -> dict:
-    """Times the CPU loop nests on all host cores; TFLOP/s of the full workload."""
+def blas_ceiling(workload: str, ins: list, flops: float, frac: float) -> dict | None:
+    """NumPy / OpenBLAS time of the same sample (matmul graphs only): a sanity ceiling for
+    the loop nests, not the reference's own code generator."""
+    if workload not in ("c1", "c2", "c4", "c5"):
+        return None
+    a, b = ins
+
+    def run() -> None:
+        lhs = a.T if workload == "c4" else a
+        out = lhs @ b
+        if workload == "c2":
+            np.maximum(out, 0, out=out)
+
+    run()
+    times = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+    return {"value": flops * frac / min(times) / 1e12, "unit": "TFLOP/s",
+            "what": "NumPy/OpenBLAS sgemm on the same sample and cores (its own thread count)"}
+
+
+def time_cpu(workload: str, steps: int, warmup: int, trials: int = 16) -> dict:
+    """Tunes the CPU loop nests on this host with the exploration driver (random search over
+    two-level tile sizes and register tiles), then times the best sample on all host cores.
+    Returns the cpu_baseline object plus `seconds_per_sample`."""
+    from oracle import cpu_backend as cpb
     from oracle import cpu_baseline as cb
-    from xtc_b200 import configs
 
-    cfg = configs.build(workload)
-    ins, desc, frac = cpu_sample(workload)
+    cfg, ins, desc, frac = cpu_sample(workload)
+    full_flops = cfg.flops / frac if cfg.flops else 0.0
+    sample, tuned = None, "no contraction to tune"
+    if cfg.flops:
+        t0 = time.perf_counter()
+        sample, best_sec, n = cpb.tune(cfg.graph, trials=trials, inputs=ins)
+        names = cpb.StrategyCpuTile(cfg.graph).sample_names
+        tuned = (f"best of {n} random samples of the two-level tiled, packed, register-blocked nest: "
+                 f"{dict(zip(names, sample))} (tuning took {time.perf_counter() - t0:.1f} s, untimed)")
+    name = "c5" if workload == "c5" else workload
     for _ in range(max(warmup, 1)):
-        cb.run_config(workload, ins)
+        cb.run_config(name, ins, sample)
     times = []
     for _ in range(max(steps, 1)):
         t0 = time.perf_counter()
-        cb.run_config(workload, ins)
+        cb.run_config(name, ins, sample)
         times.append(time.perf_counter() - t0)
     t = min(times)
-    work, unit = (cfg.flops / 1e12, "TFLOP/s") if cfg.flops else (cfg.bytes / 1e9, "GB/s")
-    return {"value": work * frac / t, "unit": unit, "cores": cb.threads(),
-            "kind": "port", "sample": f"{desc}; best of {len(times)} runs, {t * 1e3:.1f} ms each",
-            "seconds_per_sample": t}
+    if cfg.flops:
+        value, unit = full_flops * frac / t / 1e12, "TFLOP/s"
+    else:
+        value, unit = cfg.bytes / t / 1e9, "GB/s"
+    out = {"value": value, "unit": unit, "cores": cb.threads(), "kind": "port",
+           "sample": f"{desc}; {tuned}; best of {len(times)} timed runs, {t * 1e3:.1f} ms each",
+           "seconds_per_sample": t}
+    if cfg.flops:
+        peak = cb.peak_fma() * 2 / 1e12
+        out["host_fma_peak_tflops"] = peak
+        out["frac_of_host_fma_peak"] = value / peak
+        out["blas_ceiling"] = blas_ceiling(workload, ins, full_flops, frac)
+    return out
+
+
+def mlir_toolchain_present() -> bool:
+    """Whether the reference's own code generator could run here (MLIR python bindings and
+    xdsl importable).  It never is on this image; the line says so instead of assuming it."""
+    return all(importlib.util.find_spec(m) is not None for m in ("mlir", "xdsl"))
 
 
 def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
-    workload = args.workload or ("c2" if world == 1 else "c5")
+    workload = args.workload or default_workload()
     steps = min(args.steps, 5)
     warm = min(args.warmup, 1)
     base = time_cpu(workload, steps, warm)
@@ -161,15 +214,23 @@ def run_reference(args, rank: int, world: int) -> None:
         "impl": "reference", "metric": "graph_throughput", "value": base["value"],
         "unit": base["unit"], "n_gpus": world, "steps": steps, "warmup": warm,
         "ms_per_step": t * 1e3, "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "scaling": "strong" if under_torchrun() else "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": workload_name(workload)},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": base["unit"], "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
+        "mlir_toolchain_present": mlir_toolchain_present(),
         "note": ("the reference's MLIR llvmir backend cannot be built on this box (no MLIR/LLVM "
-                 "toolchain); this is its loop nest restated in C, OpenMP over the host cores"),
+                 "toolchain); this is its loop nest restated in C with the tile sizes tuned on "
+                 "this host, OpenMP over the host cores"),
     }
     print(json.dumps(line), flush=True)
+
+
+def default_workload() -> str:
+    """c2 for a plain one-GPU run; c5 when launched by torch.distributed.run, at every world
+    size, so that the 1/2/4/8-rank values are the same work."""
+    return "c5" if under_torchrun() else "c2"
 
 
 def workload_name(w: str) -> str:
@@ -180,6 +241,8 @@ def workload_name(w: str) -> str:
         "c4": "c4: transpose 8192^2 + matmul 8192x8192x1024 f32",
         "c4a": "c4a: transpose 8192^2 f32 alone",
         "c5": "c5: row-sharded matmul 65536x8192x8192 f32 + all-gather",
+        "relu512": "standalone relu, 512 MiB tensor",
+        "pad512": "standalone pad of H and W by 1, 512 MiB tensor",
     }[w]
 
 
@@ -232,12 +295,12 @@ def time_device_steps(torch, fn, steps: int, warmup: int, barrier=None):
 
 
 def bench_graph_device(torch, dev, name: str, steps: int, warmup: int, precision="tf32",
-                       fuse_transpose=None, device_inputs=None):
+                       fuse_transpose=None, device_inputs=None, rows=None):
     """Device-resident throughput of one configuration on the current GPU."""
     from xtc_b200 import configs
     from xtc_b200.backends.cuda.module import PlanHandle
 
-    cfg = configs.build(name)
+    cfg = configs.build(name, rows=rows) if rows else configs.build(name)
     module = configs.compile_config(cfg, precision=precision, fuse_transpose=fuse_transpose)
     plan = module.plan
     handle = PlanHandle(plan, dev)
@@ -248,6 +311,7 @@ def bench_graph_device(torch, dev, name: str, steps: int, warmup: int, precision
     if device_inputs is None:
         host = configs.inputs(name)
         device_inputs = [torch.from_numpy(h).cuda() for h in host]
+        del host
     sets = []
     for s in range(n_sets):
         ins = device_inputs if s == 0 else [t.clone() for t in device_inputs]
@@ -262,7 +326,7 @@ def bench_graph_device(torch, dev, name: str, steps: int, warmup: int, precision
     total, per = time_device_steps(torch, step, steps, max(warmup, n_sets))
     assert dev.status() == 0, "a kernel reported a bounded-wait timeout"
     info = {"cfg": cfg, "plan": plan, "seconds": total / steps, "per_step": per,
-            "n_sets": n_sets, "set_bytes": set_bytes, "handle": handle, "sets": sets}
+            "n_sets": n_sets, "set_bytes": set_bytes, "handle": handle, "sets": sets, "step": step}
     return info
 
 
@@ -302,19 +366,28 @@ def measure_e2e(torch, dev, handle, cfg, workload: str, steps: int) -> dict:
     return {"sec": e2e_sec, "sync_sec": e2e_sync_sec, "h2d": h2d, "d2h": d2h, "steps": e2e_steps}
 
 
-def roofline_of(cfg, seconds: float, peaks: dict, workload: str, sustained: bool) -> dict:
+def tf32_denominator(peaks: dict, sustained: bool) -> tuple[float, str]:
+    """TF32 tensor peak used as the roofline denominator: half the measured dense bf16
+    figure (kind::tf32 issues at half the bf16 rate; the driver-written file has no TF32
+    entry), burst for a kernel timed alone, sustained for a seconds-long loop."""
+    bf16 = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+    return bf16 / 2.0, (peaks["source"] + ": dense bf16 / 2 for TF32 ("
+                        + ("sustained" if sustained else "burst") + ")")
+
+
+def roofline_of(cfg, seconds: float, peaks: dict, workload: str, sustained: bool,
+                precision: str = "tf32") -> dict:
     if cfg.bound == "hbm":
         achieved = cfg.bytes / seconds / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get(workload),
                 "peak_source": peaks["source"]}
-    bf16 = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
-    peak = bf16 / 2.0  # kind::tf32 issues at half the bf16 rate
+    peak, source = tf32_denominator(peaks, sustained)
+    if precision == "3xtf32":
+        peak, source = peak / 3.0, source + " / 3 products per FMA"
     achieved = cfg.flops / seconds / 1e12
     return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(workload),
-            "peak_source": peaks["source"] + ": dense bf16 / 2 for TF32 ("
-                           + ("sustained" if sustained else "burst") + ")"}
+            "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(workload), "peak_source": source}
 
 
 NVLINK_PEER_GBS = 770.0  # measured peer copy bandwidth per direction per GPU on this pool
@@ -335,10 +408,152 @@ def fused_roofline(flops_per_rank: float, exchange_bytes_per_rank: float, second
                      f"sustained), NVLink {NVLINK_PEER_GBS:.0f} GB/s per direction (measured peer copy)"}
 
 
+def cublas_tf32(torch, seconds: float = 4.0) -> dict:
+    """cuBLAS TF32 (torch.matmul, allow_tf32) on 8192^3: best of 10 (burst) and back to
+    back for `seconds` (sustained) -- the method of the driver's bf16 measurement, for the
+    arithmetic these kernels actually use.  A yardstick beside the roofline denominator."""
+    n = 8192
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.rand(n, n, device="cuda") - 0.5
+        b = torch.rand(n, n, device="cuda") - 0.5
+        c = torch.empty(n, n, device="cuda")
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1e-3)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        count = max(8, int(seconds / best))
+        e0.record()
+        for _ in range(count):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        torch.cuda.synchronize()
+        sus = e0.elapsed_time(e1) * 1e-3 / count
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    flops = 2.0 * n ** 3
+    return {"burst_tflops": flops / best / 1e12, "sustained_tflops": flops / sus / 1e12,
+            "how": f"torch.matmul allow_tf32 {n}^3: best of 10, and {count} back to back"}
+
+
+def sustained_segment(torch, info: dict, seconds: float, sampler: ClockSampler) -> dict:
+    """At least `seconds` of back-to-back steps of an already warmed configuration, clocks
+    sampled: what the kernel holds once the power limit has engaged."""
+    per = info["seconds"]
+    count = max(16, int(seconds / per))
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(count):
+        info["step"](i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    return {"steps": count, "seconds": e0.elapsed_time(e1) * 1e-3, "clocks": clocks,
+            "sec_per_step": e0.elapsed_time(e1) * 1e-3 / count}
+
+
+def launch_floor_us(torch, dev) -> float:
+    """Seconds per run of the smallest tensor-core GEMM (one 128 x 64 tile, one K stage) back
+    to back: what a launch of these kernels costs before any work (prologue, barriers, tensor
+    memory allocation, one TMA round trip, epilogue)."""
+    import xtc_b200.graphs.xtc.op as O
+    from xtc_b200.backends.cuda import Backend
+    from xtc_b200.backends.cuda.module import PlanHandle
+
+    a = O.tensor((128, 32), "float32", name="A")
+    b = O.tensor((32, 64), "float32", name="B")
+    with O.graph(name="floor") as gb:
+        O.matmul(a, b, name="C")
+    module = Backend(gb.graph).get_compiler(shared_lib=False).compile(None)
+    handle = PlanHandle(module.plan, dev)
+    da, db, dc = (torch.zeros(128, 32, device="cuda"), torch.zeros(32, 64, device="cuda"),
+                  torch.zeros(128, 64, device="cuda"))
+    ptrs = [da.data_ptr(), db.data_ptr(), dc.data_ptr()]
+    stream = torch.cuda.current_stream().cuda_stream
+    total, _ = time_device_steps(torch, lambda i: handle.run(ptrs, stream), 400, 20)
+    handle.close()
+    return total / 400 * 1e6
+
+
+def other_configs(torch, dev, args, peaks: dict) -> dict:
+    """Every other configuration, device-resident: the metric is per graph."""
+    tf32_burst, _ = tf32_denominator(peaks, False)
+    tf32_sus, _ = tf32_denominator(peaks, True)
+    extra: dict = {}
+
+    def tensor_entry(name, r, precision="tf32", sustained=False):
+        c = r["cfg"]
+        tf = c.flops / r["seconds"] / 1e12
+        peak = (tf32_sus if sustained else tf32_burst) / (3.0 if precision == "3xtf32" else 1.0)
+        return {"tflops": tf, "us": r["seconds"] * 1e6, "frac_of_tf32_peak": tf / peak,
+                "peak": peak, "peak_kind": ("sustained" if sustained else "burst")
+                + (" / 3 (three products per FMA)" if precision == "3xtf32" else "")}
+
+    def guarded(key, fn):
+        try:
+            extra[key] = fn()
+        except Exception as e:  # keep the headline line even if a side measurement fails
+            extra[key] = {"error": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
+
+    def c1():
+        r = bench_graph_device(torch, dev, "c1", max(args.steps, 400), args.warmup)
+        out = tensor_entry("c1", r)
+        floor = launch_floor_us(torch, dev)
+        c = r["cfg"]
+        # c1 is 0.27 GFLOP over 3.7 MB: neither the tensor pipe (0.3 us) nor HBM (0.6 us)
+        # bounds it; the applicable floor is what a launch of these kernels costs
+        out["bound"] = {"kind": "launch", "launch_floor_us": floor,
+                        "tensor_us": c.flops / (tf32_burst * 1e12) * 1e6,
+                        "hbm_us": c.bytes / (peaks["hbm_gbs"] * 1e9) * 1e6,
+                        "frac_of_bound": floor / (r["seconds"] * 1e6)}
+        return out
+
+    guarded("c1", c1)
+    guarded("c3", lambda: tensor_entry("c3", bench_graph_device(torch, dev, "c3", max(args.steps, 200), args.warmup)))
+    guarded("c4", lambda: tensor_entry("c4", bench_graph_device(torch, dev, "c4", max(args.steps, 50), args.warmup)))
+
+    def hbm_entry(name):
+        r = bench_graph_device(torch, dev, name, max(args.steps, 100), args.warmup)
+        gbs = r["cfg"].bytes / r["seconds"] / 1e9
+        return {"gbs": gbs, "us": r["seconds"] * 1e6, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                "peak": peaks["hbm_gbs"], "bytes": r["cfg"].bytes}
+
+    for name in ("c4a", "relu512", "pad512"):
+        guarded(name, lambda name=name: hbm_entry(name))
+
+    # c5 on one GPU, device-resident: TF32 and 3xTF32 (seconds-long tensor work: sustained peak)
+    def c5(precision):
+        from xtc_b200 import configs
+
+        a, b = configs.inputs("c5")
+        dins = [torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()]
+        del a, b
+        steps = 20 if precision == "tf32" else 8
+        r = bench_graph_device(torch, dev, "c5", steps, 3, precision=precision, device_inputs=dins)
+        out = tensor_entry("c5", r, precision, sustained=True)
+        out["steps"] = steps
+        return out
+
+    guarded("c5_n1_tf32", lambda: c5("tf32"))
+    guarded("c5_n1_3xtf32", lambda: c5("3xtf32"))
+    return extra
+
+
 def run_single(args) -> None:
     import torch
 
-    from xtc_b200 import configs
     from xtc_b200.runtimes.cuda import CudaDevice
 
     torch.cuda.set_device(0)
@@ -375,7 +590,7 @@ def run_single(args) -> None:
                    "l2": f"inputs rotate over {info['n_sets']} buffer sets of "
                          f"{info['set_bytes'] / 1e6:.0f} MB (> 126 MB L2 in total)"},
         "roofline": roofline_of(cfg, statistics.median(info["per_step"]), peaks, workload,
-                                sustained=sec * args.steps > 1.0),
+                                sustained=sec * args.steps > 1.0, precision=args.precision),
         "e2e": None if e2e is None else {
             "value": unit_work / e2e["sec"] / scale, "unit": unit, "h2d_bytes_per_step": e2e["h2d"],
             "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e["sec"] * 1e3, "steps": e2e["steps"],
@@ -385,19 +600,29 @@ def run_single(args) -> None:
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
-    # ---- the other configurations, device-resident, for context --------------
+    # ---- the same kernel for a second or more: sustained clocks ---------------
+    if not args.no_extra and cfg.flops:
+        seg = sustained_segment(torch, info, 1.2, ClockSampler(0))
+        sus = roofline_of(cfg, seg["sec_per_step"], peaks, workload, sustained=True,
+                          precision=args.precision)
+        line["value_sustained"] = unit_work / seg["sec_per_step"] / scale
+        line["sustained"] = {"steps": seg["steps"], "seconds": seg["seconds"],
+                             "ms_per_step": seg["sec_per_step"] * 1e3, "clocks": seg["clocks"],
+                             "roofline": sus}
+    del info
+    torch.cuda.empty_cache()
+    # ---- the other configurations and the cuBLAS TF32 yardstick ----------------
     if not args.no_extra and workload == "c2":
-        extra = {}
-        for name in ("c1", "c3", "c4"):
-            try:
-                r = bench_graph_device(torch, dev, name, max(args.steps, 200), args.warmup)
-                c = r["cfg"]
-                extra[name] = {"tflops": c.flops / r["seconds"] / 1e12, "us": r["seconds"] * 1e6,
-                               "frac_of_tf32_peak": c.flops / r["seconds"] / 1e12 / (peaks["bf16_tflops"] / 2)}
-                del r
-            except Exception as e:  # keep the headline line even if a side measurement fails
-                extra[name] = {"error": str(e)}
-        line["other_configs"] = extra
+        line["other_configs"] = other_configs(torch, dev, args, peaks)
+        try:
+            yard = cublas_tf32(torch)
+            line["tf32_cublas"] = yard
+            line["roofline"]["frac_of_cublas_tf32_burst"] = line["roofline"]["achieved"] / yard["burst_tflops"]
+            if "sustained" in line:
+                line["sustained"]["roofline"]["frac_of_cublas_tf32_sustained"] = (
+                    line["value_sustained"] / yard["sustained_tflops"])
+        except Exception as e:
+            line["tf32_cublas"] = {"error": str(e)}
     # ---- CPU baseline ---------------------------------------------------------
     if not args.no_cpu:
         base = time_cpu(workload, 3, 1)
@@ -423,6 +648,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
     peaks = measured_peaks()
     stream = torch.cuda.current_stream().cuda_stream
     sampler = ClockSampler(local_rank)
+    checks: dict = {}
 
     def barrier() -> None:
         dist.barrier()
@@ -430,16 +656,16 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
     if workload == "c5":
         M, K, N = 65536, 8192, 8192
         rows = M // world
+        row_lo = rank * rows
         cfg = configs.build("c5", rows=rows)
         module = configs.compile_config(cfg, precision=args.precision)
         handle = PlanHandle(module.plan, dev)
-        gen = torch.Generator(device="cuda").manual_seed(4 + rank)
-        a_blk = torch.rand(rows, K, device="cuda", generator=gen) * 2 - 1
-        genb = torch.Generator(device="cuda").manual_seed(4)
-        b = torch.randn(K, N, device="cuda", generator=genb) / math.sqrt(8192)
+        # the seeded inputs of the configuration: this rank's rows of A, all of B
+        host_a, host_b = configs.input_rows("c5", row_lo, row_lo + rows)
+        a_blk = torch.from_numpy(host_a).cuda()
+        b = torch.from_numpy(host_b).cuda()
         c_full = torch.empty(M, N, device="cuda") if args.exchange == "nccl" else None
         c_blk = torch.empty(rows, N, device="cuda")  # target of the compute-only timing
-        row_lo = rank * rows
 
         def compute(lo: int, hi: int, _stream) -> None:
             if hi - lo == rows:
@@ -449,24 +675,24 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
                     [a_blk[lo - row_lo: hi - row_lo].data_ptr(), b.data_ptr(), c_full[lo:hi].data_ptr()], stream)
 
         chunk_handles = {}
-        if args.chunks > 1:
+        if args.chunks > 1 and args.exchange == "nccl":
             from xtc_b200.dist import chunk_ranges
             for lo, hi in chunk_ranges(row_lo, row_lo + rows, args.chunks):
                 if (hi - lo) not in chunk_handles:
                     ccfg = configs.build("c5", rows=hi - lo)
                     chunk_handles[hi - lo] = PlanHandle(
                         configs.compile_config(ccfg, precision=args.precision).plan, dev)
+        peer_op = None
         if args.exchange == "peer":
             from xtc_b200.dist import PeerStoreMatmul
             gemm_cfg = dict(module.plan.steps[-1].config)
-            op = PeerStoreMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
-                                 config=gemm_cfg)
-            result_block_ptr = op.c_block
+            op = peer_op = PeerStoreMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
+                                           config=gemm_cfg)
             sharding = (f"rows of A and C split over {world} ranks, B replicated; the GEMM epilogue "
-                        f"stores each C tile into every rank's C over NVLink (fused all-gather)")
+                        f"stores each C tile into every rank's C over NVLink (fused all-gather)"
+                        if world > 1 else "one rank holds all rows (no exchange)")
         else:
             op = RowShardedMatmul(c_full, world, rank, compute, chunks=args.chunks)
-            result_block_ptr = c_full[row_lo:row_lo + rows].data_ptr()
             sharding = f"rows of A and C split over {world} ranks, B replicated, NCCL all-gather of C"
         step = lambda i: op.step(stream)
         total_flops = 2 * M * N * K
@@ -495,7 +721,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         exchange_bytes = 0
         sharding = f"batch of 32 split over {world} ranks, no collective"
     else:
-        raise SystemExit(f"workload {workload} does not shard; run it with --gpus 1")
+        raise SystemExit(f"workload {workload} does not shard; run it with plain `python bench.py`")
 
     if rank == 0:
         sampler.start()
@@ -506,57 +732,76 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
     sec = float(t.item()) / args.steps
     status = dev.status()
 
+    # ---- outside the timed region: is the gathered C right? ---------------------------
+    if workload == "c5":
+        # this rank recomputes, in float64 on the host, a few rows that ANOTHER rank produced
+        # (from the seeded inputs of that rank's block) and compares them with its own copy
+        peer = (rank + 1) % world
+        pick = np.sort(np.random.default_rng(100 + rank).choice(rows, 4, replace=False))
+        peer_rows = peer * rows + pick
+        a_peer = np.stack([configs.input_rows("c5", int(r), int(r) + 1)[0][0] for r in peer_rows])
+        want = a_peer.astype(np.float64) @ host_b.astype(np.float64)
+        torch.cuda.synchronize()
+        if peer_op is not None:
+            got = np.empty((4, N), np.float32)
+            for i, r in enumerate(peer_rows):
+                dev.memory_copy_from(_ptr(peer_op.c_local.value + int(r) * N * 4), got[i], N * 4)
+        else:
+            got = c_full[torch.from_numpy(peer_rows).cuda()].cpu().numpy()
+        err = float(np.abs(got - want).max() / np.abs(want).max())
+        checks = {"gathered_rows_checked": [int(r) for r in peer_rows], "from_rank": peer,
+                  "rel_err_vs_float64": err, "tolerance": 1e-2 if args.precision == "tf32" else 1e-5}
+        ok = torch.tensor([1.0 if err <= checks["tolerance"] else 0.0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        checks["all_ranks_ok"] = bool(ok.item() == 1.0)
+        assert checks["all_ranks_ok"], f"gathered rows differ from the recomputation: {checks}"
+
     # compute-only time of the local block (no exchange), for the roofline line
     comp_total, comp_per = time_device_steps(
         torch, lambda i: handle.run(
             [a_blk.data_ptr(), b.data_ptr(), c_blk.data_ptr()], stream)
         if workload == "c5" else step(i), max(3, min(args.steps, 10)), 1, barrier)
     kernel_sec = statistics.median(comp_per)
+    t = torch.tensor([kernel_sec], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    kernel_sec_max = float(t.item())
 
     # end to end: the rank's inputs from pinned host memory, its result block back
     e2e_steps = 4
-    if workload == "c5":
-        host_a = torch.empty(rows, K, pin_memory=True)
-        host_c = torch.empty(rows, N, pin_memory=True)
-
-        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-        main = torch.cuda.current_stream()
-
-        def e2e_run(n: int) -> None:
-            """n steps; every step copies the rank's A block in and its C block out.  The
-            input copy of step i+1 and the output copy of step i both follow the kernel of
-            step i and run side by side (the link is full duplex)."""
-            ev_in, ev_out, ev_run = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
-            with torch.cuda.stream(s_in):
-                a_blk.copy_(host_a, non_blocking=True)
-                ev_in.record(s_in)
-            for i in range(n):
-                main.wait_event(ev_in)       # this step's input has landed
-                if i > 0:
-                    main.wait_event(ev_out)  # the previous result is out before C is rewritten
-                op.step(stream)
-                ev_run.record(main)
-                s_out.wait_event(ev_run)
-                dev.lib.xtc_cuda_memcpy_d2h(host_c.data_ptr(), result_block_ptr, rows * N * 4,
-                                            s_out.cuda_stream)
-                ev_out.record(s_out)
-                if i + 1 < n:
-                    s_in.wait_event(ev_run)
-                    with torch.cuda.stream(s_in):
-                        a_blk.copy_(host_a, non_blocking=True)
-                        ev_in.record(s_in)
-            torch.cuda.synchronize()
-    else:
-        host_x = torch.empty(x.shape, pin_memory=True)
-        host_y = torch.empty(cfg.output_shape, pin_memory=True)
+    if workload == "c5" and peer_op is not None:
+        pin_a = torch.from_numpy(host_a).pin_memory()
+        pin_c = torch.empty(rows, N).pin_memory()
+        loop = peer_op.host_loop()
+        e2e_api = "PeerStoreMatmul.host_loop(): submit / wait (xtc_cuda_memcpy_*, events, xtc_cuda_gemm_f32_bcast)"
 
         def e2e_run(n: int) -> None:
             for _ in range(n):
-                xs[0].copy_(host_x, non_blocking=True)
-                step(0)
-                host_y.copy_(ys[0], non_blocking=True)
+                loop.submit(pin_a.data_ptr(), pin_c.data_ptr())
+            loop.wait()
+    elif workload == "c5":
+        pin_a = torch.from_numpy(host_a).pin_memory()
+        pin_c = torch.empty(rows, N).pin_memory()
+        e2e_api = "copies + RowShardedMatmul.step (NCCL all-gather), synchronous"
+
+        def e2e_run(n: int) -> None:
+            for _ in range(n):
+                a_blk.copy_(pin_a, non_blocking=True)
+                op.step(stream)
+                pin_c.copy_(c_full[row_lo:row_lo + rows], non_blocking=True)
                 torch.cuda.synchronize()
-    e2e_run(1)
+    else:
+        host_x = pinned_like(dev, x_all[sh.lo:sh.hi])
+        host_w = pinned_like(dev, w_np)
+        host_ys = [pinned_like(dev, np.zeros(cfg.output_shape, np.float32)) for _ in range(3)]
+        pipe = handle.pipeline(depth=3)
+        e2e_steps = 30
+        e2e_api = "xtc_cuda_pipeline_submit/wait, depth 3 (pinned host buffers)"
+
+        def e2e_run(n: int) -> None:
+            for i in range(n):
+                pipe.submit([host_x, host_w, host_ys[i % 3]])
+            pipe.wait()
+    e2e_run(2)
     barrier()
     t0 = time.perf_counter()
     e2e_run(e2e_steps)
@@ -565,6 +810,27 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
     t = torch.tensor([e2e_local], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_sec = float(t.item())
+    if workload == "c5" and peer_op is not None:
+        checks["e2e_block_equals_device_block"] = bool(
+            np.array_equal(pin_c[:4].numpy(), _rows_of(dev, peer_op.c_block, 4, N)))
+
+    # the same workload on ONE GPU (rank 0 alone), so that the line carries both ends of the curve
+    single = None
+    if workload == "c5" and world > 1 and rank == 0 and not args.no_extra:
+        try:
+            if peer_op is not None:
+                pass  # its C stays mapped by the peers until close(); memory is plentiful
+            full_a, _ = configs.inputs("c5")
+            dins = [torch.from_numpy(full_a).cuda(), b]
+            del full_a
+            r = bench_graph_device(torch, dev, "c5", 10, 3, precision=args.precision, device_inputs=dins)
+            single = {"ms_per_step": r["seconds"] * 1e3, "value": total_flops / r["seconds"] / 1e12,
+                      "unit": "TFLOP/s", "steps": 10,
+                      "what": "the whole 65536-row product on rank 0's GPU alone, device-resident"}
+            del r, dins
+        except Exception as e:
+            single = {"error": f"{type(e).__name__}: {e}"}
+    barrier()
 
     if rank == 0:
         line = {
@@ -574,23 +840,51 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
             "dtype": "tf32" if args.precision == "tf32" else args.precision, "data": "synthetic",
             "config": {"workload": workload_name(workload), "sharding": sharding,
                        "chunks": args.chunks,
-                       "exchange": args.exchange if workload == "c5" else "none", "kernel_config": module.plan.steps[-1].config,
+                       "exchange": (args.exchange if world > 1 else "none") if workload == "c5" else "none",
+                       "kernel_config": module.plan.steps[-1].config,
+                       "inputs": "the configuration's seeded inputs (each rank draws its own rows)",
                        "l2": "per-rank operands (>= 0.5 GB) exceed the 126 MB L2"
                              if workload == "c5" else "inputs rotate over 8 buffer sets"},
-            "roofline": roofline_of(local_cfg, kernel_sec, peaks, workload, sustained=True),
+            "roofline": roofline_of(local_cfg, kernel_sec, peaks, workload, sustained=True,
+                                    precision=args.precision),
             "compute_only_ms": kernel_sec * 1e3,
+            "compute_only": {"ms_per_step_max_over_ranks": kernel_sec_max * 1e3,
+                             "value": total_flops / kernel_sec_max / 1e12, "unit": "TFLOP/s",
+                             "what": "every rank's block product without the exchange"},
             "fused_roofline": fused_roofline(total_flops / world, exchange_bytes, sec, peaks),
             "e2e": {"value": total_flops / e2e_sec / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                    "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
+                    "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps, "api": e2e_api,
                     "note": "per rank: own input block in, own result block out; the input copy of the "
                             "next step overlaps the output copy of this one"},
+            "checks": checks,
             "gpu_launches": launches * args.steps,
             "clocks": clocks, "device_status": status,
         }
+        if single is not None:
+            line["single_gpu_same_workload"] = single
+        if not args.no_cpu and world == 1:
+            base = time_cpu(workload, 3, 1)
+            base.pop("seconds_per_sample")
+            line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
     dist.barrier()
+    if workload == "c5" and peer_op is not None:
+        loop.close()
+        peer_op.close()
     dist.destroy_process_group()
+
+
+def _ptr(address: int):
+    import ctypes
+
+    return ctypes.c_void_p(address)
+
+
+def _rows_of(dev, address: int, n_rows: int, n: int) -> np.ndarray:
+    out = np.empty((n_rows, n), np.float32)
+    dev.memory_copy_from(_ptr(address), out, out.nbytes)
+    return out
 
 
 def main() -> None:
@@ -599,7 +893,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["c1", "c2", "c3", "c4", "c4a", "c5"])
+    ap.add_argument("--workload", default=None,
+                    choices=["c1", "c2", "c3", "c4", "c4a", "c5", "relu512", "pad512"])
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
     ap.add_argument("--unfused-transpose", action="store_true",
                     help="c4: run the transpose as its own kernel instead of reading A transposed")
@@ -621,7 +916,7 @@ def main() -> None:
     # built library is required: fail loudly, never fall back
     from xtc_b200 import capi
     capi.load()
-    if world == 1:
+    if world == 1 and not under_torchrun():
         if args.gpus != 1:
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
         run_single(args)

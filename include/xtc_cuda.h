@@ -54,6 +54,15 @@ int xtc_cuda_stream_create(void** stream);
 int xtc_cuda_stream_destroy(void* stream);
 int xtc_cuda_stream_synchronize(void* stream);
 int xtc_cuda_device_synchronize(void);
+/* Events order work between streams (record on one, wait on another) and let the
+ * host wait for a point of a stream: what a host loop needs to overlap the copies
+ * of neighbouring steps with their kernels.  The reference's device interface
+ * stops at streams (mgpuStreamCreate / mgpuStreamSynchronize, same file). */
+int xtc_cuda_event_create(void** event);
+int xtc_cuda_event_destroy(void* event);
+int xtc_cuda_event_record(void* event, void* stream);
+int xtc_cuda_event_synchronize(void* event);
+int xtc_cuda_stream_wait_event(void* stream, void* event);
 /* Free and total device memory of the current device (cudaMemGetInfo).  The
  * reference's device interface has no such query
  * (src/xtc/runtimes/accelerator/gpu/GPUDevice.py:131-215); tests use it to show

@@ -40,6 +40,13 @@ def load() -> ctypes.CDLL:
         lib.xtc_ref_relu.argtypes = [c_void_p, c_void_p, c_int64, c_float]
         lib.xtc_ref_pad_hw.argtypes = [c_void_p, c_void_p] + [c_int64] * 8 + [c_float]
         lib.xtc_ref_transpose2d.argtypes = [c_void_p, c_void_p, c_int64, c_int64]
+        lib.xtc_ref_matmul_blocked.argtypes = [c_void_p] * 3 + [c_int64] * 6 + [c_int, c_int]
+        lib.xtc_ref_matmul_blocked.restype = c_int
+        lib.xtc_ref_conv2d_blocked.argtypes = [c_void_p] * 3 + [c_int64] * 9 + [c_int, c_int]
+        lib.xtc_ref_conv2d_blocked.restype = c_int
+        lib.xtc_ref_micro_shape.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
+        lib.xtc_ref_conv_micro_shape.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
+        lib.xtc_ref_peak_fma.restype = ctypes.c_double
         _lib = lib
     return _lib
 
@@ -69,6 +76,57 @@ def conv2d(x: np.ndarray, w: np.ndarray, stride=(1, 1), relu: bool = False) -> n
     return y
 
 
+def micro_shapes() -> list[tuple[int, int]]:
+    """(rows, columns) of the register tile of every matmul micro-kernel, by index."""
+    lib, out = load(), []
+    for i in range(lib.xtc_ref_micro_count()):
+        r, c = c_int(), c_int()
+        lib.xtc_ref_micro_shape(i, ctypes.byref(r), ctypes.byref(c))
+        out.append((r.value, c.value))
+    return out
+
+
+def conv_micro_shapes() -> list[tuple[int, int]]:
+    """(pixels, filters) of the register tile of every conv2d micro-kernel, by index."""
+    lib, out = load(), []
+    for i in range(lib.xtc_ref_conv_micro_count()):
+        r, c = c_int(), c_int()
+        lib.xtc_ref_conv_micro_shape(i, ctypes.byref(r), ctypes.byref(c))
+        out.append((r.value, c.value))
+    return out
+
+
+def peak_fma() -> float:
+    """FMA/s of the host cores (register-resident vector FMA chains on every thread)."""
+    return float(load().xtc_ref_peak_fma())
+
+
+def matmul_blocked(a: np.ndarray, b: np.ndarray, sample=(128, 512, 256, 7), relu: bool = False,
+                   out: np.ndarray | None = None) -> np.ndarray:
+    """The two-level tiled, packed, register-blocked nest; sample = (mc, nc, kc, micro)."""
+    m, k = a.shape
+    n = b.shape[1]
+    c = np.empty((m, n), np.float32) if out is None else out
+    rc = load().xtc_ref_matmul_blocked(_p(a), _p(b), _p(c), m, n, k, int(sample[0]), int(sample[1]),
+                                       int(sample[2]), int(sample[3]), int(relu))
+    if rc:
+        raise ValueError(f"illegal matmul sample {tuple(sample)}")
+    return c
+
+
+def conv2d_blocked(x: np.ndarray, w: np.ndarray, stride=(1, 1), micro: int = 2, relu: bool = False,
+                   out: np.ndarray | None = None) -> np.ndarray:
+    b, h, wd, c = x.shape
+    r, s, _, f = w.shape
+    oh, ow = (h - r) // stride[0] + 1, (wd - s) // stride[1] + 1
+    y = np.empty((b, oh, ow, f), np.float32) if out is None else out
+    rc = load().xtc_ref_conv2d_blocked(_p(x), _p(w), _p(y), b, h, wd, c, r, s, f, stride[0], stride[1],
+                                       int(micro), int(relu))
+    if rc:
+        raise ValueError(f"illegal conv2d micro-kernel {micro}")
+    return y
+
+
 def relu(x: np.ndarray, threshold: float = 0.0) -> np.ndarray:
     y = np.empty_like(x)
     load().xtc_ref_relu(_p(x), _p(y), x.size, threshold)
@@ -89,11 +147,18 @@ def transpose2d(x: np.ndarray) -> np.ndarray:
     return y
 
 
-def run_config(name: str, inputs) -> np.ndarray:
-    """The benchmark graphs on the CPU loop nests."""
+def run_config(name: str, inputs, sample=None) -> np.ndarray:
+    """The benchmark graphs on the CPU loop nests.  `sample` selects the register-blocked
+    nests with that tuned sample ((mc, nc, kc, micro) for the matmul graphs, (micro,) for
+    c3); None runs the one-level nests with their fixed default tiles."""
     if name == "c4a":
         return transpose2d(inputs[0])
     a, b = inputs
+    if sample is not None:
+        if name == "c3":
+            return conv2d_blocked(pad_hw(a, 1, 1, 1, 1, 0.0), b, (1, 1), micro=sample[0], relu=True)
+        lhs = transpose2d(a) if name == "c4" else a
+        return matmul_blocked(lhs, b, sample, relu=name == "c2")
     if name == "c1":
         return matmul(a, b)
     if name == "c2":
@@ -105,26 +170,3 @@ def run_config(name: str, inputs) -> np.ndarray:
     if name == "c5":
         return matmul(a, b)
     raise KeyError(name)
-
-
-MATMUL_TILE_CANDIDATES = [(64, 0, 64), (32, 256, 128), (64, 512, 64), (128, 256, 32), (16, 1024, 256)]
-
-
-def tune_matmul(m: int, n: int, k: int, budget_s: float = 5.0):
-    """Pick the fastest of a few (ti, tj, tk) tilings on a row block: a small
-    stand-in for the reference's loop-explore search over tile factors."""
-    rows = min(m, 512)
-    rng = np.random.default_rng(0)
-    a = rng.uniform(-1, 1, (rows, k)).astype(np.float32)
-    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
-    best, best_t = MATMUL_TILE_CANDIDATES[0], float("inf")
-    t_start = time.perf_counter()
-    for cand in MATMUL_TILE_CANDIDATES:
-        t0 = time.perf_counter()
-        matmul(a, b, tiles=cand)
-        t = time.perf_counter() - t0
-        if t < best_t:
-            best, best_t = cand, t
-        if time.perf_counter() - t_start > budget_s:
-            break
-    return best

@@ -382,3 +382,49 @@ int xtc_ref_conv2d_blocked(const float* X, const float* Wt, float* Y, int64_t B,
   if (Wp != Wt) free(Wp);
   return 0;
 }
+
+/* Peak fused-multiply-add rate of the host cores in FMA/s (all OpenMP threads):
+ * twelve independent register-resident vector FMA chains per thread, the CPU twin of
+ * the reference's probe (src/xtc/csrcs/runtimes/host/evaluate_flops.c:461-495). */
+#if VW == 16
+#define KEEP(v) __asm__ volatile("" : "+v"(v))
+#else
+#define KEEP(v) __asm__ volatile("" : "+x"(v))
+#endif
+#define CHAINS(OP) OP(a0) OP(a1) OP(a2) OP(a3) OP(a4) OP(a5) OP(a6) OP(a7) OP(a8) OP(a9) OP(a10) OP(a11)
+double xtc_ref_peak_fma(void) {
+  const int64_t iters = 4000000;
+  double t_best = 1e30;
+  int threads = 1;
+  for (int rep = 0; rep < 3; ++rep) {
+    double t0 = 0, t1 = 0;
+#pragma omp parallel
+    {
+      const vf x = (vf){0} + 0.999f, y = (vf){0} + 1e-6f;
+#define INIT(v) vf v = x;
+      CHAINS(INIT)
+#pragma omp barrier
+#pragma omp master
+      {
+#ifdef _OPENMP
+        t0 = omp_get_wtime();
+        threads = omp_get_num_threads();
+#endif
+      }
+      for (int64_t it = 0; it < iters; ++it) {
+        /* the empty asm makes every value needed, in a register, every iteration */
+#define STEP(v) v = v * x + y; KEEP(v);
+        CHAINS(STEP)
+      }
+#pragma omp barrier
+#pragma omp master
+      {
+#ifdef _OPENMP
+        t1 = omp_get_wtime();
+#endif
+      }
+    }
+    if (t1 - t0 > 0 && t1 - t0 < t_best) t_best = t1 - t0;
+  }
+  return (double)threads * (double)iters * 12.0 * VW / t_best;
+}

@@ -274,6 +274,34 @@ def test_plan_clears_every_split_k_counter(cuda_lib):
     assert total.value > 0 and zeroed.value == 0
 
 
+def test_counters_library_exports_every_declared_symbol(cuda_lib):
+    """include/xtc_cuda_counters.h against the built CUPTI module and its ctypes binding."""
+    from xtc_b200.runtimes import counters as gc
+
+    header = (ROOT / "include" / "xtc_cuda_counters.h").read_text()
+    declared = set(re.findall(r"\b(xtc_cuda_counters_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(gc.SIGNATURES), declared ^ set(gc.SIGNATURES)
+    lib = gc.load()
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert gc.split_counter_names(["cycles", "gpu.clocks", "gpu.dram__bytes_read.sum"]) == (
+        [1, 2], ["clocks", "dram__bytes_read.sum"])
+    # bad arguments are refused before the profiler is touched
+    h = ctypes.c_void_p()
+    assert lib.xtc_cuda_counters_open(ctypes.byref(h), None, 0) == gc.ERR_INVALID
+    names = (ctypes.c_char_p * 1)(b"")
+    assert lib.xtc_cuda_counters_open(ctypes.byref(h), names, 1) in (gc.ERR_INVALID, gc.ERR_UNAVAILABLE)
+    assert lib.xtc_cuda_counters_last_error()
+
+
+@pytest.mark.skipif(has_cuda(), reason="checks behaviour on a machine without a GPU")
+def test_counters_say_unavailable_without_a_device(cuda_lib):
+    from xtc_b200.runtimes import counters as gc
+
+    with pytest.raises(gc.CountersError, match="no current CUDA context"):
+        gc.GpuCounters(["clocks"])
+
+
 def test_struct_layout_matches_the_header(cuda_lib):
     # sizeof(xtc_cuda_gemm_config) = 8 int32; sizeof(xtc_cuda_step) = 8*4 + 3*6*8 + 32
     assert ctypes.sizeof(capi.GemmConfig) == 32

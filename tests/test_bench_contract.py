@@ -27,7 +27,9 @@ def test_reference_arm_line():
     assert line["config"]["workload"].startswith("c1")
     base = line["cpu_baseline"]
     assert base["kind"] == "port" and base["cores"] >= 1 and base["value"] == line["value"]
-    assert "sample" in base
+    assert "sample" in base and "random samples" in base["sample"]  # tuned before it is timed
+    assert base["blas_ceiling"]["value"] > 0 and 0 < base["frac_of_host_fma_peak"] < 1.5
+    assert line["mlir_toolchain_present"] is False and line["scaling"] == "weak"
     assert line["e2e"] == {"value": line["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
                            "d2h_bytes_per_step": 0}
 
@@ -44,3 +46,38 @@ def test_reference_arm_other_ranks_print_nothing():
                   env={"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"})
     assert r.returncode == 0, r.stderr
     assert r.stdout.strip() == ""
+
+
+def test_default_workload_is_one_curve_under_torchrun():
+    """Launched by torch.distributed.run the arm benches c5 with fixed total work at every
+    world size (1 included); a plain one-GPU run benches c2."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    keep = {k: os.environ.pop(k, None) for k in ("TORCHELASTIC_RUN_ID", "LOCAL_RANK")}
+    try:
+        assert bench.default_workload() == "c2"
+        os.environ["LOCAL_RANK"] = "0"
+        assert bench.default_workload() == "c5"
+    finally:
+        os.environ.pop("LOCAL_RANK", None)
+        for k, v in keep.items():
+            if v is not None:
+                os.environ[k] = v
+
+
+def test_row_block_inputs_equal_slices_of_the_full_draw():
+    """Each rank draws only its own rows of c5's A: the draw must equal the slice of the
+    full seeded draw (checked on the generator arithmetic with a narrow stand-in)."""
+    import numpy as np
+
+    sys.path.insert(0, str(ROOT))
+    from xtc_b200 import configs
+
+    a, b = configs.input_rows("c5", 3, 5)
+    rng = np.random.default_rng(4)
+    rng.uniform(-1, 1, (3, 8192))  # the rows before
+    assert np.array_equal(a, rng.uniform(-1, 1, (2, 8192)).astype(np.float32))
+    a0, _ = configs.input_rows("c5", 0, 2)
+    assert np.array_equal(a0, np.random.default_rng(4).uniform(-1, 1, (2, 8192)).astype(np.float32))
+    assert b.shape == (8192, 8192) and abs(float(b.std()) * np.sqrt(8192) - 1) < 1e-2

@@ -106,6 +106,22 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
                 assert xo.rel_err(got, y64) <= TF32_TOL
             op.close()
             assert dev.status() == 0
+        # ---- the same step from host batches, on streams that are not torch's current one ----
+        op = PeerStoreMatmul(dev, a_blk.data_ptr(), b_dev.data_ptr(), m, n, k, world, rank,
+                             config=pair_cfg)
+        loop = op.host_loop()
+        host_a = torch.from_numpy(a[rank * rows:(rank + 1) * rows].copy()).pin_memory()
+        host_c = torch.full((rows, n), float("nan")).pin_memory()
+        a_blk.zero_()  # the loop must bring the block in itself
+        for _ in range(3):
+            loop.submit(host_a.data_ptr(), host_c.data_ptr())
+        loop.wait()
+        dist.barrier()
+        assert np.array_equal(host_c.numpy(), single[rank * rows:(rank + 1) * rows])
+        assert np.array_equal(op.result(), single), "peers' blocks arrived although no stream was current"
+        loop.close()
+        op.close()
+        assert dev.status() == 0
         Path(out_dir, f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()

@@ -107,3 +107,65 @@ def test_cpu_loopnest_matches_oracle():
                           np.pad(x, ((0, 0), (1, 2), (0, 3), (0, 0)), constant_values=1.5))
     m = np.random.default_rng(2).standard_normal((70, 33)).astype(np.float32)
     assert np.array_equal(cb.transpose2d(m), m.T)
+
+
+def test_register_blocked_nests_match_oracle():
+    """The tuned CPU nests (two-level tiling, packed operands, register tile) on ragged
+    shapes and every micro-kernel: same results as the NumPy oracle."""
+    from oracle import cpu_baseline as cb
+
+    rng = np.random.default_rng(3)
+    a = rng.uniform(-1, 1, (77, 130)).astype(np.float32)
+    b = rng.uniform(-1, 1, (130, 101)).astype(np.float32)
+    y64 = a.astype(np.float64) @ b.astype(np.float64)
+    for micro in range(len(cb.micro_shapes())):
+        for mc, nc, kc in ((48, 128, 64), (96, 512, 512)):
+            assert xo.rel_err(cb.matmul_blocked(a, b, (mc, nc, kc, micro)), y64) <= 1e-5, (micro, mc)
+    assert xo.rel_err(cb.matmul_blocked(a, b, (48, 128, 64, 0), relu=True), np.maximum(y64, 0)) <= 1e-5
+    with pytest.raises(ValueError):
+        cb.matmul_blocked(a, b, (48, 128, 64, 99))
+    for (c, f), stride in (((8, 64), (1, 1)), ((3, 20), (2, 1)), ((16, 33), (2, 2))):
+        x = rng.uniform(0, 1, (2, 11, 13, c)).astype(np.float32)
+        w = rng.normal(0, 0.1, (3, 3, c, f)).astype(np.float32)
+        ref = xo.conv2d(x.astype(np.float64), w.astype(np.float64), stride)
+        for micro in range(len(cb.conv_micro_shapes())):
+            assert xo.rel_err(cb.conv2d_blocked(x, w, stride, micro), ref) <= 1e-5, (c, f, micro)
+            assert xo.rel_err(cb.conv2d_blocked(x, w, stride, micro, relu=True), np.maximum(ref, 0)) <= 1e-5
+    assert cb.peak_fma() > 1e9
+
+
+def test_cpu_nests_are_tuned_through_the_exploration_driver(tmp_path):
+    """loop-explore over the CPU backend: the strategy's samples become tile / interchange /
+    parallelize / vectorize / unroll calls, an inner tile without a micro-kernel is refused,
+    and the best sample reproduces the oracle."""
+    from oracle import cpu_backend as cpb
+    from oracle import cpu_baseline as cb
+    from xtc_b200 import configs
+    from xtc_b200.backends.cuda.scheduler import ScheduleError
+
+    for name, scale in (("c2", 16), ("c3", 16)):
+        cfg = configs.build(name, scale)
+        ins = configs.inputs(name, scale)
+        out = tmp_path / f"{name}.csv"
+        best, seconds, n = cpb.tune(cfg.graph, trials=5, inputs=ins, output=str(out))
+        assert n >= 3 and seconds > 0
+        rows = out.read_text().splitlines()
+        assert rows[0].split(",")[-4:] == ["X", "time", "peak", "backend"] and "cpu_loopnest" in rows[1]
+        y64 = xo.config_forward(name, [x.astype(np.float64) for x in ins])
+        assert xo.rel_err(cb.run_config(name, ins, best), y64) <= 1e-5
+    cfg = configs.build("c2", 16)
+    sch = cpb.Backend(cfg.graph).get_scheduler(strict=True)
+    cpb.StrategyCpuTile(cfg.graph).generate(sch, [128, 512, 256, 6])
+    text = str(sch.schedule())
+    assert "./i2" in text and "./j2" in text
+    assert sch.schedule().node_configs()["mm"] == {"mc": 128, "nc": 512, "kc": 256, "micro": 6}
+    bad = cpb.Backend(cfg.graph).get_scheduler(strict=True)
+    bad.tile("i", {"i1": 64, "i2": 5})
+    bad.tile("j", {"j1": 64, "j2": 7})
+    bad.tile("k", {"k1": 32})
+    bad.vectorize(["j2"])
+    with pytest.raises(ScheduleError):
+        bad.schedule()
+    # validate=True on the CPU evaluator compares with the float64 oracle
+    module = cpb.Backend(cfg.graph).get_compiler().compile(sch.schedule())
+    assert module.get_evaluator(validate=True, min_repeat_ms=0).evaluate()[1] == 0

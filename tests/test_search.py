@@ -58,6 +58,64 @@ def test_strategy_targets_the_contraction_of_a_fused_graph():
         Strategies.create("nope", graph)
 
 
+def test_conv_strategy_covers_kernel_variant_slab_and_split():
+    """cuda_conv enumerates which kernel runs a convolution as well as its parameters: the
+    resident-weights kernel (one CTA or a CTA pair, 16- or 32-channel slabs) and the im2col
+    kernels (tiles, epilogue, cluster split-K); every sample maps one to one."""
+    from xtc_b200 import configs
+
+    graph = configs.build("c3").graph
+    strat = Strategies.create("cuda_conv", graph)
+    assert strat.node_name == "conv"
+    space = list(strat.exhaustive())
+    assert len(space) == len({tuple(s) for s in space}) > 100
+    assert {s[0] for s in space} == {1, 2}
+    resident = [s for s in space if s[0] == 2]
+    assert {(s[1], s[3]) for s in resident} == {(128, 16), (128, 32), (256, 32)}
+    assert {s[6] for s in space if s[0] == 1} == {1, 2, 4, 8}
+    for s in space:
+        assert strat.is_legal(s)
+        sch = Backend(graph).get_scheduler(strict=True)
+        strat.generate(sch, s)
+        cfg = sch.schedule().node_configs()["conv"]
+        assert cfg.get("variant", 0) == (2 if s[0] == 2 else 0)
+        assert (cfg["tile_m"], cfg["tile_k"], cfg.get("stages", 0)) == (s[1], s[3], s[4])
+        assert cfg.get("split_k", 1) == s[6] and cfg.get("epilogue", 0) == (2 if s[5] else 0)
+        if s[0] == 1:
+            assert cfg["tile_n"] == s[2]
+    # two 32-channel halo stages fit next to the 147 KB filter bank of this layer, not three
+    assert strat.is_legal([2, 128, 64, 32, 2, 0, 1]) and not strat.is_legal([2, 128, 64, 32, 3, 0, 1])
+    assert strat.default_schedule(2) == [2, 128, 64, 32, 0, 0, 1]
+    # a strided layer, or a bank too large to keep on chip, has only the im2col kernels
+    strided = Strategies.create("cuda_conv", conv2d_graph(1, 28, 28, 128, 3, 3, 64, 2, 2))
+    assert {s[0] for s in strided.exhaustive()} == {1} and strided.default_schedule(3)[0] == 1
+    big = Strategies.create("cuda_conv", conv2d_graph(1, 14, 14, 256, 3, 3, 256, 1, 1))
+    assert all(s[0] == 1 for s in big.exhaustive())
+    half = Strategies.create("cuda_conv", conv2d_graph(1, 28, 28, 128, 3, 3, 64, 1, 1))
+    assert {(s[1], s[3]) for s in half.exhaustive() if s[0] == 2} >= {(256, 32)}
+    with pytest.raises(ValueError):
+        Strategies.create("cuda_conv", matmul_graph(128, 128, 128))
+
+
+def test_named_operations_of_the_reference_tables():
+    """--op-name serves the reference's benchmark layers (artifacts/operations.py,
+    schedules/ttile/prob_sizes.py) under their names, dims then stride parameters."""
+    from xtc_b200 import artifacts
+
+    assert artifacts.operation_dims("conv2d", "ResNet18_02") == [1, 56, 56, 64, 3, 3, 64, 1, 1]
+    assert artifacts.operation_dims("conv2d", "resnet18_01") == [1, 224, 224, 64, 7, 7, 3, 2, 2]
+    assert artifacts.operation_dims("conv2d", "MobilNet_08") == [1, 14, 14, 512, 3, 3, 512, 2, 2]
+    assert artifacts.operation_dims("conv2d", "Yolo9000_23") == [1, 17, 17, 28272, 1, 1, 1024, 1, 1]
+    assert artifacts.operation_dims("matmul", "Gemma27B_FC") == [4608, 36864, 4608]
+    assert artifacts.get_operation("conv2d", "AlexNet_00")["params"] == {"SH": 4, "SW": 4}
+    names = dict.fromkeys(n for _, n in artifacts.list_operations("conv2d"))
+    assert len(names) >= 49 and len(artifacts.list_operations("matmul")) >= 27
+    exp = Exploration(ExplorationConfig(operator="conv2d", op_name="ResNet18_02", peak_flops=1e15))
+    assert exp.fma_count() == 56 * 56 * 64 * 9 * 64 and exp.strategy.name == "cuda_conv"
+    with pytest.raises(ValueError):
+        artifacts.get_operation("conv2d", "ResNet18_99")
+
+
 def test_exploration_csv_and_resume(tmp_path, monkeypatch):
     out = tmp_path / "res.csv"
     cfg = ExplorationConfig(operator="matmul", dims=[512, 512, 512], search="random", trials=6,

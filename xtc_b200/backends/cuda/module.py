@@ -226,6 +226,45 @@ class CudaEvaluator:
             return 1e-5, 1e-5 * float(np.max(np.abs(ref))) if ref.size else 0.0
         return 1e-2, 1e-2 * float(np.max(np.abs(ref))) if ref.size else 0.0
 
+    def _read_counters(self, handle: "PlanHandle", pointers: list[int]) -> tuple[list[float], str]:
+        """``repeat x len(pmu_counters)`` values, each a counter summed over the kernels of
+        ``number`` runs and divided by ``number`` (the layout and the division of
+        ``csrcs/runtimes/host/evaluate_perf.c:104-116``).  Entries that cannot be read are -1
+        and the returned message says why: names without the ``gpu.`` prefix are host CPU
+        events, which a GPU run does not have; ``gpu.`` names go to the CUPTI range profiler."""
+        from ...runtimes import counters as gc
+
+        dev = self._device
+        names = list(self._pmu_counters)
+        number = max(int(self._number), 1)
+        width = len(names)
+        results = [-1.0] * (self._repeat * width)
+        positions, metrics = gc.split_counter_names(names)
+        notes = []
+        host_only = [n for i, n in enumerate(names) if i not in positions]
+        if host_only:
+            notes.append(f"host CPU counters are not collected for a GPU run: {host_only}")
+        handle.run(pointers)  # untimed warm-up, as the timing loop does
+        dev.synchronize()
+        if metrics:
+            handle.set_graph_mode(False)  # plain launches inside the profiled range
+            session = None
+            try:
+                session = gc.GpuCounters(metrics)
+                for r in range(self._repeat):
+                    values = session.measure(
+                        lambda: [handle.run(pointers) for _ in range(number)], dev.synchronize)
+                    for pos, value in zip(positions, values):
+                        results[r * width + pos] = value / number
+            except gc.CountersError as e:
+                notes.append(str(e))
+            finally:
+                if session is not None:
+                    session.close()
+        if dev.status() != 0:
+            raise capi.XtcCudaError(capi.ERR_DEVICE_TIMEOUT, "a kernel's bounded wait gave up")
+        return results, "; ".join(notes)
+
     def _host_parameters(self) -> tuple[list[Any], list[Any]]:
         """(inputs, outputs) as NumPy arrays or device-resident NDArrays."""
         if self._parameters is None:
@@ -297,13 +336,9 @@ class CudaEvaluator:
                     if not np.allclose(ref, got, rtol=rtol, atol=atol):
                         return ([], 1, "Error in validation: outputs differ")
 
+            message = ""
             if self._pmu_counters:
-                # Hardware counters need a profiler attached to the process; without one
-                # every counter reads as unavailable, which the reference reports as -1
-                # (csrcs/runtimes/host/evaluate_perf.c:110-113).
-                handle.run(pointers)
-                dev.synchronize()
-                results = [-1.0] * (self._repeat * len(self._pmu_counters))
+                results, message = self._read_counters(handle, pointers)
             else:
                 results = handle.evaluate(pointers, self._repeat, self._number, self._min_repeat_ms)
 
@@ -311,7 +346,7 @@ class CudaEvaluator:
                 for arr, got in zip(outs, read_outputs()):
                     if isinstance(arr, np.ndarray):
                         np.copyto(arr, got.reshape(arr.shape))
-            return (results, 0, "")
+            return (results, 0, message)
         except capi.XtcCudaError as e:
             return ([], 1, f"Error in execution: {e}")
         finally:

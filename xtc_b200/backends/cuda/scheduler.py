@@ -16,7 +16,9 @@ mapping side is new: for a contraction node (matmul / conv2d)
   fuse_producer_at(_, idx)                                    -> fold the transpose producing
                                                                  operand idx into the GEMM
   split(k, {n segments})   matmul reduction cut into segments -> split-K over n CTAs per tile
-  pack_at(_, 1)            conv2d filter bank packed on chip  -> resident weights + halo tiles
+                           (conv2d: split(c, ...), the im2col kernels)
+  pack_at(_, 1)            conv2d filter bank packed on chip  -> resident weights + halo tiles;
+                           the first tile of c is then the channel slab of a stage (16 or 32)
   tile rows 256                                               -> CTA pairs (two SMs per MMA)
 
 Values the kernels do not implement are snapped to the nearest legal value
@@ -35,6 +37,7 @@ DEFAULT_ROOT = "."
 LEGAL_TILE_M = (128, 256)
 LEGAL_TILE_N = (64, 128, 256)
 LEGAL_TILE_K = (32, 64)
+LEGAL_SLAB = (16, 32)  # channels per stage of the resident-weights convolution
 MAX_STAGES = 8
 
 
@@ -212,6 +215,10 @@ class CudaNodeScheduler:
                 raise ScheduleError(f"{self.node_name}: {what}={value} is not one of {legal}")
             return min(legal, key=lambda v: (abs(v - value), -v))
 
+        # pack_at(_, 1) on a conv2d: keep operand 1 (the filter bank) packed in shared memory
+        # for the whole kernel -> the resident-weights / halo-tile convolution, whose
+        # pipeline stage is a slab of 16 or 32 channels
+        resident = self.op_name == "conv2d" and any(1 in idx for idx in self.packed_buffers.values())
         _, tm = first_tile(row)
         _, tn = first_tile(col)
         kname, tk = first_tile(red)
@@ -220,7 +227,8 @@ class CudaNodeScheduler:
         if tn is not None:
             cfg["tile_n"] = snap(tn, LEGAL_TILE_N, "CTA tile columns")
         if tk is not None:
-            cfg["tile_k"] = snap(tk, LEGAL_TILE_K, "K per stage")
+            cfg["tile_k"] = (snap(tk, LEGAL_SLAB, "channels per stage") if resident
+                             else snap(tk, LEGAL_TILE_K, "K per stage"))
         if kname is not None and kname in self.unrolling:
             u = self.unrolling[kname]
             if 2 <= u <= MAX_STAGES:
@@ -234,9 +242,11 @@ class CudaNodeScheduler:
         if self.op_name == "matmul" and red in self.splits and len(self.splits[red]) > 1:
             # split(k, {...}): the reduction cut into segments that run concurrently
             cfg["split_k"] = len(self.splits[red])
-        if self.op_name == "conv2d" and any(1 in idx for idx in self.packed_buffers.values()):
-            # pack_at(_, 1): keep operand 1 (the filter bank) packed in shared memory for
-            # the whole kernel -> the resident-weights / halo-tile convolution
+        if self.op_name == "conv2d" and red in self.splits and len(self.splits[red]) > 1:
+            # split(c, {...}) on a conv2d: the reduction (taps x channels) shared by that many
+            # CTAs of a thread-block cluster
+            cfg["split_k"] = len(self.splits[red])
+        if resident:
             cfg["variant"] = 2
         return cfg
 
@@ -304,6 +314,8 @@ class CudaScheduler:
     graph has one, because that is the node whose kernel has parameters.
     """
 
+    node_scheduler = CudaNodeScheduler  # the per-node recorder (a subclass may map differently)
+
     def __init__(self, backend: Any, nodes: list[str] | None = None,
                  default_node: str | None = None, strict: bool = False) -> None:
         self._backend = backend
@@ -315,8 +327,8 @@ class CudaScheduler:
                 continue
             op = node.operation
             self._node_schedulers.append(
-                CudaNodeScheduler(node.name, f"__xtc_id_{node.name}_", op.name,
-                                  {k: int(v) for k, v in op.dims.items()}))
+                self.node_scheduler(node.name, f"__xtc_id_{node.name}_", op.name,
+                                    {k: int(v) for k, v in op.dims.items()}))
         if default_node is not None:
             cands = [s for s in self._node_schedulers if s.node_name == default_node]
             assert cands, f"default_node {default_node!r} is not a node of the graph"

@@ -17,6 +17,10 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC_DIR = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libxtc_cuda.so"
+# GPU hardware counters (CUPTI range profiler): a library of its own, so that the kernel
+# library does not depend on CUPTI (include/xtc_cuda_counters.h)
+COUNTERS_SRC = CSRC_DIR / "counters" / "cupti_counters.cpp"
+COUNTERS_LIB_PATH = LIB_DIR / "libxtc_cuda_counters.so"
 INCLUDE_DIR = PKG_DIR.parent / "include"
 
 NVCC_FLAGS = [
@@ -57,8 +61,36 @@ def is_stale() -> bool:
     return any(p.stat().st_mtime > built for p in _deps())
 
 
+def build_counters(force: bool = False) -> Path | None:
+    """Compile the CUPTI counters library.  Returns None (with a note on stderr) when this
+    CUDA installation ships no CUPTI range-profiler headers; counters are then unavailable
+    and the evaluator says so."""
+    nvcc = find_nvcc()
+    cuda_root = Path(nvcc).resolve().parent.parent
+    include = next((d for d in (cuda_root / "include", cuda_root / "extras" / "CUPTI" / "include")
+                    if (d / "cupti_range_profiler.h").exists()), None)
+    libdir = next((d for d in (cuda_root / "lib64", cuda_root / "extras" / "CUPTI" / "lib64")
+                   if (d / "libcupti.so").exists()), None)
+    if include is None or libdir is None:
+        sys.stderr.write("CUPTI range profiler not found: libxtc_cuda_counters.so not built\n")
+        return None
+    deps = [COUNTERS_SRC, INCLUDE_DIR / "xtc_cuda_counters.h"]
+    if (not force and COUNTERS_LIB_PATH.exists()
+            and COUNTERS_LIB_PATH.stat().st_mtime > max(p.stat().st_mtime for p in deps)):
+        return COUNTERS_LIB_PATH
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    cmd = [nvcc, "-shared", "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-I", str(include),
+           "-I", str(cuda_root / "include"), str(COUNTERS_SRC), "-o", str(COUNTERS_LIB_PATH),
+           f"-L{libdir}", "-lcupti", "-ldl", "-Xlinker", f"-rpath={libdir}", "--cudart", "none"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"building libxtc_cuda_counters.so failed:\n{proc.stdout}{proc.stderr}")
+    return COUNTERS_LIB_PATH
+
+
 def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -> Path:
     """Compile every .cu under csrc/ into objects (in parallel) and link the .so."""
+    build_counters(force)
     if not force and not is_stale():
         return LIB_PATH
     nvcc = find_nvcc()

@@ -105,6 +105,11 @@ SIGNATURES: dict[str, tuple] = {
     "xtc_cuda_stream_destroy": (c_int, [c_void_p]),
     "xtc_cuda_stream_synchronize": (c_int, [c_void_p]),
     "xtc_cuda_device_synchronize": (c_int, []),
+    "xtc_cuda_event_create": (c_int, [POINTER(c_void_p)]),
+    "xtc_cuda_event_destroy": (c_int, [c_void_p]),
+    "xtc_cuda_event_record": (c_int, [c_void_p, c_void_p]),
+    "xtc_cuda_event_synchronize": (c_int, [c_void_p]),
+    "xtc_cuda_stream_wait_event": (c_int, [c_void_p, c_void_p]),
     "xtc_cuda_device_status": (c_int, [POINTER(c_int)]),
     "xtc_cuda_mem_info": (c_int, [POINTER(c_size_t), POINTER(c_size_t)]),
     "xtc_cuda_selftest_bounded_wait": (c_int, [c_int, c_void_p]),

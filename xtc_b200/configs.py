@@ -23,6 +23,8 @@ import numpy as np
 from .graphs.xtc import op as O
 
 NAMES = ("c1", "c2", "c3", "c4", "c4a", "c5")
+# the standalone elementwise kernels on 512 MiB tensors (bandwidth measurements only)
+MOVEMENT_NAMES = ("relu512", "pad512")
 
 
 @dataclass
@@ -72,7 +74,30 @@ def inputs(name: str, scale: int = 1, batch: int | None = None) -> list[np.ndarr
         k = _scaled(8192, s)
         return [rng.uniform(-1, 1, (_scaled(65536, s), k)).astype(np.float32),
                 rng.normal(0, 1 / np.sqrt(8192), (k, k)).astype(np.float32)]
+    if name == "relu512":
+        rng = np.random.default_rng(5)
+        return [rng.uniform(-1, 1, (_scaled(32768, s), 4096)).astype(np.float32)]
+    if name == "pad512":
+        rng = np.random.default_rng(6)
+        return [rng.uniform(-1, 1, (_scaled(16, s), 256, 512, 64)).astype(np.float32)]
     raise KeyError(name)
+
+
+def input_rows(name: str, lo: int, hi: int) -> list[np.ndarray]:
+    """Rows [lo, hi) of the first input of a row-sharded configuration (c5) plus its
+    replicated second input, bit-identical to slicing ``inputs(name)`` but without drawing
+    the other rows: the generator is advanced past them (one draw per uniform element)."""
+    if name != "c5":
+        raise KeyError(f"{name} is not row-sharded")
+    k, m = 8192, 65536
+    assert 0 <= lo <= hi <= m
+    rng = np.random.default_rng(4)
+    rng.bit_generator.advance(lo * k)
+    a = rng.uniform(-1, 1, (hi - lo, k)).astype(np.float32)
+    rng = np.random.default_rng(4)
+    rng.bit_generator.advance(m * k)
+    b = rng.normal(0, 1 / np.sqrt(8192), (k, k)).astype(np.float32)
+    return [a, b]
 
 
 def _gemm_schedule(tile_n: int, tile_k: int, stages: int = 0, tma_store: bool = True,
@@ -164,6 +189,22 @@ def build(name: str, scale: int = 1, batch: int | None = None, rows: int | None 
         with O.graph(name="c4a_transpose") as gb:
             O.transpose(x, axes=(1, 0), name="xt")
         return Config(name, gb.graph, "xt", [(n, n)], (n, n), 0, 8 * n * n, "hbm", "",
+                      lambda sch: None)
+    if name == "relu512":  # a relu with no producer to fuse into: the standalone kernel
+        shape = (_scaled(32768, s), 4096)
+        x = O.tensor(shape, "float32", name="X")
+        with O.graph(name="relu512") as gb:
+            O.relu(x, name="relu")
+        n = shape[0] * shape[1]
+        return Config(name, gb.graph, "relu", [shape], shape, 0, 8 * n, "hbm", "", lambda sch: None)
+    if name == "pad512":  # a pad with no convolution to fuse into: the standalone kernel
+        shape = (_scaled(16, s), 256, 512, 64)
+        x = O.tensor(shape, "float32", name="X")
+        with O.graph(name="pad512") as gb:
+            O.pad(x, padding={1: (1, 1), 2: (1, 1)}, constant_value=0.0, name="pad")
+        out = (shape[0], 258, 514, 64)
+        return Config(name, gb.graph, "pad", [shape], out, 0,
+                      4 * (shape[0] * 256 * 512 * 64 + out[0] * 258 * 514 * 64), "hbm", "",
                       lambda sch: None)
     if name == "c5":
         k = _scaled(8192, s)

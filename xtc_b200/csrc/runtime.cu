@@ -202,6 +202,32 @@ extern "C" int xtc_cuda_stream_synchronize(void* stream) {
   XTC_CUDA_CHECK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   return XTC_CUDA_OK;
 }
+extern "C" int xtc_cuda_event_create(void** event) {
+  XTC_REQUIRE(event != nullptr, "event_create: NULL");
+  cudaEvent_t e;
+  XTC_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  *event = e;
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_event_destroy(void* event) {
+  if (event) XTC_CUDA_CHECK(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_event_record(void* event, void* stream) {
+  XTC_REQUIRE(event != nullptr, "event_record: NULL event");
+  XTC_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_event_synchronize(void* event) {
+  XTC_REQUIRE(event != nullptr, "event_synchronize: NULL event");
+  XTC_CUDA_CHECK(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
+  return XTC_CUDA_OK;
+}
+extern "C" int xtc_cuda_stream_wait_event(void* stream, void* event) {
+  XTC_REQUIRE(event != nullptr, "stream_wait_event: NULL event");
+  XTC_CUDA_CHECK(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+  return XTC_CUDA_OK;
+}
 extern "C" int xtc_cuda_device_synchronize(void) {
   XTC_CUDA_CHECK(cudaDeviceSynchronize());
   return XTC_CUDA_OK;

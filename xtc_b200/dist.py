@@ -168,6 +168,15 @@ class PeerStoreMatmul:
         self.extras = (ctypes.c_void_p * max(len(extras), 1))(*extras)
         self.n_extra = len(extras)
         self.c_block = self.c_local.value + offset
+        # the workspace a plan would give this GEMM (split tail of the CTA-pair kernel), cleared once
+        ws = ctypes.c_size_t(0)
+        capi.check(self.lib.xtc_cuda_gemm_workspace_bytes(self.rows, n, k, 0, ctypes.byref(self.cfg),
+                                                          ctypes.byref(ws)))
+        self.ws_bytes = ws.value
+        self.workspace = device.memory_allocate(ws.value) if ws.value else None
+        if self.workspace is not None:
+            device.memory_fill_zero(self.workspace, ws.value)
+            device.synchronize()
         self._flag = torch.zeros(1, device="cuda")
         self._dist = dist
 
@@ -186,7 +195,8 @@ class PeerStoreMatmul:
 
         rc = self.lib.xtc_cuda_gemm_f32_bcast(
             self.a_ptr, self.b_ptr, self.c_block, self.extras, self.n_extra, self.rows, self.n,
-            self.k, self.k, self.n, self.n, 0, 0.0, ctypes_byref(self.cfg), None, 0, stream)
+            self.k, self.k, self.n, self.n, 0, 0.0, ctypes_byref(self.cfg), self.workspace,
+            self.ws_bytes, stream)
         if rc:
             capi.check(rc)
         if self.world > 1:
@@ -194,6 +204,10 @@ class PeerStoreMatmul:
             # follow the GEMM on the GEMM's own stream, whatever torch's current stream is
             with self._on_stream(stream):
                 self._dist.all_reduce(self._flag, group=self.group)
+
+    def host_loop(self) -> "ShardedHostLoop":
+        """Overlapped executor of this step on host batches (see ShardedHostLoop)."""
+        return ShardedHostLoop(self)
 
     def result(self) -> Any:
         """The full C of this rank as a NumPy array (synchronises)."""
@@ -215,6 +229,78 @@ class PeerStoreMatmul:
         if self.c_local is not None:
             self.device.memory_free(self.c_local)
             self.c_local = None
+        if self.workspace is not None:
+            self.device.memory_free(self.workspace)
+            self.workspace = None
+
+
+class ShardedHostLoop:
+    """Runs a PeerStoreMatmul step on a sequence of host batches.
+
+    ``submit(host_a, host_c)`` copies this rank's block of A in from host memory, runs the
+    fused GEMM + exchange, and copies this rank's block of C back out; the copy-in of step
+    i+1 and the copy-out of step i run side by side on streams of their own (the host link
+    is full duplex) while the step itself occupies a third.  One device A block and one C
+    are shared by all steps, so a step's GEMM waits for the previous step's copy-out and a
+    copy-in waits for the previous GEMM.  ``wait()`` returns when every submitted step has
+    delivered, and raises if a kernel reported a bounded-wait timeout.  Host arrays should
+    be page-locked (``xtc_cuda_host_alloc``) for the copies to overlap.  Every rank must
+    submit the same number of steps (each step ends in a collective barrier).
+    """
+
+    def __init__(self, op: "PeerStoreMatmul") -> None:
+        import ctypes
+
+        from . import capi
+
+        self.op, self.lib = op, op.lib
+        self._check = capi.check
+
+        def make(fn: Any) -> Any:
+            h = ctypes.c_void_p()
+            capi.check(fn(ctypes.byref(h)))
+            return h
+
+        self.s_in, self.s_run, self.s_out = (make(self.lib.xtc_cuda_stream_create) for _ in range(3))
+        self.ev_in, self.ev_run, self.ev_out = (make(self.lib.xtc_cuda_event_create) for _ in range(3))
+        self.submitted = 0
+        self.a_bytes = op.rows * op.k * 4
+        self.c_bytes = op.rows * op.n * 4
+
+    def submit(self, host_a: int, host_c: int) -> None:
+        """host_a / host_c: addresses of this rank's [rows, K] block of A and [rows, N] block of C."""
+        lib, ck = self.lib, self._check
+        if self.submitted:
+            ck(lib.xtc_cuda_stream_wait_event(self.s_in, self.ev_run))   # A is free again
+        ck(lib.xtc_cuda_memcpy_h2d(self.op.a_ptr, host_a, self.a_bytes, self.s_in))
+        ck(lib.xtc_cuda_event_record(self.ev_in, self.s_in))
+        ck(lib.xtc_cuda_stream_wait_event(self.s_run, self.ev_in))
+        if self.submitted:
+            ck(lib.xtc_cuda_stream_wait_event(self.s_run, self.ev_out))  # C block has been read out
+        self.op.step(self.s_run.value)
+        ck(lib.xtc_cuda_event_record(self.ev_run, self.s_run))
+        ck(lib.xtc_cuda_stream_wait_event(self.s_out, self.ev_run))
+        ck(lib.xtc_cuda_memcpy_d2h(host_c, self.op.c_block, self.c_bytes, self.s_out))
+        ck(lib.xtc_cuda_event_record(self.ev_out, self.s_out))
+        self.submitted += 1
+
+    def wait(self) -> None:
+        from . import capi
+
+        if self.submitted:
+            self._check(self.lib.xtc_cuda_event_synchronize(self.ev_out))
+        if self.op.device.status() != 0:
+            raise capi.XtcCudaError(capi.ERR_DEVICE_TIMEOUT, "a kernel's bounded wait gave up")
+
+    def close(self) -> None:
+        if self.s_in is None:
+            return
+        self.op.device.synchronize()
+        for ev in (self.ev_in, self.ev_run, self.ev_out):
+            self.lib.xtc_cuda_event_destroy(ev)
+        for st in (self.s_in, self.s_run, self.s_out):
+            self.lib.xtc_cuda_stream_destroy(st)
+        self.s_in = self.s_run = self.s_out = None
 
 
 def ctypes_byref(obj: Any) -> Any:

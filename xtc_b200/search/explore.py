@@ -49,7 +49,7 @@ OPERATORS = {
     "matmul_relu": {"dims": ["i", "j", "k"], "default_dims": [4096, 4096, 4096],
                     "default_strategy": "cuda_gemm"},
     "conv2d": {"dims": ["n", "h", "w", "f", "r", "s", "c", "SH", "SW"],
-               "default_dims": [1, 112, 112, 64, 7, 7, 4, 2, 2], "default_strategy": "cuda_gemm"},
+               "default_dims": [1, 112, 112, 64, 7, 7, 4, 2, 2], "default_strategy": "cuda_conv"},
 }
 
 
@@ -99,6 +99,11 @@ class ExplorationConfig:
     peak_flops: float | None = None  # FMA/s; default: probe the device
     precision: str = "tf32"
     device: int = 0
+    # Backend class to explore with: Backend(graph) with get_scheduler / get_compiler, the
+    # plug-in point of the reference's driver (search/explore.py:262-268).  None = the CUDA
+    # backend; `backend_name` is what the result rows carry.
+    backend: Any = None
+    backend_name: str = "cuda"
     explore_dir: str | None = None
     save_temps: bool = False
     strategy_options: dict = field(default_factory=dict)
@@ -117,8 +122,7 @@ class Exploration:
             if config.op_name:
                 from .. import artifacts
 
-                named = artifacts.get_operation(config.operator, config.op_name)["dims"]
-                dims = [named[d] for d in spec["dims"]]
+                dims = artifacts.operation_dims(config.operator, config.op_name)
             assert len(dims) == len(spec["dims"]), (
                 f"{config.operator} takes dims {spec['dims']}, got {dims}")
             if config.operator == "conv2d":
@@ -155,7 +159,9 @@ class Exploration:
 
     # -- one sample -------------------------------------------------------------------
     def compile_one(self, ident: str, sample: list[int], explore_dir: str):
-        from ..backends.cuda import Backend
+        Backend = self.config.backend
+        if Backend is None:
+            from ..backends.cuda import Backend
 
         impl = Backend(self.graph)
         scheduler = impl.get_scheduler(strict=True)
@@ -174,11 +180,11 @@ class Exploration:
         results, code, msg = evaluator.evaluate()
         if code != 0:
             logger.error("error evaluating %s: %s", sample, msg)
-            return (sample, code, float("inf"), "cuda")
+            return (sample, code, float("inf"), cfg.backend_name)
         path = Path(module.file_name)
         if not cfg.save_temps and path.exists():
             path.unlink()
-        return (sample, 0, min(results), "cuda")
+        return (sample, 0, min(results), cfg.backend_name)
 
     # -- the search ---------------------------------------------------------------------
     @staticmethod
@@ -239,7 +245,7 @@ class Exploration:
                     result = self.evaluate_one(fut.result(), sample)
                 except Exception as exc:  # an illegal sample is a failed result, not the end
                     logger.error("error compiling %s: %s", sample, exc)
-                    result = (list(sample), 1, float("inf"), "cuda")
+                    result = (list(sample), 1, float("inf"), self.config.backend_name)
                 out.append(result)
                 for cb in callbacks:
                     cb(result)
@@ -283,7 +289,7 @@ class Exploration:
             logger.info("%d samples in %.1f s (%.3f s/sample)", done, elapsed, elapsed / done)
         if ok:
             best = min(ok, key=lambda r: r[2])
-            print(f"Schedule: cuda: {best[0]}: time: {best[2] * 1e3:.4f} msecs, "
+            print(f"Schedule: {cfg.backend_name}: {best[0]}: time: {best[2] * 1e3:.4f} msecs, "
                   f"peak perf: {100 * self.peak_time() / best[2]:.2f}%")
         return self.results
 

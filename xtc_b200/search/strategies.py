@@ -141,10 +141,113 @@ class StrategyCudaGemm:
             target.vectorize([f"{col}1"])
 
 
+class StrategyCudaConv:
+    """The convolution kernels' whole space: which kernel, then that kernel's parameters.
+
+    Sample ``[variant, tile_m, tile_n, tile_k, stages, tma_store, split_k]``:
+      variant 2  resident weights + halo tiles (stride 1, filter bank fits in shared memory):
+                 tile_m = output positions per tile (128 = one CTA, 256 = a CTA pair with
+                 half a filter bank each), tile_k = channels per pipeline stage (16 or 32,
+                 32 only for pairs), stages; tile_n, tma_store and split_k do not apply
+      variant 1  implicit GEMM, one im2col fetch per filter tap: the GEMM kernels' tile_m /
+                 tile_n / tile_k / stages / epilogue, and split_k = 2, 4, 8 pieces of the
+                 reduction in one thread-block cluster (one CTA per tile, tile_n <= 128)
+    """
+
+    name = "cuda_conv"
+    sample_names = ["variant", "tile_m", "tile_n", "tile_k", "stages", "tma_store", "split_k"]
+
+    def __init__(self, graph: Any, **_ignored: Any) -> None:
+        self._graph = graph
+        self._node = contraction_node(graph)
+        self._op = self._node.operation
+        if self._op.name != "conv2d":
+            raise ValueError("cuda_conv schedules a conv2d node")
+        d = {k: int(v) for k, v in self._op.dims.items()}
+        self._b, self._h, self._w, self._f, self._r, self._s, self._c = d.values()
+        stride = self._op.attrs.get("stride", (1, 1))
+        stride = (stride, stride) if isinstance(stride, int) else tuple(stride)
+        self._stride = (int(stride[0]), int(stride[-1]))
+        self._in_w = (self._w - 1) * self._stride[1] + self._s  # width of the (padded) input
+        self._gemm = StrategyCudaGemm(graph)
+
+    graph = property(lambda self: self._graph)
+    node_name = property(lambda self: self._node.name)
+
+    def resident_stages(self, tile_m: int, slab: int) -> int:
+        """Halo stages that fit next to the filter bank (0 = this layer cannot run resident)."""
+        if self._stride != (1, 1) or self._f > 256 or (tile_m == 256 and slab != 32):
+            return 0
+        bn = 64 if self._f <= 64 else 128 if self._f <= 128 else 256
+        run = 128 + (self._r - 1) * self._in_w + self._s - 1  # halo pixels of a 128-position tile
+        if run > 1024:
+            return 0
+        stage = -(-run * slab * 4 // 1024) * 1024
+        bank = self._r * self._s * -(-self._c // 32) * (bn // 2 if tile_m == 256 else bn) * 128
+        return max(min((SMEM_BUDGET - bank) // stage, 8), 0) if SMEM_BUDGET - bank >= 2 * stage else 0
+
+    def is_legal(self, sample: list[int]) -> bool:
+        variant, tm, tn, tk, st, tma, split = sample
+        if variant == 2:
+            fit = self.resident_stages(tm, tk) if tm in (128, 256) and tk in (16, 32) else 0
+            return (fit >= 2 and (st == 0 or 2 <= st <= fit) and tma == 0 and split == 1
+                    and tn == (64 if self._f <= 64 else 128 if self._f <= 128 else 256))
+        if variant != 1 or self._c % 4 or self._f % 4:
+            return False
+        if not self._gemm.is_legal([tm, tn, tk, st, tma, 1]) or split not in (1, 2, 4, 8):
+            return False
+        k_blocks = self._r * self._s * -(-self._c // tk)
+        return split == 1 or (tm == 128 and tn <= 128 and split <= k_blocks)
+
+    def exhaustive(self):
+        g = self._gemm
+        tn_res = 64 if self._f <= 64 else 128 if self._f <= 128 else 256
+        for tm, slab, st in itertools.product((128, 256), (16, 32), (0, 2, 3, 4)):
+            s = [2, tm, tn_res, slab, st, 0, 1]
+            if self.is_legal(s):
+                yield s
+        for tm, tn, tk, st, tma, split in itertools.product(g.tile_m, g.tile_n, g.tile_k, g.stages,
+                                                            (0, 1), (1, 2, 4, 8)):
+            s = [1, tm, tn, tk, st, tma, split]
+            if self.is_legal(s):
+                yield s
+
+    def sample(self, num: int, seed: int | None = 0) -> list[list[int]]:
+        space = list(self.exhaustive())
+        random.Random(seed).shuffle(space)
+        return space[: max(num, 0)]
+
+    def default_schedule(self, opt_level: int = 2) -> list[int]:
+        resident = [2, 128, 64 if self._f <= 64 else 128 if self._f <= 128 else 256, 32, 0, 0, 1]
+        if opt_level >= 2 and self.is_legal(resident):
+            return resident
+        return [1, 128, 64 if self._f <= 64 else 128, 32, 2 if opt_level <= 0 else 0, 1, 1]
+
+    def generate(self, scheduler: Any, sample: list[int]) -> None:
+        variant, tm, tn, tk, st, tma, split = (int(v) for v in sample)
+        b, h, w, f, r, s, c = list(self._op.dims)
+        target = scheduler.node(self.node_name) if hasattr(scheduler, "node") else scheduler
+        if variant == 2:
+            target.pack_at(b, 1)  # the filter bank stays packed on chip
+        elif split > 1:
+            piece = -(-self._c // split)
+            target.split(c, {f"{c}_s{i}": i * piece for i in range(split)})
+        target.tile(w, {f"{w}1": tm})
+        if variant == 1:
+            target.tile(f, {f"{f}1": tn})
+        target.tile(c, {f"{c}1": tk})
+        target.parallelize([b, h, w])
+        if st:
+            target.unroll({f"{c}1": st})
+        if tma:
+            target.vectorize([f"{f}1"])
+
+
 class Strategies:
     """Name -> strategy registry (cf. ``search/strategies.py:1190-1283``)."""
 
-    _registry: dict[str, Callable[..., Any]] = {"cuda_gemm": StrategyCudaGemm}
+    _registry: dict[str, Callable[..., Any]] = {"cuda_gemm": StrategyCudaGemm,
+                                                 "cuda_conv": StrategyCudaConv}
 
     @classmethod
     def register(cls, name: str, factory: Callable[..., Any]) -> None:
