@@ -683,13 +683,16 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
                     chunk_handles[hi - lo] = PlanHandle(
                         configs.compile_config(ccfg, precision=args.precision).plan, dev)
         peer_op = None
-        if args.exchange == "peer":
+        if args.exchange != "nccl":
             from xtc_b200.dist import PeerStoreMatmul
             gemm_cfg = dict(module.plan.steps[-1].config)
             op = peer_op = PeerStoreMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
-                                           config=gemm_cfg)
-            sharding = (f"rows of A and C split over {world} ranks, B replicated; the GEMM epilogue "
-                        f"stores each C tile into every rank's C over NVLink (fused all-gather)"
+                                           config=gemm_cfg,
+                                           exchange={"peer": "peer", "multimem": "multimem"}.get(args.exchange, "auto"))
+            how = ("one multicast store per vector through an NVLink multicast object (NVLS)"
+                   if peer_op.exchange == "multimem" else "one 128-bit store per peer")
+            sharding = (f"rows of A and C split over {world} ranks, B replicated; copier warps of the GEMM "
+                        f"write each C tile into every rank's C over NVLink, {how} (fused all-gather)"
                         if world > 1 else "one rank holds all rows (no exchange)")
         else:
             op = RowShardedMatmul(c_full, world, rank, compute, chunks=args.chunks)
@@ -699,7 +702,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         local_cfg = cfg
         h2d = a_blk.numel() * 4
         d2h = rows * N * 4
-        launches = 1 if (args.chunks <= 1 or args.exchange == "peer") else args.chunks
+        launches = 1 if (args.chunks <= 1 or args.exchange != "nccl") else args.chunks
         exchange_bytes = rows * N * 4 * (world - 1)  # the rank's block of C, to every other rank
     elif workload == "c3":
         sh = BatchSharded(32, world, rank)
@@ -840,7 +843,8 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
             "dtype": "tf32" if args.precision == "tf32" else args.precision, "data": "synthetic",
             "config": {"workload": workload_name(workload), "sharding": sharding,
                        "chunks": args.chunks,
-                       "exchange": (args.exchange if world > 1 else "none") if workload == "c5" else "none",
+                       "exchange": ((peer_op.exchange if peer_op is not None else "nccl") if world > 1
+                                    else "none") if workload == "c5" else "none",
                        "kernel_config": module.plan.steps[-1].config,
                        "inputs": "the configuration's seeded inputs (each rank draws its own rows)",
                        "l2": "per-rank operands (>= 0.5 GB) exceed the 126 MB L2"
@@ -899,8 +903,10 @@ def main() -> None:
     ap.add_argument("--unfused-transpose", action="store_true",
                     help="c4: run the transpose as its own kernel instead of reading A transposed")
     ap.add_argument("--chunks", type=int, default=1, help="row chunks overlapped with the exchange (N>1)")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="c5 at N>1: fused peer stores in the GEMM epilogue, or an NCCL all-gather")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "multimem", "peer", "nccl"],
+                    help="c5 at N>1: fused all-gather by NVLink multicast stores (multimem), by one store "
+                         "per peer (peer), whichever of the two the box offers (auto), or GEMM followed "
+                         "by an NCCL all-gather (nccl)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-e2e", action="store_true",

@@ -113,7 +113,9 @@ typedef struct xtc_cuda_gemm_config {
   int32_t precision; /* XTC_CUDA_PRECISION_*                                      */
   int32_t epilogue;  /* 0 = default; 1 = direct global stores; 2 = TMA stores     */
   int32_t variant;   /* conv2d: 0 = auto; 1 = im2col fetch per filter tap;
-                        2 = resident weights + halo tiles (stride 1 only)          */
+                        2 = resident weights + halo tiles (stride 1 only);
+                        3 = the same with two filter taps per MMA (at most 64
+                        filters, filter rows of two taps or more)                 */
   int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off unless
                         the whole config is zero, when the library decides.  2, 4 or 8
                         pieces of a tile at most 128 columns wide, N a multiple of 4, C
@@ -162,6 +164,20 @@ int xtc_cuda_gemm_f32_bcast(const float* A, const float* B, float* C, float* con
                             int n_extra, int64_t M, int64_t N, int64_t K, int64_t lda,
                             int64_t ldb, int64_t ldc, int flags, float relu_threshold,
                             const xtc_cuda_gemm_config* cfg, void* workspace,
+                            size_t workspace_bytes, void* stream);
+/* The same fused all-gather through an NVLink multicast object (NVLS): every
+ * rank's full-size C is bound to one multicast object, mcast_C is this rank's row
+ * block seen through the multicast mapping (C is the same block through the
+ * rank's own unicast mapping), and the copier warps issue ONE multimem.st per
+ * 128-bit vector, which the NVSwitch writes into every bound GPU's memory (this
+ * GPU's too), instead of one store per peer.  CTA-pair kernel only (tile_m = 256 or
+ * 0), TF32 only.  Creating and binding the multicast object is the caller's job
+ * (xtc_b200.dist uses torch's symmetric-memory allocator); every rank must unbind
+ * before any rank exits.  Ordering against readers as for xtc_cuda_gemm_f32_bcast.
+ * No reference counterpart (same remark). */
+int xtc_cuda_gemm_f32_mcast(const float* A, const float* B, float* C, float* mcast_C, int64_t M,
+                            int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int flags,
+                            float relu_threshold, const xtc_cuda_gemm_config* cfg, void* workspace,
                             size_t workspace_bytes, void* stream);
 /* Share a device allocation (from xtc_cuda_malloc) with the other processes of
  * the box: export fills a 64-byte handle to send them; import maps the peer's

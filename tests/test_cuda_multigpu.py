@@ -122,6 +122,22 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         loop.close()
         op.close()
         assert dev.status() == 0
+        # ---- the same broadcast by NVLink multicast stores, where the box offers them ----
+        # (no rank may fail while its memory is bound to the multicast object: compare, unbind
+        # on every rank, and only then judge)
+        op = PeerStoreMatmul(dev, a_blk.data_ptr(), b_dev.data_ptr(), m, n, k, world, rank,
+                             config=pair_cfg, exchange="auto")
+        used = op.exchange
+        for _ in range(2):
+            op.step(stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        same = bool(np.array_equal(op.result(), single)) and dev.status() == 0
+        op.close()
+        verdict = torch.tensor([1.0 if same else 0.0], device="cuda")
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+        Path(out_dir, f"exchange{rank}").write_text(used)
+        assert verdict.item() == 1.0, f"{used}: a rank's C differs from the single-GPU product"
         Path(out_dir, f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()
@@ -134,3 +150,6 @@ def test_row_sharded_matmul_on_two_gpus(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+    used = {(tmp_path / f"exchange{r}").read_text() for r in range(world)}
+    assert len(used) == 1 and used <= {"multimem", "peer"}, used  # every rank took the same path
+    print("fused all-gather ran by", used.pop())

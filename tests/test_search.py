@@ -69,16 +69,17 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
     assert strat.node_name == "conv"
     space = list(strat.exhaustive())
     assert len(space) == len({tuple(s) for s in space}) > 100
-    assert {s[0] for s in space} == {1, 2}
+    assert {s[0] for s in space} == {1, 2, 3}
     resident = [s for s in space if s[0] == 2]
     assert {(s[1], s[3]) for s in resident} == {(128, 16), (128, 32), (256, 32)}
+    assert {(s[1], s[3]) for s in space if s[0] == 3} == {(128, 16), (128, 32)}  # two taps per MMA
     assert {s[6] for s in space if s[0] == 1} == {1, 2, 4, 8}
     for s in space:
         assert strat.is_legal(s)
         sch = Backend(graph).get_scheduler(strict=True)
         strat.generate(sch, s)
         cfg = sch.schedule().node_configs()["conv"]
-        assert cfg.get("variant", 0) == (2 if s[0] == 2 else 0)
+        assert cfg.get("variant", 0) == (s[0] if s[0] in (2, 3) else 0)
         assert (cfg["tile_m"], cfg["tile_k"], cfg.get("stages", 0)) == (s[1], s[3], s[4])
         assert cfg.get("split_k", 1) == s[6] and cfg.get("epilogue", 0) == (2 if s[5] else 0)
         if s[0] == 1:
@@ -193,6 +194,35 @@ def test_exhaustive_search_on_gpu(tmp_path):
     assert len(rows) == len(results)
     assert all(0 < float(r["peak"]) <= 1.5 for r in rows)
     assert exp.best() is not None
+
+
+@pytest.mark.gpu
+def test_conv_search_on_gpu_confirms_the_shipped_c3_schedule(tmp_path):
+    """Every resident-weights sample of c3 (one tap or two per MMA, one CTA or a pair, 16- or
+    32-channel slabs, every depth) and a draw of the im2col samples, measured: the schedule
+    the benchmark configuration ships must be the best of them, or within 3 % of it."""
+    from xtc_b200 import configs
+
+    cfg = configs.build("c3")
+    exp = Exploration(ExplorationConfig(graph=cfg.graph, strategy="cuda_conv", output=str(tmp_path / "c3.csv"),
+                                        repeat=3, number=20, min_repeat_ms=5,
+                                        explore_dir=str(tmp_path / "x")))
+    space = list(exp.strategy.exhaustive())
+    resident = [s for s in space if s[0] in (2, 3)]
+    im2col = [s for s in exp.strategy.sample(len(space), seed=3) if s[0] == 1][:16]
+    shipped = [2, 128, 64, 32, 0, 0, 1]
+    assert shipped in resident
+    sch = Backend(cfg.graph).get_scheduler(default_node=cfg.contraction)
+    cfg.schedule(sch)
+    shipped_cfg = sch.schedule().node_configs()[cfg.contraction]
+    ref = Backend(cfg.graph).get_scheduler(strict=True)
+    exp.strategy.generate(ref, shipped)
+    assert ref.schedule().node_configs()[cfg.contraction]["variant"] == shipped_cfg["variant"] == 2
+    results = exp.evaluate_batch(resident + im2col, str(tmp_path / "x"), exp.result_callbacks())
+    assert all(code == 0 for _, code, _, _ in results), [r for r in results if r[1]]
+    times = {tuple(s): t for s, _, t, _ in results}
+    best = min(times, key=times.get)
+    assert times[tuple(shipped)] <= 1.03 * times[best], (best, times[best], times[tuple(shipped)])
 
 
 @pytest.mark.gpu

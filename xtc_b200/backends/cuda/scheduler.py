@@ -18,7 +18,8 @@ mapping side is new: for a contraction node (matmul / conv2d)
   split(k, {n segments})   matmul reduction cut into segments -> split-K over n CTAs per tile
                            (conv2d: split(c, ...), the im2col kernels)
   pack_at(_, 1)            conv2d filter bank packed on chip  -> resident weights + halo tiles;
-                           the first tile of c is then the channel slab of a stage (16 or 32)
+                           the first tile of c is then the channel slab of a stage (16 or 32),
+                           tile(s, {s1: 2}) puts two neighbouring filter taps into one MMA
   tile rows 256                                               -> CTA pairs (two SMs per MMA)
 
 Values the kernels do not implement are snapped to the nearest legal value
@@ -248,6 +249,13 @@ class CudaNodeScheduler:
             cfg["split_k"] = len(self.splits[red])
         if resident:
             cfg["variant"] = 2
+            # tile(s, {s1: 2}): two neighbouring taps of a filter row per MMA
+            s_dim = self.dims[5]
+            s_tiles = list(self.tiles.get(s_dim, {}).values())
+            if s_tiles and s_tiles[0] == 2:
+                cfg["variant"] = 3
+            elif s_tiles and strict and s_tiles[0] != 1:
+                raise ScheduleError(f"{self.node_name}: taps per MMA = {s_tiles[0]} is not 1 or 2")
         return cfg
 
     def node_schedule(self, strict: bool = False) -> CudaNodeSchedule:

@@ -126,6 +126,11 @@ SIGNATURES: dict[str, tuple] = {
          c_int64, c_int64, c_int64, c_int, c_float, POINTER(GemmConfig), c_void_p, c_size_t,
          c_void_p],
     ),
+    "xtc_cuda_gemm_f32_mcast": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+         c_int64, c_int, c_float, POINTER(GemmConfig), c_void_p, c_size_t, c_void_p],
+    ),
     "xtc_cuda_ipc_export": (c_int, [c_void_p, c_void_p]),
     "xtc_cuda_ipc_import": (c_int, [c_void_p, POINTER(c_void_p)]),
     "xtc_cuda_ipc_release": (c_int, [c_void_p]),

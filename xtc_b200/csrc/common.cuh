@@ -365,6 +365,15 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t adesc, 
       : "memory");
 }
 
+// ---- NVLink multicast --------------------------------------------------------
+// One 128-bit store to a multicast address: the switch writes it to the same offset of every
+// GPU memory bound to the multicast object (this GPU's included).
+__device__ __forceinline__ void multimem_st_f4(float* mc_addr, float4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(v.x),
+               "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
 // ---- UMMA descriptors ------------------------------------------------------
 // Shared-memory matrix descriptor (64 bit): start address, leading/stride byte
 // offsets (all >> 4), descriptor version 1 (sm_100), swizzle mode in bits 61..63.

@@ -48,6 +48,19 @@
 
 namespace xtc {
 
+// Optional per-CTA event trace (clock64 stamps) for kernel studies: compiled in only with
+// -DXTC_TRACE, where the host sets g_halo_trace to a device buffer of
+// [CTA][role 0..3][XTC_TRACE_EVENTS] stamps.
+#ifdef XTC_TRACE
+#define XTC_TRACE_EVENTS 128
+static __device__ long long* g_halo_trace = nullptr;  // one translation unit includes this header
+#define XTC_TRACE_DECL(role) int _tn = 0; long long* _tb = g_halo_trace ? g_halo_trace + ((static_cast<size_t>(blockIdx.x) * 4 + (role)) * XTC_TRACE_EVENTS) : nullptr
+#define XTC_TRACE_MARK() do { if (_tb && _tn < XTC_TRACE_EVENTS) _tb[_tn++] = clock64(); } while (0)
+#else
+#define XTC_TRACE_DECL(role)
+#define XTC_TRACE_MARK()
+#endif
+
 struct ConvHaloParams {
   float* Y;
   int* status;
@@ -123,15 +136,23 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------ producer --------------------------------
+    // The filter bank, once: one thread announces the bytes, then every lane issues its share
+    // of the copies (issuing them all from one thread takes longer than they take to arrive).
+    if (lane == 0) mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(p.taps * p.nblk * WBLOCK));
+    __syncwarp();
+    {
+      const int copies = p.taps * p.nblk * (BN / 32);
+      for (int i = lane; i < copies; i += 32) {
+        const int g = i % (BN / 32);
+        const int tb = i / (BN / 32);  // tap * nblk + blk
+        const int tap = tb / p.nblk, blk = tb - tap * p.nblk;
+        tma_load_2d(wts + static_cast<size_t>(tb) * WBLOCK + g * 4096, &tmW, wbar, g * 32,
+                    tap * p.C + blk * 32);
+      }
+    }
     if (lane == 0) {
-      // the filter bank, once
-      mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(p.taps * p.nblk * WBLOCK));
-      for (int tap = 0; tap < p.taps; ++tap)
-        for (int blk = 0; blk < p.nblk; ++blk)
-#pragma unroll
-          for (int g = 0; g < BN / 32; ++g)
-            tma_load_2d(wts + (static_cast<size_t>(tap) * p.nblk + blk) * WBLOCK + g * 4096, &tmW,
-                        wbar, g * 32, tap * p.C + blk * 32);
+      XTC_TRACE_DECL(0);
+      XTC_TRACE_MARK();  // start
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < p.tiles && !failed; tile += gridDim.x) {
@@ -146,6 +167,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             failed = true;
             break;
           }
+          XTC_TRACE_MARK();  // stage free: load issued
           mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(p.stage_tx));
           tma_load_im2col_4d(ring + static_cast<size_t>(stage) * p.stage_bytes, &tmX, &full[stage],
                              slab * SLAB, iw, ih, img, 0, 0);
@@ -165,10 +187,13 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const int t0 = DUAL ? (w == 0 ? 0 : (p.taps + 1) / 2) : 0;
       const int t1 = DUAL ? (w == 0 ? (p.taps + 1) / 2 : p.taps) : p.taps;
       const int r0 = t0 / p.S, s0 = t0 - r0 * p.S;
+      XTC_TRACE_DECL(1 + w);
+      XTC_TRACE_MARK();  // start
       if (!mbar_wait(wbar, 0)) {
         atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
         failed = true;
       }
+      XTC_TRACE_MARK();  // bank landed
       const uint32_t w0 = smem_u32(wts) + static_cast<uint32_t>(t0) * p.nblk * WBLOCK;
       // A: K-major rows of ROW bytes, 8-row swizzle atoms
       const uint32_t a_hi = umma_desc_hi(8 * ROW, static_cast<uint32_t>(SLAB == 32 ? UMMA_SWIZZLE_128B
@@ -190,6 +215,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           break;
         }
         tc_fence_after();
+        XTC_TRACE_MARK();  // accumulator free
         const uint32_t d_tmem = tmem_base + (acc * NACC + w) * BN;
         for (int slab = 0; slab < p.nslab; ++slab) {
           if (!mbar_wait(&full[stage], phase)) {
@@ -197,7 +223,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             failed = true;
             break;
           }
-          tc_fence_after();
+          XTC_TRACE_MARK();  // slab landed
           const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * p.stage_bytes);
           uint32_t a_row = umma_desc_lo(sA, 16) + a_first;  // tap (r, 0)
           // k rows [slab * SLAB, +SLAB) of the filter bank: block slab*SLAB/32, 128 B per k row
@@ -219,6 +245,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             }
           }
           tc_commit(&empty[stage]);
+          XTC_TRACE_MARK();  // slab issued
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;
@@ -232,6 +259,12 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int quad = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const bool vec_ok = (p.F % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0);
+    XTC_TRACE_DECL(3);
+    if (quad != 0 || lane != 0) {
+#ifdef XTC_TRACE
+      _tb = nullptr;
+#endif
+    }
     int local = 0;
     for (int tile = blockIdx.x; tile < p.tiles && !failed; tile += gridDim.x, ++local) {
       const int acc = local & 1;
@@ -242,6 +275,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         break;
       }
       tc_fence_after();
+      XTC_TRACE_MARK();  // accumulator ready
       const long long q = static_cast<long long>(tile) * BM + quad * 32 + lane;
       const int img = static_cast<int>(q / plane);
       const int rem = static_cast<int>(q - static_cast<long long>(img) * plane);
@@ -285,6 +319,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
+      XTC_TRACE_MARK();  // tile stored
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
   }

@@ -7,7 +7,14 @@
 // relu into the epilogue.  Shapes TMA cannot address (C or F not a multiple of
 // 4) run on a direct CUDA-core kernel.
 #include "conv2d_halo_pair.cuh"
+#include "conv2d_halo_taps.cuh"
 #include "gemm_tf32_pair.cuh"
+
+#ifdef XTC_TRACE
+extern "C" int xtc_cuda_debug_set_halo_trace(long long* buffer) {
+  return cudaMemcpyToSymbol(xtc::g_halo_trace, &buffer, sizeof(buffer)) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 namespace xtc {
 
@@ -160,6 +167,7 @@ int launch_conv_tc(const ConvArgs& a) {
   const int tiles = p.tiles_m * p.tiles_n * p.split_k;
   // cluster split: one work item per CTA, the pieces of a tile in consecutive CTAs
   const int grid = p.cluster_k ? tiles : (tiles < sm_count(dev) ? tiles : sm_count(dev));
+  p.group_n = panel_columns(sm_count(dev), BM, BN, p.tiles_n);
   XTC_CUDA_CHECK(launch_overlapped_clustered(kernel, grid, p.cluster_k ? p.split_k : 1, NUM_THREADS,
                                              smem, a.stream, tmA, tmB, tmZ, tmZ, tmC, p, stages));
   return XTC_CUDA_OK;
@@ -174,10 +182,13 @@ struct HaloPlan {
 // Whether the halo kernel can run this convolution, and with what footprint.
 // pair = the CTA-pair kernel, where each CTA keeps half of the filter columns.
 // slab = channels per pipeline stage (32, or 16 in the single-CTA kernel).
-HaloPlan plan_halo(const ConvArgs& a, bool pair = false, int slab = 32) {
+// taps = the two-taps-per-MMA kernel (conv2d_halo_taps.cuh): at most 64 filters, a filter
+// row of at least two taps, one CTA per tile, 1 KB more for the rows that cross warps.
+HaloPlan plan_halo(const ConvArgs& a, bool pair = false, int slab = 32, bool taps = false) {
   HaloPlan h;
   h.slab = slab;
   if (a.sh != 1 || a.sw != 1 || a.F > 256) return h;
+  if (taps && (pair || a.F > 64 || a.S < 2)) return h;
   const int64_t Wp = a.W + a.pl + a.pr;
   const int64_t P = BM + (a.R - 1) * Wp + (a.S - 1);
   if (P > 1024 || a.pl > 127 || a.pt > 127 || a.pr > 127 || a.pb > 127) return h;
@@ -187,16 +198,17 @@ HaloPlan plan_halo(const ConvArgs& a, bool pair = false, int slab = 32) {
   h.nslab = static_cast<int>((a.C + slab - 1) / slab);
   h.nblk = static_cast<int>((a.C + 31) / 32);
   const int64_t wbytes = a.R * a.S * h.nblk * (pair ? h.bn / 2 : h.bn) * 128;
-  const int64_t budget = 232448 - 1024 - 1024;
+  const int64_t fixed = 1024 + 1024 + (taps ? 1024 : 0);  // alignment slack, barriers, exchange rows
+  const int64_t budget = 232448 - fixed;
   const int64_t stages = (budget - wbytes) / h.stage_bytes;
   if (stages < 2) return h;
   h.stages = static_cast<int>(stages > 8 ? 8 : stages);
-  h.smem = static_cast<int>(1024 + 1024 + wbytes + static_cast<int64_t>(h.stages) * h.stage_bytes);
+  h.smem = static_cast<int>(fixed + wbytes + static_cast<int64_t>(h.stages) * h.stage_bytes);
   h.ok = true;
   return h;
 }
 
-template <int BN, bool PAIR, int SLAB>
+template <int BN, bool PAIR, int SLAB, bool TAPS = false>
 int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
   encode_im2col_fn enc = get_encode_im2col();
   XTC_REQUIRE(enc != nullptr, "cuTensorMapEncodeIm2col is not available from this driver");
@@ -230,7 +242,7 @@ int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
   p.status = device_status_word(dev);
   XTC_REQUIRE(p.status != nullptr, "conv2d: device status word unavailable");
   p.Q = a.B * Hp * Wp;
-  const int tile_positions = PAIR ? 2 * BM : BM;
+  const int tile_positions = TAPS ? TAPS_TILE : PAIR ? 2 * BM : BM;
   p.tiles = static_cast<int>((p.Q + tile_positions - 1) / tile_positions);
   p.Hp = static_cast<int>(Hp);
   p.Wp = static_cast<int>(Wp);
@@ -254,9 +266,11 @@ int launch_conv_halo(const ConvArgs& a, const HaloPlan& h) {
   constexpr bool CAN_DUAL = BN <= 128;
   const bool dual = CAN_DUAL && p.taps >= 2;
   static_assert(!PAIR || SLAB == 32, "the CTA-pair kernel has 32-channel slabs only");
-  auto kernel = PAIR ? (dual ? conv2d_halo_pair_kernel<BN, CAN_DUAL> : conv2d_halo_pair_kernel<BN, false>)
-                     : (dual ? conv2d_halo_kernel<BN, CAN_DUAL, SLAB>
-                             : conv2d_halo_kernel<BN, false, SLAB>);
+  static_assert(!TAPS || (BN == 64 && !PAIR), "two taps per MMA: 64 filters, one CTA per tile");
+  auto kernel = TAPS ? conv2d_halo_taps_kernel<SLAB>
+                : PAIR ? (dual ? conv2d_halo_pair_kernel<BN, CAN_DUAL> : conv2d_halo_pair_kernel<BN, false>)
+                       : (dual ? conv2d_halo_kernel<BN, CAN_DUAL, SLAB>
+                               : conv2d_halo_kernel<BN, false, SLAB>);
   static thread_local int configured_dev[2] = {-1, -1};
   static thread_local int configured_smem[2] = {0, 0};
   const int which = dual ? 1 : 0;
@@ -277,7 +291,10 @@ int dispatch_conv_halo_bn(const ConvArgs& a, const HaloPlan& h, bool pair) {
   return h.slab == 16 ? launch_conv_halo<BN, false, 16>(a, h) : launch_conv_halo<BN, false, 32>(a, h);
 }
 
-int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h, bool pair) {
+int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h, bool pair, bool taps = false) {
+  if (taps)
+    return h.slab == 16 ? launch_conv_halo<64, false, 16, true>(a, h)
+                        : launch_conv_halo<64, false, 32, true>(a, h);
   switch (h.bn) {
     case 64: return dispatch_conv_halo_bn<64>(a, h, pair);
     case 128: return dispatch_conv_halo_bn<128>(a, h, pair);
@@ -339,6 +356,7 @@ int launch_conv_pair(const ConvArgs& a) {
   const int tiles = p.tiles_m * p.tiles_n;
   const int max_pairs = sm_count(dev) / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  p.group_n = panel_columns(pairs, 2 * BM, BN, p.tiles_n);
   XTC_CUDA_CHECK(launch_overlapped(kernel, 2 * pairs, NUM_THREADS, smem, a.stream, tmA, tmB, tmC, p,
                                    stages));
   return XTC_CUDA_OK;
@@ -420,7 +438,8 @@ extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, 
   a.sh = stride_h; a.sw = stride_w;
   a.pt = pad_top; a.pb = pad_bottom; a.pl = pad_left; a.pr = pad_right;
   a.OH = OH; a.OW = OW;
-  if (plan_halo(a, false, 32).ok || plan_halo(a, false, 16).ok || plan_halo(a, true, 32).ok)
+  if (plan_halo(a, false, 32).ok || plan_halo(a, false, 16).ok || plan_halo(a, true, 32).ok ||
+      plan_halo(a, false, 32, true).ok || plan_halo(a, false, 16, true).ok)
     return XTC_CUDA_OK;  // resident weights: no workspace
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
@@ -490,7 +509,18 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     XTC_CUDA_CHECK(cudaGetLastError());
     return XTC_CUDA_OK;
   }
-  XTC_REQUIRE(c.variant >= 0 && c.variant <= 2, "conv2d: unknown variant %d", c.variant);
+  XTC_REQUIRE(c.variant >= 0 && c.variant <= 3, "conv2d: unknown variant %d", c.variant);
+  if (c.variant == 3) {
+    // Resident weights with two filter taps per MMA (only when asked for: see the numbers in
+    // conv2d_halo_taps.cuh).
+    HaloPlan t = plan_halo(a, false, 32, true);
+    const HaloPlan t16 = plan_halo(a, false, 16, true);
+    if (t16.ok && (c.tile_k == 16 || (c.tile_k != 32 && !t.ok))) t = t16;
+    if (t.ok && c.tile_m != 2 * BM) return dispatch_conv_halo(a, t, false, true);
+    set_error("conv2d: two taps per MMA (variant 3) needs stride 1, at most 64 filters, a filter row "
+              "of two taps or more, one CTA per tile and a filter bank that fits in shared memory");
+    return XTC_CUDA_ERR_UNSUPPORTED;
+  }
   if (c.variant != 1) {
     // Resident weights + halo tiles: chosen when asked for, and by default when
     // the caller named no im2col-kernel parameter (pixel tile, K per stage).

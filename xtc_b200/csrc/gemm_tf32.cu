@@ -86,6 +86,7 @@ struct LaunchArgs {
   int* status = nullptr;  // status word to use instead of the per-device one
   int n_extra = 0;        // further copies of C to write (broadcast epilogue)
   float* extra[7] = {};
+  float* mcast = nullptr;  // this rank's block of C through a multicast mapping (CTA-pair kernel)
   bool copier_warps = true;  // CTA-pair kernel: peers written by copier warps, not by the epilogue
   int split_k = 1;        // CTAs per output tile along K (needs partials + counters)
   float* partials = nullptr;
@@ -185,6 +186,7 @@ int launch_tc(const LaunchArgs& a) {
   const int tiles = p.tiles_m * p.tiles_n * p.split_k;
   // cluster split: one work item per CTA, the pieces of a tile in consecutive CTAs
   const int grid = p.cluster_k ? tiles : (tiles < sm_count(dev) ? tiles : sm_count(dev));
+  p.group_n = panel_columns(sm_count(dev), BM, BN, p.tiles_n);
   XTC_CUDA_CHECK(launch_overlapped_clustered(kernel, grid, p.cluster_k ? p.split_k : 1, NUM_THREADS,
                                              smem, a.stream, tmA, tmB, tmAlo, tmBlo, tmC, p, stages));
   return XTC_CUDA_OK;
@@ -228,6 +230,7 @@ int launch_pair(const LaunchArgs& a) {
   XTC_REQUIRE(p.status != nullptr, "gemm: device status word unavailable");
   p.n_extra = a.n_extra;
   for (int d = 0; d < p.n_extra; ++d) p.extra_dst[d] = a.extra[d];
+  p.mc_dst = a.mcast;
 
   auto kernel = gemm_tf32_pair_kernel<BN, KSPANS, A_MN, B_MN>;
   const int smem = L::total(stages);
@@ -260,6 +263,7 @@ int launch_pair(const LaunchArgs& a) {
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  p.group_n = panel_columns(pairs, 2 * BM, BN, p.tiles_n);
   // Split tail: the tiles of a last round that would leave at least half of the
   // pairs idle are cut along K, one piece per pair (see gemm_tf32_pair.cuh).
   const int rem = tiles % pairs;
@@ -278,7 +282,8 @@ int launch_pair(const LaunchArgs& a) {
                                              pair_tail_flag_bytes(sm_count(dev) / 2));
     if (p.tail_split < 2) p.tail_split = 0;
   }
-  const int threads = (p.n_extra > 0 && a.copier_warps) ? PAIR_THREADS_BCAST : PAIR_THREADS;
+  const int threads =
+      ((p.n_extra > 0 && a.copier_warps) || p.mc_dst != nullptr) ? PAIR_THREADS_BCAST : PAIR_THREADS;
   XTC_CUDA_CHECK(launch_overlapped(kernel, 2 * pairs, threads, smem, a.stream, tmA, tmB, tmC, p, stages));
   return XTC_CUDA_OK;
 }
@@ -556,7 +561,7 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
 static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                      int64_t lda, int64_t ldb, int64_t ldc, int flags, float relu_threshold,
                      const xtc_cuda_gemm_config* cfg, void* workspace, size_t workspace_bytes,
-                     void* stream, int n_extra, float* const* extra) {
+                     void* stream, int n_extra, float* const* extra, float* mcast = nullptr) {
   XTC_REQUIRE(A && B && C, "gemm: NULL operand");
   XTC_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %lldx%lldx%lld", (long long)M,
               (long long)N, (long long)K);
@@ -593,6 +598,16 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
       XTC_REQUIRE(tma_addressable(extra[d], ldc), "gemm_bcast: destination %d is NULL or misaligned", d);
       a.extra[d] = extra[d];
     }
+  }
+  if (mcast != nullptr) {
+    XTC_REQUIRE(tma_ok && tma_addressable(C, ldc) && tma_addressable(mcast, ldc) &&
+                    c.precision == XTC_CUDA_PRECISION_TF32,
+                "gemm_mcast: TF32 only; operands, C and the multicast address must be 16-byte aligned "
+                "with pitches that are multiples of 4");
+    XTC_REQUIRE(c.tile_m == 0 || c.tile_m == 2 * BM,
+                "gemm_mcast: the multicast stores are issued by the CTA-pair kernel (tile_m = 256)");
+    c.tile_m = 2 * BM;
+    a.mcast = mcast;
   }
   if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
 
@@ -695,6 +710,16 @@ extern "C" int xtc_cuda_gemm_f32_bcast(const float* A, const float* B, float* C,
   XTC_REQUIRE(n_extra >= 0, "gemm_bcast: negative destination count");
   return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, flags, relu_threshold, cfg, workspace,
                    workspace_bytes, stream, n_extra, extra_dst);
+}
+
+extern "C" int xtc_cuda_gemm_f32_mcast(const float* A, const float* B, float* C, float* mcast_C,
+                                       int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                       int64_t ldc, int flags, float relu_threshold,
+                                       const xtc_cuda_gemm_config* cfg, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  XTC_REQUIRE(mcast_C != nullptr, "gemm_mcast: NULL multicast address");
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, flags, relu_threshold, cfg, workspace,
+                   workspace_bytes, stream, 0, nullptr, mcast_C);
 }
 
 // Exporting device memory to the other processes of the box (one process per GPU)

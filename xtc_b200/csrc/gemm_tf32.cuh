@@ -37,6 +37,7 @@ struct GemmParams {
   int64_t ldc;
   int M, N, K;
   int tiles_m, tiles_n, k_blocks;
+  int group_n;        // tile columns per panel of the tile order (0 = 4), see tile_coords
   int chunk_kblocks;  // K stages accumulated in one TMEM buffer before the epilogue takes it
   int relu;
   float relu_threshold;
@@ -50,6 +51,11 @@ struct GemmParams {
   // row-sharded matmul into the GEMM.
   int n_extra;
   float* extra_dst[7];
+  // The same broadcast through an NVLink multicast mapping (CTA-pair kernel, copier warps):
+  // mc_dst addresses this rank's block of C in a multicast object that every rank's C is
+  // bound to, so ONE multimem.st per vector reaches every GPU (the NVSwitch replicates it)
+  // where the unicast form issues one store per peer.  NULL = unicast stores to extra_dst.
+  float* mc_dst;
   // Split-K (small problems with fewer tiles than SMs): `split_k` CTAs share one
   // output tile, each over `split_kblocks` K stages.  Every CTA writes its raw
   // partial tile to `partials` [split][tile][128][BN]; the last one to arrive on
@@ -95,18 +101,33 @@ struct SmemLayout {
   }
 };
 
-// tile index -> (m, n) tile coordinates.  Tiles are walked in panels of
-// GROUP_N tile columns, rows fastest, so that CTAs running at the same time
-// share a few B panels and stream A once per panel.
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  constexpr int GROUP_N = 4;
-  int per_group = tiles_m * GROUP_N;
+// tile index -> (m, n) tile coordinates.  Tiles are walked in panels of group_n tile
+// columns, columns fastest inside a panel, so that the tiles in flight at one time (one per
+// SM or SM pair) form a near-square block: its A rows and B columns are then the smallest
+// operand set L2 has to keep for that wave (panel_columns() picks group_n on the host).
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_n, int& tm,
+                                            int& tn) {
+  const int gw = group_n > 0 ? group_n : 4;
+  int per_group = tiles_m * gw;
   int g = tile / per_group;
-  int first_n = g * GROUP_N;
-  int gn = min(GROUP_N, tiles_n - first_n);
+  int first_n = g * gw;
+  int gn = min(gw, tiles_n - first_n);
   int r = tile - g * per_group;
   tm = r / gn;
   tn = first_n + (r - tm * gn);
+}
+
+// Panel width for `slots` tiles in flight of tile_rows x tile_cols outputs: the width w that
+// minimises the operand bytes of a wave, w * tile_cols + (slots / w) * tile_rows (both times K).
+inline int panel_columns(int slots, int tile_rows, int tile_cols, int tiles_n) {
+  int best = 1;
+  double best_cost = 1e300;
+  for (int w = 1; w <= tiles_n && w <= slots; ++w) {
+    const double rows = static_cast<double>(slots) / w;
+    const double cost = static_cast<double>(w) * tile_cols + rows * tile_rows;
+    if (cost < best_cost) { best_cost = cost; best = w; }
+  }
+  return best;
 }
 
 template <int BN, int KSPANS, int A_MODE, bool B_MN, bool SPLIT3, bool TMA_STORE>
@@ -179,7 +200,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int kb_lo = (item - tile * p.split_k) * p.split_kblocks;
         const int kb_hi = min(kb_lo + p.split_kblocks, p.k_blocks);
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
         int img = 0, ih0 = 0, iw0 = 0;  // input pixel under the filter origin of row m0
         if (A_MODE == A_IM2COL) {
@@ -401,7 +422,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int kb_lo = my_split * p.split_kblocks;
       const int kb_hi = min(kb_lo + p.split_kblocks, p.k_blocks);
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
       float sum[SPLIT3 ? BN : 1];
       if (SPLIT3) {
@@ -521,7 +542,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (warp >= 2) {
       const int tile = static_cast<int>(blockIdx.x) / p.split_k;
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
       const int rows_own = BM / p.split_k;
       const int rank = static_cast<int>(cluster_ctarank());  // = this CTA's piece

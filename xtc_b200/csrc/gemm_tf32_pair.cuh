@@ -135,7 +135,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   // Broadcast with copier warps: the epilogue only stores the tile locally and counts
   // it; warps 6..9 copy finished tiles from the local C to the peers, so the tensor
   // pipeline never waits for NVLink.
-  const bool copiers = p.n_extra > 0 && blockDim.x > PAIR_THREADS;
+  const bool copiers = (p.n_extra > 0 || p.mc_dst != nullptr) && blockDim.x > PAIR_THREADS;
 
   if (threadIdx.x == 0) {
     for (int q = 0; q < 4; ++q) stored[q] = 0;
@@ -176,7 +176,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       PairWork w;
       while (!failed && work.next(p, w)) {
         int tm, tn;
-        tile_coords(w.tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
         const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
         const int n0 = tn * BN + static_cast<int>(rank) * HALF;
         int img = 0, ih0 = 0, iw0 = 0;  // input pixel under the filter origin of row m0
@@ -304,7 +304,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     PairWork w;
     for (; !failed && work.next(p, w); ++local) {
       int tm, tn;
-      tile_coords(w.tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
       const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
       const int n0 = tn * BN;
       const int acc = local & 1;
@@ -448,7 +448,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       __threadfence();
       int tm, tn;
-      tile_coords(w.tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
       const int row0 = tm * (2 * BM) + static_cast<int>(rank) * BM + q * 32;
       const int n0 = tn * BN;
 #pragma unroll 1
@@ -464,6 +464,20 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             if (idx < V && row < p.M && col < p.N)
               v[rr][j] = __ldcg(reinterpret_cast<const float4*>(p.C + static_cast<int64_t>(row) * p.ldc + col));
           }
+        }
+        if (p.mc_dst != nullptr) {  // one multicast store per vector reaches every GPU
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int row = row0 + r + rr;
+#pragma unroll
+            for (int j = 0; j < JT; ++j) {
+              const int idx = j * 32 + lane;
+              const int col = n0 + idx * 4;
+              if (idx < V && row < p.M && col < p.N)
+                multimem_st_f4(p.mc_dst + static_cast<int64_t>(row) * p.ldc + col, v[rr][j]);
+            }
+          }
+          continue;
         }
         for (int d = 0; d < p.n_extra; ++d) {
 #pragma unroll

@@ -16,12 +16,25 @@ relu_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n, f
   const int64_t n4 = n >> 2;
   const float4* x4 = reinterpret_cast<const float4*>(x);
   float4* y4 = reinterpret_cast<float4*>(y);
-  for (int64_t i = tid; i < n4; i += stride) {
+  int64_t i = tid;
+  // four independent 128-bit loads in flight per thread before the first store
+  for (; i + 3 * stride < n4; i += 4 * stride) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcs(x4 + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      v[u].x = fmaxf(v[u].x, thr); v[u].y = fmaxf(v[u].y, thr);
+      v[u].z = fmaxf(v[u].z, thr); v[u].w = fmaxf(v[u].w, thr);
+      __stcs(y4 + i + u * stride, v[u]);
+    }
+  }
+  for (; i < n4; i += stride) {
     float4 v = __ldcs(x4 + i);
     v.x = fmaxf(v.x, thr); v.y = fmaxf(v.y, thr); v.z = fmaxf(v.z, thr); v.w = fmaxf(v.w, thr);
     __stcs(y4 + i, v);
   }
-  for (int64_t i = (n4 << 2) + tid; i < n; i += stride) y[i] = fmaxf(x[i], thr);
+  for (int64_t j = (n4 << 2) + tid; j < n; j += stride) y[j] = fmaxf(x[j], thr);
 }
 
 __global__ void __launch_bounds__(256)
@@ -288,23 +301,56 @@ __device__ __forceinline__ T splat(float v);
 template <> __device__ __forceinline__ float splat<float>(float v) { return v; }
 template <> __device__ __forceinline__ float4 splat<float4>(float v) { return make_float4(v, v, v, v); }
 
+// One output row (the innermost axis, after axes without padding have been merged into
+// their outer neighbours) per `lanes` threads: the row's position along the outer axes is
+// decoded once per row, the copy along the row needs no division.  lanes is a power of two
+// <= 256; a block handles 256 / lanes rows at a time.
 template <typename T>
 __global__ void __launch_bounds__(256)
-pad_kernel(const T* __restrict__ x, T* __restrict__ y, PadParams p) {
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+pad_kernel(const T* __restrict__ x, T* __restrict__ y, PadParams p, int lane_shift, int64_t rows,
+           int64_t chunks, int64_t chunk_width) {
+  const int lanes = 1 << lane_shift;
+  const int rows_per_block = 256 >> lane_shift;
+  const int lane = threadIdx.x & (lanes - 1);
+  const int sub = threadIdx.x >> lane_shift;
   const T fill = splat<T>(p.value);
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.total;
-       i += stride) {
-    int64_t rem = i, off = 0;
+  const int last = p.ndim - 1;
+  const int64_t width = p.out_shape[last], in_width = p.in_shape[last], lo = p.lo[last];
+  // work item = (row, chunk of chunk_width columns): long rows are shared by several groups
+  for (int64_t item = static_cast<int64_t>(blockIdx.x) * rows_per_block + sub; item < rows * chunks;
+       item += static_cast<int64_t>(gridDim.x) * rows_per_block) {
+    const int64_t row = item / chunks;
+    const int64_t col_lo = (item - row * chunks) * chunk_width;
+    const int64_t col_hi = col_lo + chunk_width < width ? col_lo + chunk_width : width;
+    int64_t rem = row, off = 0;
     bool inside = true;
-    for (int d = p.ndim - 1; d >= 0; --d) {
+    for (int d = last - 1; d >= 0; --d) {
       const int64_t q = rem / p.out_shape[d];
       const int64_t c = (rem - q * p.out_shape[d]) - p.lo[d];
       rem = q;
       inside = inside && c >= 0 && c < p.in_shape[d];
       off += c * p.in_stride[d];
     }
-    y[i] = inside ? x[off] : fill;
+    T* dst = y + row * width;
+    const T* src = x + off - lo;  // src[col] is the input element under output column col
+    if (!inside) {
+      for (int64_t col = col_lo + lane; col < col_hi; col += lanes) __stcs(dst + col, fill);
+      continue;
+    }
+    const int64_t hi_edge = lo + in_width;
+    int64_t col = col_lo + lane;
+    for (; col + 3 * lanes < col_hi; col += 4 * lanes) {
+      T v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t c = col + u * lanes;
+        v[u] = (c >= lo && c < hi_edge) ? __ldcs(src + c) : fill;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) __stcs(dst + col + u * lanes, v[u]);
+    }
+    for (; col < col_hi; col += lanes)
+      __stcs(dst + col, (col >= lo && col < hi_edge) ? __ldcs(src + col) : fill);
   }
 }
 
@@ -517,28 +563,62 @@ extern "C" int xtc_cuda_pad_f32(const float* X, float* Y, int ndim, const int64_
   }
   if (total == 0) return XTC_CUDA_OK;
   XTC_REQUIRE(Y && (X || in_total == 0), "pad: NULL operand");
+  // An axis without padding merges into its outer neighbour: [.., a, b] with b untouched is
+  // [.., a*b] padded by lo_a*b and hi_a*b.  NHWC padded on H and W becomes [B, H, W*C].
   {
+    int64_t hi_w[XTC_CUDA_MAX_DIMS];
+    for (int d = 0; d < ndim; ++d) hi_w[d] = hi[d];
+    int n = ndim;
+    for (int d = n - 1; d >= 1; --d) {
+      if (p.lo[d] == 0 && hi_w[d] == 0) {
+        const int64_t inner = p.in_shape[d];
+        p.in_shape[d - 1] *= inner;
+        p.out_shape[d - 1] *= inner;
+        p.lo[d - 1] *= inner;
+        hi_w[d - 1] *= inner;
+        for (int e = d; e < n - 1; ++e) {
+          p.in_shape[e] = p.in_shape[e + 1];
+          p.out_shape[e] = p.out_shape[e + 1];
+          p.lo[e] = p.lo[e + 1];
+          hi_w[e] = hi_w[e + 1];
+        }
+        --n;
+      }
+    }
+    p.ndim = n;
     int64_t st = 1;
-    for (int d = ndim - 1; d >= 0; --d) { p.in_stride[d] = st; st *= shape[d]; }
+    for (int d = n - 1; d >= 0; --d) { p.in_stride[d] = st; st *= p.in_shape[d]; }
   }
   int dev = 0;
   XTC_CUDA_CHECK(cudaGetDevice(&dev));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int last = ndim - 1;
-  const bool vec = aligned16(X) && aligned16(Y) && shape[last] % 4 == 0 && lo[last] % 4 == 0 &&
-                   hi[last] % 4 == 0 && in_total > 0;
+  const int last = p.ndim - 1;
+  const int64_t hi_last = p.out_shape[last] - p.in_shape[last] - p.lo[last];
+  const bool vec = aligned16(X) && aligned16(Y) && p.in_shape[last] % 4 == 0 && p.lo[last] % 4 == 0 &&
+                   hi_last % 4 == 0 && in_total > 0;
   if (vec) {
     p.in_shape[last] /= 4;
     p.out_shape[last] /= 4;
     p.lo[last] /= 4;
     for (int d = 0; d < last; ++d) p.in_stride[d] /= 4;
-    p.total = total / 4;
-    pad_kernel<float4><<<grid_for(p.total, dev), 256, 0, s>>>(
-        reinterpret_cast<const float4*>(X), reinterpret_cast<float4*>(Y), p);
-  } else {
-    p.total = total;
-    pad_kernel<float><<<grid_for(p.total, dev), 256, 0, s>>>(X, Y, p);
   }
+  const int64_t width = p.out_shape[last];
+  const int64_t rows = total / (vec ? 4 : 1) / width;
+  int lane_shift = 0;
+  while (lane_shift < 8 && (1ll << lane_shift) < width) ++lane_shift;
+  const int64_t chunk_width = (1ll << lane_shift) * 16;  // 16 accesses per thread and work item
+  const int64_t chunks = (width + chunk_width - 1) / chunk_width;
+  const int64_t groups = (rows * chunks + (256 >> lane_shift) - 1) / (256 >> lane_shift);
+  int64_t blocks = static_cast<int64_t>(sm_count(dev)) * 8;
+  if (blocks > groups) blocks = groups;
+  p.total = total;
+  if (vec)
+    pad_kernel<float4><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        reinterpret_cast<const float4*>(X), reinterpret_cast<float4*>(Y), p, lane_shift, rows, chunks,
+        chunk_width);
+  else
+    pad_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, s>>>(X, Y, p, lane_shift, rows, chunks,
+                                                                    chunk_width);
   XTC_CUDA_CHECK(cudaGetLastError());
   return XTC_CUDA_OK;
 }

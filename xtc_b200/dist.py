@@ -134,7 +134,13 @@ class PeerStoreMatmul:
     """
 
     def __init__(self, device: Any, a_ptr: int, b_ptr: int, m: int, n: int, k: int, world: int,
-                 rank: int, group: Any = None, config: dict | None = None) -> None:
+                 rank: int, group: Any = None, config: dict | None = None,
+                 exchange: str = "peer") -> None:
+        """exchange: "peer" = one 128-bit store per peer (CUDA IPC mappings of the peers' C);
+        "multimem" = one multicast store per vector through an NVLink multicast object that
+        every rank's C is bound to (NVLS; the buffers come from torch's symmetric-memory
+        allocator); "auto" = multimem where the box offers it, else peer.  ``self.exchange``
+        says which one runs."""
         import ctypes
 
         import torch
@@ -143,28 +149,41 @@ class PeerStoreMatmul:
         from . import capi
 
         assert m % world == 0, f"M ({m}) must be divisible by the number of ranks ({world})"
+        assert exchange in ("peer", "multimem", "auto"), exchange
         self.device, self.lib = device, device.lib
         self.world, self.rank, self.group = world, rank, group
         self.m, self.n, self.k = m, n, k
         self.rows = m // world
         self.a_ptr, self.b_ptr = int(a_ptr), int(b_ptr)
         self.cfg = capi.GemmConfig(**(config or {}))
-        self.c_local = device.memory_allocate(m * n * 4)
-        handle = ctypes.create_string_buffer(64)
-        capi.check(self.lib.xtc_cuda_ipc_export(self.c_local, handle))
-        handles: list[Any] = [None] * world
-        dist.all_gather_object(handles, handle.raw, group=group)
-        self.imported: list[Any] = []
         offset = rank * self.rows * n * 4
-        extras = []
-        for r in range(world):
-            if r == rank:
-                continue
-            ptr = ctypes.c_void_p()
-            capi.check(self.lib.xtc_cuda_ipc_import(ctypes.create_string_buffer(handles[r], 64),
-                                                    ctypes.byref(ptr)))
-            self.imported.append(ptr)
-            extras.append(ptr.value + offset)
+        self.imported: list[Any] = []
+        self.mcast_block = 0
+        self._symm = None
+        self.exchange = "none" if world == 1 else "peer"
+        if world > 1 and exchange in ("multimem", "auto"):
+            self._symm = self._multicast_buffer(m * n, group, required=exchange == "multimem")
+        if self._symm is not None:
+            tensor, handle = self._symm
+            self.c_local = ctypes.c_void_p(tensor.data_ptr())
+            self.mcast_block = int(handle.multicast_ptr) + offset
+            self.exchange = "multimem"
+            extras: list[int] = []
+        else:
+            self.c_local = device.memory_allocate(m * n * 4)
+            handle = ctypes.create_string_buffer(64)
+            capi.check(self.lib.xtc_cuda_ipc_export(self.c_local, handle))
+            handles: list[Any] = [None] * world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            extras = []
+            for r in range(world):
+                if r == rank:
+                    continue
+                ptr = ctypes.c_void_p()
+                capi.check(self.lib.xtc_cuda_ipc_import(ctypes.create_string_buffer(handles[r], 64),
+                                                        ctypes.byref(ptr)))
+                self.imported.append(ptr)
+                extras.append(ptr.value + offset)
         self.extras = (ctypes.c_void_p * max(len(extras), 1))(*extras)
         self.n_extra = len(extras)
         self.c_block = self.c_local.value + offset
@@ -180,6 +199,35 @@ class PeerStoreMatmul:
         self._flag = torch.zeros(1, device="cuda")
         self._dist = dist
 
+    def _multicast_buffer(self, numel: int, group: Any, required: bool) -> Any:
+        """(tensor, handle) of a float32 buffer of `numel` elements on every rank, all bound
+        to one NVLink multicast object, or None where the box cannot (every rank must take
+        the same branch: the outcome is agreed on with an all-reduce)."""
+        import torch
+        import torch.distributed as dist
+
+        pair, reason = None, ""
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            pg = group if group is not None else dist.group.WORLD
+            tensor = symm_mem.empty((numel,), dtype=torch.float32,
+                                    device=torch.device("cuda", self.device.ordinal))
+            handle = symm_mem.rendezvous(tensor, pg)
+            if int(getattr(handle, "multicast_ptr", 0) or 0) != 0:
+                pair = (tensor, handle)
+            else:
+                reason = "the symmetric-memory handle has no multicast address"
+        except Exception as e:  # allocator or driver without multicast support
+            reason = f"{type(e).__name__}: {e}"
+        ok = torch.tensor([1.0 if pair is not None else 0.0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() != 1.0:
+            if required:
+                raise RuntimeError(f"multimem exchange unavailable on rank {self.rank}: {reason or 'a peer could not'}")
+            return None
+        return pair
+
     def _on_stream(self, stream: int | None) -> Any:
         """Context that makes `stream` (a raw cudaStream_t; None or 0 = the legacy default
         stream) torch's current stream, so that a collective issued inside it is ordered
@@ -193,10 +241,16 @@ class PeerStoreMatmul:
     def step(self, stream: int | None = None) -> None:
         from . import capi
 
-        rc = self.lib.xtc_cuda_gemm_f32_bcast(
-            self.a_ptr, self.b_ptr, self.c_block, self.extras, self.n_extra, self.rows, self.n,
-            self.k, self.k, self.n, self.n, 0, 0.0, ctypes_byref(self.cfg), self.workspace,
-            self.ws_bytes, stream)
+        if self.mcast_block:
+            rc = self.lib.xtc_cuda_gemm_f32_mcast(
+                self.a_ptr, self.b_ptr, self.c_block, self.mcast_block, self.rows, self.n, self.k,
+                self.k, self.n, self.n, 0, 0.0, ctypes_byref(self.cfg), self.workspace,
+                self.ws_bytes, stream)
+        else:
+            rc = self.lib.xtc_cuda_gemm_f32_bcast(
+                self.a_ptr, self.b_ptr, self.c_block, self.extras, self.n_extra, self.rows, self.n,
+                self.k, self.k, self.n, self.n, 0, 0.0, ctypes_byref(self.cfg), self.workspace,
+                self.ws_bytes, stream)
         if rc:
             capi.check(rc)
         if self.world > 1:
@@ -226,6 +280,16 @@ class PeerStoreMatmul:
         for ptr in self.imported:
             self.lib.xtc_cuda_ipc_release(ptr)
         self.imported = []
+        if self._symm is not None:
+            # drop the multicast binding while every rank is still alive (all ranks are past
+            # the barrier above, none has exited)
+            self._symm = None
+            self.c_local = None
+            self.mcast_block = 0
+            import torch
+
+            torch.cuda.synchronize()
+            self._dist.barrier(group=self.group)
         if self.c_local is not None:
             self.device.memory_free(self.c_local)
             self.c_local = None

@@ -149,6 +149,8 @@ class StrategyCudaConv:
                  tile_m = output positions per tile (128 = one CTA, 256 = a CTA pair with
                  half a filter bank each), tile_k = channels per pipeline stage (16 or 32,
                  32 only for pairs), stages; tile_n, tma_store and split_k do not apply
+      variant 3  the same with two neighbouring filter taps per MMA (at most 64 filters, filter
+                 rows of two taps or more, one CTA per tile)
       variant 1  implicit GEMM, one im2col fetch per filter tap: the GEMM kernels' tile_m /
                  tile_n / tile_k / stages / epilogue, and split_k = 2, 4, 8 pieces of the
                  reduction in one thread-block cluster (one CTA per tile, tile_n <= 128)
@@ -174,9 +176,11 @@ class StrategyCudaConv:
     graph = property(lambda self: self._graph)
     node_name = property(lambda self: self._node.name)
 
-    def resident_stages(self, tile_m: int, slab: int) -> int:
+    def resident_stages(self, tile_m: int, slab: int, taps: bool = False) -> int:
         """Halo stages that fit next to the filter bank (0 = this layer cannot run resident)."""
         if self._stride != (1, 1) or self._f > 256 or (tile_m == 256 and slab != 32):
+            return 0
+        if taps and (tile_m != 128 or self._f > 64 or self._s < 2):
             return 0
         bn = 64 if self._f <= 64 else 128 if self._f <= 128 else 256
         run = 128 + (self._r - 1) * self._in_w + self._s - 1  # halo pixels of a 128-position tile
@@ -184,12 +188,13 @@ class StrategyCudaConv:
             return 0
         stage = -(-run * slab * 4 // 1024) * 1024
         bank = self._r * self._s * -(-self._c // 32) * (bn // 2 if tile_m == 256 else bn) * 128
-        return max(min((SMEM_BUDGET - bank) // stage, 8), 0) if SMEM_BUDGET - bank >= 2 * stage else 0
+        room = SMEM_BUDGET - bank - (1024 if taps else 0)  # the two-tap kernel exchanges rows
+        return max(min(room // stage, 8), 0) if room >= 2 * stage else 0
 
     def is_legal(self, sample: list[int]) -> bool:
         variant, tm, tn, tk, st, tma, split = sample
-        if variant == 2:
-            fit = self.resident_stages(tm, tk) if tm in (128, 256) and tk in (16, 32) else 0
+        if variant in (2, 3):
+            fit = self.resident_stages(tm, tk, variant == 3) if tm in (128, 256) and tk in (16, 32) else 0
             return (fit >= 2 and (st == 0 or 2 <= st <= fit) and tma == 0 and split == 1
                     and tn == (64 if self._f <= 64 else 128 if self._f <= 128 else 256))
         if variant != 1 or self._c % 4 or self._f % 4:
@@ -202,8 +207,8 @@ class StrategyCudaConv:
     def exhaustive(self):
         g = self._gemm
         tn_res = 64 if self._f <= 64 else 128 if self._f <= 128 else 256
-        for tm, slab, st in itertools.product((128, 256), (16, 32), (0, 2, 3, 4)):
-            s = [2, tm, tn_res, slab, st, 0, 1]
+        for variant, tm, slab, st in itertools.product((2, 3), (128, 256), (16, 32), (0, 2, 3, 4)):
+            s = [variant, tm, tn_res, slab, st, 0, 1]
             if self.is_legal(s):
                 yield s
         for tm, tn, tk, st, tma, split in itertools.product(g.tile_m, g.tile_n, g.tile_k, g.stages,
@@ -227,8 +232,10 @@ class StrategyCudaConv:
         variant, tm, tn, tk, st, tma, split = (int(v) for v in sample)
         b, h, w, f, r, s, c = list(self._op.dims)
         target = scheduler.node(self.node_name) if hasattr(scheduler, "node") else scheduler
-        if variant == 2:
+        if variant in (2, 3):
             target.pack_at(b, 1)  # the filter bank stays packed on chip
+            if variant == 3:
+                target.tile(s, {f"{s}1": 2})  # two neighbouring taps per MMA
         elif split > 1:
             piece = -(-self._c // split)
             target.split(c, {f"{c}_s{i}": i * piece for i in range(split)})
