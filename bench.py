@@ -688,7 +688,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
             gemm_cfg = dict(module.plan.steps[-1].config)
             op = peer_op = PeerStoreMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
                                            config=gemm_cfg,
-                                           exchange={"peer": "peer", "multimem": "multimem"}.get(args.exchange, "auto"))
+                                           exchange=args.exchange)
             how = ("one multicast store per vector through an NVLink multicast object (NVLS)"
                    if peer_op.exchange == "multimem" else "one 128-bit store per peer")
             sharding = (f"rows of A and C split over {world} ranks, B replicated; copier warps of the GEMM "
@@ -904,9 +904,9 @@ def main() -> None:
                     help="c4: run the transpose as its own kernel instead of reading A transposed")
     ap.add_argument("--chunks", type=int, default=1, help="row chunks overlapped with the exchange (N>1)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "multimem", "peer", "nccl"],
-                    help="c5 at N>1: fused all-gather by NVLink multicast stores (multimem), by one store "
-                         "per peer (peer), whichever of the two the box offers (auto), or GEMM followed "
-                         "by an NCCL all-gather (nccl)")
+                    help="c5 at N>1: fused all-gather by one store per peer (peer), by NVLink multicast "
+                         "stores (multimem), the faster of the two as measured (auto = peer), or GEMM "
+                         "followed by an NCCL all-gather (nccl)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-e2e", action="store_true",

@@ -126,7 +126,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         # (no rank may fail while its memory is bound to the multicast object: compare, unbind
         # on every rank, and only then judge)
         op = PeerStoreMatmul(dev, a_blk.data_ptr(), b_dev.data_ptr(), m, n, k, world, rank,
-                             config=pair_cfg, exchange="auto")
+                             config=pair_cfg, exchange="multimem?")
         used = op.exchange
         for _ in range(2):
             op.step(stream)
