@@ -361,6 +361,13 @@ int xtc_cuda_plan_step_count(const xtc_cuda_plan* plan, int* n_steps);
  * in FMA/s: same unit as evaluate_flops, src/xtc/csrcs/runtimes/host/
  * evaluate_flops.c:461-495, so ops_count / peak keeps its meaning. */
 int xtc_cuda_peak_fma(const char* dtype, double* fma_per_second);
+/* The same probe for one MMA instruction shape (rows 64 or 128, columns 64, 128 or
+ * 256, K = 8, operands resident in shared memory): the rate the tensor pipe and the
+ * shared-memory operand reads sustain for that shape, in FMA/s.  What a search
+ * space is pruned with: a 64-row instruction occupies the pipe as long as a
+ * 128-row one, so a 64-row tile halves the rate.  evaluate_flops in the reference
+ * probes one shape per dtype only. */
+int xtc_cuda_mma_rate(int tile_m, int tile_n, double* fma_per_second);
 
 #ifdef __cplusplus
 }

@@ -179,6 +179,7 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "xtc_cuda_plan_step_count": (c_int, [c_void_p, POINTER(c_int)]),
     "xtc_cuda_peak_fma": (c_int, [c_char_p, POINTER(c_double)]),
+    "xtc_cuda_mma_rate": (c_int, [c_int, c_int, POINTER(c_double)]),
 }
 
 _lib: ctypes.CDLL | None = None

@@ -365,6 +365,16 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t adesc, 
       : "memory");
 }
 
+// ---- 256-bit global store ----------------------------------------------------
+// Eight consecutive floats in one instruction: a whole 32-byte sector per lane, so a thread
+// that owns a row of a tile never leaves a half-written sector for L2 to merge.  The address
+// must be 32-byte aligned.
+__device__ __forceinline__ void st_global_f8(float* addr, const uint32_t* r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(addr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // ---- NVLink multicast --------------------------------------------------------
 // One 128-bit store to a multicast address: the switch writes it to the same offset of every
 // GPU memory bound to the multicast object (this GPU's included).

@@ -259,6 +259,7 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int quad = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const bool vec_ok = (p.F % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0);
+    const bool wide_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 31) == 0);
     XTC_TRACE_DECL(3);
     if (quad != 0 || lane != 0) {
 #ifdef XTC_TRACE
@@ -304,7 +305,10 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
         if (valid) {
           const int col0 = c * 32;
-          if (vec_ok && col0 + 32 <= p.F) {
+          if (wide_ok && col0 + 32 <= p.F) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) st_global_f8(dst + col0 + 8 * j, r + 8 * j);
+          } else if (vec_ok && col0 + 32 <= p.F) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               reinterpret_cast<float4*>(dst + col0)[j] =

@@ -225,6 +225,7 @@ conv2d_halo_taps_kernel(const __grid_constant__ CUtensorMap tmX,
     const int quad = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const bool vec_ok = (p.F % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0);
+    const bool wide_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 31) == 0);
     const int m = quad * 32 + lane;  // row of the tile = output position q0 + m
     XTC_TRACE_DECL(3);
     if (quad != 0 || lane != 0) {
@@ -286,7 +287,10 @@ conv2d_halo_taps_kernel(const __grid_constant__ CUtensorMap tmX,
         // line was measured slower: 26.1 us against 24.9 us on 32x56x56x64 -> 64.)
         if (valid) {
           const int col0 = c * 32;
-          if (vec_ok && col0 + 32 <= p.F) {
+          if (wide_ok && col0 + 32 <= p.F) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) st_global_f8(dst + col0 + 8 * j, lo + 8 * j);
+          } else if (vec_ok && col0 + 32 <= p.F) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               reinterpret_cast<float4*>(dst + col0)[j] =

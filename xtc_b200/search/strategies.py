@@ -39,6 +39,10 @@ class StrategyCudaGemm:
     name = "cuda_gemm"
     sample_names = ["tile_m", "tile_n", "tile_k", "stages", "tma_store", "split_k"]
 
+    # Rows: 128 (one CTA per tile) or 256 (a CTA pair).  No 64-row tile: a 64 x N x 8 MMA
+    # occupies the tensor pipe exactly as long as a 128 x N x 8 one (xtc_cuda_mma_rate on a
+    # B200: 57 / 67 / 133 clocks for N = 64 / 128 / 256 with either row count), so it can only
+    # halve the rate; small problems get more CTAs by splitting K inside a cluster instead.
     TILE_M = (128, 256)
     TILE_N = (64, 128, 256)
     TILE_K = (32, 64)
