@@ -43,7 +43,8 @@ sys.path.insert(0, str(ROOT))
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes per launch of the dominant kernel from one ncu capture each
 # (dram__bytes_read.sum + dram__bytes_write.sum, see profiles/); None = not captured.
-NCU_TRAFFIC = {"c1": None, "c2": 395.1e6, "c3": 25.9e6, "c4": None, "c4a": 488.1e6, "c5": None}
+NCU_TRAFFIC = {"c1": None, "c2": 332.5e6, "c3": 25.9e6, "c4": None, "c4a": 488.1e6, "c5": None,
+               "pad512": None, "relu512": None}
 
 
 def measured_peaks() -> dict:
