@@ -43,7 +43,7 @@ sys.path.insert(0, str(ROOT))
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes per launch of the dominant kernel from one ncu capture each
 # (dram__bytes_read.sum + dram__bytes_write.sum, see profiles/); None = not captured.
-NCU_TRAFFIC = {"c1": None, "c2": 332.5e6, "c3": 25.9e6, "c4": None, "c4a": 488.1e6, "c5": None,
+NCU_TRAFFIC = {"c1": None, "c2": 327.6e6, "c3": 25.9e6, "c4": None, "c4a": 488.1e6, "c5": None,
                "pad512": None, "relu512": None}
 
 
@@ -650,6 +650,7 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
     stream = torch.cuda.current_stream().cuda_stream
     sampler = ClockSampler(local_rank)
     checks: dict = {}
+    nccl_rows = None
 
     def barrier() -> None:
         dist.barrier()
@@ -696,8 +697,11 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
                         f"write each C tile into every rank's C over NVLink, {how} (fused all-gather)"
                         if world > 1 else "one rank holds all rows (no exchange)")
         else:
-            op = RowShardedMatmul(c_full, world, rank, compute, chunks=args.chunks)
-            sharding = f"rows of A and C split over {world} ranks, B replicated, NCCL all-gather of C"
+            from xtc_b200.dist import NcclRows
+            nccl_rows = NcclRows(dev, world, rank) if world > 1 else None
+            op = RowShardedMatmul(c_full, world, rank, compute, chunks=args.chunks, comm=nccl_rows)
+            sharding = (f"rows of A and C split over {world} ranks, B replicated, NCCL all-gather of C "
+                        "(xtc_cuda_allgather_rows)")
         step = lambda i: op.step(stream)
         total_flops = 2 * M * N * K
         local_cfg = cfg
@@ -877,6 +881,9 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
     if workload == "c5" and peer_op is not None:
         loop.close()
         peer_op.close()
+    if nccl_rows is not None:
+        dist.barrier()
+        nccl_rows.close()
     dist.destroy_process_group()
 
 

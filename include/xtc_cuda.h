@@ -115,7 +115,9 @@ typedef struct xtc_cuda_gemm_config {
   int32_t variant;   /* conv2d: 0 = auto; 1 = im2col fetch per filter tap;
                         2 = resident weights + halo tiles (stride 1 only);
                         3 = the same with two filter taps per MMA (at most 64
-                        filters, filter rows of two taps or more)                 */
+                        filters, filter rows of two taps or more).
+                        GEMM with tile_m = 256: 2 = store C without the L2
+                        evict-first hint (the default hints it)                   */
   int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off unless
                         the whole config is zero, when the library decides.  2, 4 or 8
                         pieces of a tile at most 128 columns wide, N a multiple of 4, C
@@ -185,6 +187,29 @@ int xtc_cuda_gemm_f32_mcast(const float* A, const float* B, float* C, float* mca
 int xtc_cuda_ipc_export(void* device_ptr, void* handle64);
 int xtc_cuda_ipc_import(const void* handle64, void** device_ptr);
 int xtc_cuda_ipc_release(void* device_ptr);
+
+/* The library all-gather of a row-sharded matmul, for hosts that keep the GEMM
+ * and the exchange apart instead of using xtc_cuda_gemm_f32_bcast: NCCL, one
+ * process per GPU.  Rank 0 fills a 128-byte identifier with
+ * xtc_cuda_comm_unique_id and hands it to the other ranks by the host's own
+ * channel; every rank then calls xtc_cuda_comm_init (collective; the calling
+ * thread's current device is the rank's GPU).  xtc_cuda_allgather_rows works in
+ * place on a buffer of world x rows_per_rank rows of row_bytes bytes that every
+ * rank holds: rank r owns rows [r * rows_per_rank, (r + 1) * rows_per_rank), and
+ * the call delivers rows [row_lo, row_hi) OF EVERY RANK'S BLOCK (block-relative
+ * numbers) to all ranks, stream-ordered.  The whole block (0, rows_per_rank) is
+ * one ncclAllGather; a sub-range, which lets the host overlap the exchange of
+ * finished row chunks with the GEMM of the next, is one grouped broadcast per
+ * owner.  NCCL is loaded with dlopen at the first call (libnccl.so.2; the copy
+ * already in the process, if any): without it these calls return
+ * XTC_CUDA_ERR_UNSUPPORTED and nothing else in the library is affected.
+ * The reference has no multi-GPU execution (GPUDevice.py:95-97, as above). */
+typedef struct xtc_cuda_comm xtc_cuda_comm;
+int xtc_cuda_comm_unique_id(void* id128);
+int xtc_cuda_comm_init(xtc_cuda_comm** comm, int world, int rank, const void* id128);
+int xtc_cuda_allgather_rows(xtc_cuda_comm* comm, void* c, int64_t rows_per_rank,
+                            int64_t row_bytes, int64_t row_lo, int64_t row_hi, void* stream);
+int xtc_cuda_comm_destroy(xtc_cuda_comm* comm);
 
 /* The 3xTF32 GEMM for callers that must not allocate device memory.  This entry
  * point has no counterpart in the reference.

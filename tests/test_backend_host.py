@@ -274,6 +274,21 @@ def test_plan_clears_every_split_k_counter(cuda_lib):
     assert total.value > 0 and zeroed.value == 0
 
 
+def test_row_exchange_entry_points_check_their_arguments(cuda_lib):
+    """xtc_cuda_comm_* / xtc_cuda_allgather_rows refuse bad arguments before NCCL is loaded
+    or a device is touched."""
+    handle = ctypes.c_void_p()
+    ident = ctypes.create_string_buffer(128)
+    assert cuda_lib.xtc_cuda_comm_unique_id(None) == capi.ERR_INVALID
+    assert cuda_lib.xtc_cuda_comm_init(None, 2, 0, ident) == capi.ERR_INVALID
+    assert cuda_lib.xtc_cuda_comm_init(ctypes.byref(handle), 2, 2, ident) == capi.ERR_INVALID
+    assert "rank 2 of 2" in capi.last_error() and not handle.value
+    assert cuda_lib.xtc_cuda_comm_init(ctypes.byref(handle), 2, 0, None) == capi.ERR_INVALID
+    assert cuda_lib.xtc_cuda_allgather_rows(None, 1, 4, 16, 0, 4, None) == capi.ERR_INVALID
+    assert "NULL communicator" in capi.last_error()
+    assert cuda_lib.xtc_cuda_comm_destroy(None) == capi.OK
+
+
 def test_counters_library_exports_every_declared_symbol(cuda_lib):
     """include/xtc_cuda_counters.h against the built CUPTI module and its ctypes binding."""
     from xtc_b200.runtimes import counters as gc

@@ -45,7 +45,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     from oracle import xtc_oracle as xo
     from xtc_b200 import capi, configs
     from xtc_b200.backends.cuda.module import PlanHandle
-    from xtc_b200.dist import PeerStoreMatmul, RowShardedMatmul
+    from xtc_b200.dist import NcclRows, PeerStoreMatmul, RowShardedMatmul, chunk_ranges
     from xtc_b200.runtimes.cuda import CudaDevice
 
     torch.cuda.set_device(rank)
@@ -84,6 +84,24 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         RowShardedMatmul(c_full, world, rank, compute).step(stream)
         torch.cuda.synchronize()
         assert np.array_equal(c_full.cpu().numpy(), single)
+
+        # ---- the same exchange through the C ABI's own NCCL communicator ----------------
+        comm = NcclRows(dev, world, rank)
+        c_full.zero_()
+        RowShardedMatmul(c_full, world, rank, compute, comm=comm).step(stream)
+        torch.cuda.synchronize()
+        assert np.array_equal(c_full.cpu().numpy(), single)
+        # ... and in three row ranges of every block (what a chunked overlap issues)
+        c_full.zero_()
+        compute(rank * rows, (rank + 1) * rows, stream)
+        for lo, hi in chunk_ranges(0, rows, 3):
+            comm.allgather_rows(c_full.data_ptr(), rows, n * 4, lo, hi, stream)
+        torch.cuda.synchronize()
+        assert np.array_equal(c_full.cpu().numpy(), single)
+        with pytest.raises(RuntimeError, match="rows"):
+            comm.allgather_rows(c_full.data_ptr(), rows, n * 4, 0, rows + 1, stream)
+        dist.barrier()
+        comm.close()
 
         # ---- fused peer stores -----------------------------------------------------
         pair_cfg = dict(module.plan.steps[-1].config)

@@ -134,6 +134,12 @@ SIGNATURES: dict[str, tuple] = {
     "xtc_cuda_ipc_export": (c_int, [c_void_p, c_void_p]),
     "xtc_cuda_ipc_import": (c_int, [c_void_p, POINTER(c_void_p)]),
     "xtc_cuda_ipc_release": (c_int, [c_void_p]),
+    "xtc_cuda_comm_unique_id": (c_int, [c_void_p]),
+    "xtc_cuda_comm_init": (c_int, [POINTER(c_void_p), c_int, c_int, c_void_p]),
+    "xtc_cuda_allgather_rows": (
+        c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p],
+    ),
+    "xtc_cuda_comm_destroy": (c_int, [c_void_p]),
     "xtc_cuda_gemm_f32_3xtf32_noalloc": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_float, c_void_p],

@@ -136,9 +136,27 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------ producer --------------------------------
-    // The filter bank, once: one thread announces the bytes, then every lane issues its share
-    // of the copies (issuing them all from one thread takes longer than they take to arrive).
-    if (lane == 0) mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(p.taps * p.nblk * WBLOCK));
+    // The first tile's halo copies go out before anything else: they come from DRAM (the
+    // input of a step is cold) while the filter bank comes from L2, and the first MMA needs
+    // both.  Every stage is free at this point, so nothing is waited for.
+    const int first_slabs = p.nslab < p.stages ? p.nslab : p.stages;
+    auto issue_halo = [&](int tile, int slab, int stage) {
+      const long long q0 = static_cast<long long>(tile) * BM;
+      const int img = static_cast<int>(q0 / plane);
+      const int rem = static_cast<int>(q0 - static_cast<long long>(img) * plane);
+      const int ih = rem / p.Wp - p.pad_top;
+      const int iw = rem % p.Wp - p.pad_left;
+      mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(p.stage_tx));
+      tma_load_im2col_4d(ring + static_cast<size_t>(stage) * p.stage_bytes, &tmX, &full[stage],
+                         slab * SLAB, iw, ih, img, 0, 0);
+    };
+    if (lane == 0) {
+      for (int slab = 0; slab < first_slabs; ++slab) issue_halo(blockIdx.x, slab, slab);
+      // The filter bank, once: one thread announces the bytes, then every lane issues its
+      // share of the copies (issuing them all from one thread takes longer than they take to
+      // arrive).
+      mbar_arrive_expect_tx(wbar, static_cast<uint32_t>(p.taps * p.nblk * WBLOCK));
+    }
     __syncwarp();
     {
       const int copies = p.taps * p.nblk * (BN / 32);
@@ -155,22 +173,18 @@ conv2d_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       XTC_TRACE_MARK();  // start
       int stage = 0;
       uint32_t phase = 0;
+      int issued = 0;  // copies counted so far; the first `first_slabs` are already out
       for (int tile = blockIdx.x; tile < p.tiles && !failed; tile += gridDim.x) {
-        const long long q0 = static_cast<long long>(tile) * BM;
-        const int img = static_cast<int>(q0 / plane);
-        const int rem = static_cast<int>(q0 - static_cast<long long>(img) * plane);
-        const int ih = rem / p.Wp - p.pad_top;
-        const int iw = rem % p.Wp - p.pad_left;
-        for (int slab = 0; slab < p.nslab; ++slab) {
-          if (!mbar_wait(&empty[stage], phase ^ 1)) {
-            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
-            failed = true;
-            break;
+        for (int slab = 0; slab < p.nslab; ++slab, ++issued) {
+          if (issued >= first_slabs) {
+            if (!mbar_wait(&empty[stage], phase ^ 1)) {
+              atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
+              failed = true;
+              break;
+            }
+            XTC_TRACE_MARK();  // stage free: load issued
+            issue_halo(tile, slab, stage);
           }
-          XTC_TRACE_MARK();  // stage free: load issued
-          mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(p.stage_tx));
-          tma_load_im2col_4d(ring + static_cast<size_t>(stage) * p.stage_bytes, &tmX, &full[stage],
-                             slab * SLAB, iw, ih, img, 0, 0);
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;

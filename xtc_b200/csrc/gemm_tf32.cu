@@ -88,6 +88,7 @@ struct LaunchArgs {
   float* extra[7] = {};
   float* mcast = nullptr;  // this rank's block of C through a multicast mapping (CTA-pair kernel)
   bool copier_warps = true;  // CTA-pair kernel: peers written by copier warps, not by the epilogue
+  bool c_evict_first = true;  // CTA-pair kernel: L2 evict-first hint on the stores of C
   int split_k = 1;        // CTAs per output tile along K (needs partials + counters)
   float* partials = nullptr;
   int* counters = nullptr;
@@ -231,6 +232,7 @@ int launch_pair(const LaunchArgs& a) {
   p.n_extra = a.n_extra;
   for (int d = 0; d < p.n_extra; ++d) p.extra_dst[d] = a.extra[d];
   p.mc_dst = a.mcast;
+  p.c_evict_first = a.n_extra == 0 && a.mcast == nullptr && a.c_evict_first;
 
   auto kernel = gemm_tf32_pair_kernel<BN, KSPANS, A_MN, B_MN>;
   const int smem = L::total(stages);
@@ -586,6 +588,7 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   a.thr = relu_threshold;
   a.stages = c.stages;
   a.stream = static_cast<cudaStream_t>(stream);
+  a.c_evict_first = c.variant != 2;
 
   const bool tma_ok = tma_addressable(A, lda) && tma_addressable(B, ldb);
   if (n_extra > 0) {

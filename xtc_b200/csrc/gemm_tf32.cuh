@@ -56,6 +56,10 @@ struct GemmParams {
   // bound to, so ONE multimem.st per vector reaches every GPU (the NVSwitch replicates it)
   // where the unicast form issues one store per peer.  NULL = unicast stores to extra_dst.
   float* mc_dst;
+  // CTA-pair kernel: the TMA stores of C carry an L2 evict-first hint, so that the output
+  // passing through L2 pushes out as little of the operand panels the wave still re-reads
+  // as possible.  Off when copier warps read the finished tiles back from L2.
+  int c_evict_first;
   // Split-K (small problems with fewer tiles than SMs): `split_k` CTAs share one
   // output tile, each over `split_kblocks` K stages.  Every CTA writes its raw
   // partial tile to `partials` [split][tile][128][BN]; the last one to arrive on

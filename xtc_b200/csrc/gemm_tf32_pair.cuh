@@ -297,6 +297,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const int quad = warp & 3;
     const int epi_id = warp - 2;
     float* stage_buf = reinterpret_cast<float*>(epi + epi_id * (2 * 32 * 32 * 4));
+    const uint64_t store_policy = l2_policy_evict_first();
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     int local = 0;
     int buf = 0;
@@ -377,8 +378,12 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M)
-          tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
+        if (lane == 0 && col0 < p.N && m0 + quad * 32 < p.M) {
+          if (p.c_evict_first)
+            tma_store_2d_hint(&tmC, sb, col0, m0 + quad * 32, store_policy);
+          else
+            tma_store_2d(&tmC, sb, col0, m0 + quad * 32);
+        }
         if (lane == 0) tma_store_commit();
         if (p.n_extra > 0 && !copiers) {
           const int chunk = lane & 7;

@@ -41,6 +41,47 @@ def chunk_ranges(start: int, stop: int, chunks: int) -> list[tuple[int, int]]:
     return out
 
 
+class NcclRows:
+    """The NCCL communicator of the C ABI (``xtc_cuda_comm_*``, ``xtc_cuda_allgather_rows``):
+    what a host without torch would use for the row exchange.  Rank 0 creates the 128-byte
+    identifier; here it travels to the other ranks over the torch process group, which is
+    only the out-of-band channel."""
+
+    def __init__(self, device: Any, world: int, rank: int, group: Any = None) -> None:
+        import ctypes
+
+        import torch.distributed as dist
+
+        from . import capi
+
+        self._capi = capi
+        self.lib = device.lib
+        self.world, self.rank = world, rank
+        ident = ctypes.create_string_buffer(128)
+        if rank == 0:
+            capi.check(self.lib.xtc_cuda_comm_unique_id(ident))
+        box = [ident.raw]
+        if world > 1:
+            dist.broadcast_object_list(box, src=0, group=group)
+        ident = ctypes.create_string_buffer(box[0], 128)
+        device.activate()
+        handle = ctypes.c_void_p()
+        capi.check(self.lib.xtc_cuda_comm_init(ctypes.byref(handle), world, rank, ident))
+        self._handle = handle
+
+    def allgather_rows(self, ptr: int, rows_per_rank: int, row_bytes: int, lo: int = 0,
+                       hi: int | None = None, stream: Any = None) -> None:
+        """Rows [lo, hi) of every rank's block (block-relative) to all ranks, in place."""
+        hi = rows_per_rank if hi is None else hi
+        self._capi.check(self.lib.xtc_cuda_allgather_rows(
+            self._handle, ptr, rows_per_rank, row_bytes, lo, hi, stream))
+
+    def close(self) -> None:
+        if self._handle:
+            self._capi.check(self.lib.xtc_cuda_comm_destroy(self._handle))
+            self._handle = None
+
+
 @dataclass
 class RowShardedMatmul:
     """C[M,N] = A[M,K] @ B[K,N] with A and C row-sharded over the process group.
@@ -48,6 +89,9 @@ class RowShardedMatmul:
     ``compute(row_lo, row_hi, stream)`` must write rows [row_lo, row_hi) of
     ``c_full`` (it is given global row numbers; the caller maps them onto its
     local A block).  ``c_full`` is a torch tensor [M, N] present on every rank.
+    The exchange is torch.distributed's all-gather or, when ``comm`` is an
+    ``NcclRows``, the C ABI's ``xtc_cuda_allgather_rows`` on the stream given to
+    ``step`` (which must then be torch's current stream when ``chunks > 1``).
     """
 
     c_full: Any
@@ -56,6 +100,7 @@ class RowShardedMatmul:
     compute: Callable[[int, int, Any], None]
     group: Any = None
     chunks: int = 1
+    comm: Any = None
 
     def __post_init__(self) -> None:
         m = self.c_full.shape[0]
@@ -65,10 +110,17 @@ class RowShardedMatmul:
         self.row_lo = self.rank * self.rows
         self._comm_stream = None
 
-    def _exchange_all(self) -> None:
+    def _row_bytes(self) -> int:
+        return self.c_full.shape[1] * self.c_full.element_size()
+
+    def _exchange_all(self, stream: Any = None) -> None:
         import torch.distributed as dist
 
         if self.world == 1:
+            return
+        if self.comm is not None:
+            self.comm.allgather_rows(self.c_full.data_ptr(), self.rows, self._row_bytes(),
+                                     stream=stream)
             return
         mine = self.c_full[self.row_lo : self.row_lo + self.rows]
         dist.all_gather_into_tensor(self.c_full, mine, group=self.group)
@@ -80,6 +132,10 @@ class RowShardedMatmul:
 
         ops = []
         off_lo, off_hi = lo - self.row_lo, hi - self.row_lo
+        if self.comm is not None:
+            self.comm.allgather_rows(self.c_full.data_ptr(), self.rows, self._row_bytes(), off_lo,
+                                     off_hi, stream=self._comm_stream.cuda_stream)
+            return []
         for peer in range(self.world):
             if peer == self.rank:
                 continue
@@ -94,7 +150,7 @@ class RowShardedMatmul:
         On return the work is enqueued (GPU) or done (CPU)."""
         if self.chunks <= 1 or self.world == 1:
             self.compute(self.row_lo, self.row_lo + self.rows, stream)
-            self._exchange_all()
+            self._exchange_all(stream)
             return
         import torch
 
