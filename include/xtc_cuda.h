@@ -253,7 +253,18 @@ int xtc_cuda_gemm_f32_3xtf32_noalloc(const float* A, const float* B, float* C, i
  * into the operand fetch (the reference needs a separate O.pad node for it).
  * Replaces the 7-D linalg.generic of src/xtc/backends/mlir/MlirOps.py:331-420;
  * semantics src/xtc/graphs/xtc/operators.py:252-347 and, for the fused pad,
- * operators.py:350-433 with constant_value == 0. */
+ * operators.py:350-433 with constant_value == 0.
+ * `workspace` (size from xtc_cuda_conv2d_workspace_bytes for the same shape and
+ * cfg; zeroed before its first use, may be reused by later calls) serves two
+ * things: the partial sums of a split of K the library chose, and, for thin
+ * inputs (C not a multiple of 4, or at most 8 channels where the
+ * resident-weights kernel does not apply, with nothing named in cfg), the
+ * packed form of the layer: the S*C values a filter row needs per output
+ * position are contiguous in NHWC, so they are gathered into
+ * P[B, H, OW, ceil4(S*C)] and the layer runs as an R x 1 convolution on the
+ * tensor cores (K = 7 x 32 for a 7x7 filter on 3 channels, where one K block
+ * per tap would be 49 x 32).  Without the workspace the call still succeeds:
+ * unsplit, and thin inputs with C % 4 != 0 on a CUDA-core kernel. */
 int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* Y, int64_t B, int64_t H,
                              int64_t W, int64_t C, int64_t R, int64_t S, int64_t F, int stride_h,
                              int stride_w, int pad_top, int pad_bottom, int pad_left,

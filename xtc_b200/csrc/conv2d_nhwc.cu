@@ -63,6 +63,62 @@ conv2d_direct_kernel(const float* __restrict__ X, const float* __restrict__ Wt,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Thin inputs (a few channels: the first layer of an image network)
+// ---------------------------------------------------------------------------
+// With C channels the tensor-core kernels spend a K block of 32 on every filter tap, so a
+// 7x7 filter on 3 channels would multiply 49 x 32 = 1568 deep for 147 values (and C = 3 is
+// not addressable by TMA at all: a pixel is 12 bytes).  In NHWC the S*C values a filter row
+// needs for one output position are CONTIGUOUS in the input row, so the layer is rewritten
+// as a convolution with an R x 1 filter on a packed input
+//
+//   P[b, h, ow, k] = X[b, h, ow*sw - pad_left + k / C, k % C]   (k < S*C, else 0; 0 outside)
+//   V[r, 0, k, f]  = W[r, k / C, k % C, f]                      (k < S*C, else 0)
+//   Y = conv(P, V, stride (sh, 1), padding (top, bottom, 0, 0))
+//
+// with KR = S*C rounded up to 4 channels: K = R * ceil(KR / 32) * 32 (224 for the 7x7x3
+// layer).  P costs one pass over B*H*OW*KR floats, written 16 bytes per thread.
+__global__ void __launch_bounds__(256)
+conv2d_pack_rows_kernel(const float* __restrict__ X, float* __restrict__ P, int rows, int W, int C,
+                        int OW, int KR4, int valid, int sw, int pl, const float* __restrict__ Wt,
+                        float* __restrict__ V, int filter_total, int F) {
+  // the convolution that follows is launched with programmatic stream serialisation: let its
+  // CTAs set themselves up while this kernel runs (they wait for its memory before reading)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (blockIdx.y == gridDim.y - 1) {
+    // the last row of blocks packs the filter: V[r, k, f] = W[r, k, f] for k < S*C, else 0
+    const int KR = KR4 * 4;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < filter_total; i += gridDim.x * blockDim.x) {
+      const int f = i % F;
+      const int rk = i / F;
+      const int k = rk % KR;
+      const int r = rk / KR;
+      V[i] = k < valid ? __ldg(Wt + (static_cast<int64_t>(r) * valid + k) * F + f) : 0.f;
+    }
+    return;
+  }
+  // blockIdx.y walks the B*H input rows, blockIdx.x * 256 + threadIdx.x the OW * KR4 groups of
+  // four packed values of one row: all index arithmetic stays in 32 bits
+  const int per_row = OW * KR4;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= per_row) return;
+  const int ow = i / KR4;
+  const int k0 = (i - ow * KR4) * 4;
+  const int row_len = W * C;
+  const int e0 = (ow * sw - pl) * C + k0;  // element k of the packed pixel is element e0 + k of the row
+  for (int row = blockIdx.y; row < rows; row += gridDim.y - 1) {
+    const float* xr = X + static_cast<int64_t>(row) * row_len;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = e0 + j;
+      v[j] = (k0 + j < valid && e >= 0 && e < row_len) ? __ldg(xr + e) : 0.f;
+    }
+    reinterpret_cast<float4*>(P)[static_cast<int64_t>(row) * per_row + i] =
+        make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
 namespace {
 
 int make_tmap_im2col(CUtensorMap* map, const ConvArgs& a, uint32_t pixels) {
@@ -411,6 +467,44 @@ static bool conv_names_nothing(const xtc_cuda_gemm_config& c) {
          c.tile_k == 0 && c.split_k == 0;
 }
 
+// The packed form of a thin-input layer (see conv2d_pack_rows_kernel): whether it applies and
+// how much workspace the packed input and filter take (each rounded up to 256 bytes).
+struct ThinPlan {
+  bool ok = false;
+  int64_t KR = 0, OW = 0;
+  size_t p_bytes = 0, v_bytes = 0;
+};
+static ThinPlan plan_thin(int64_t B, int64_t H, int64_t W, int64_t C, int64_t R, int64_t S, int64_t F,
+                          int sh, int sw, int pt, int pb, int pl, int pr,
+                          const xtc_cuda_gemm_config& c) {
+  ThinPlan t;
+  // layers the tensor-core kernels cannot address (C not a multiple of 4), and aligned ones of
+  // at most 8 channels when the caller named no kernel parameter
+  bool thin = C % 4 != 0;
+  if (!thin && C <= 8 && S > 1) {
+    // aligned and thin: the resident-weights kernel is the faster where it applies (stride 1;
+    // 32x58x58x8 -> 64, 3x3: 12.6 us against 22.6 us packed), the packed form elsewhere
+    // (453x453x8 -> 64, 7x7 stride 2: 33.3 us against 57.6 us)
+    ConvArgs a;
+    memset(&a, 0, sizeof(a));
+    a.B = B; a.H = H; a.W = W; a.C = C; a.R = R; a.S = S; a.F = F;
+    a.sh = sh; a.sw = sw; a.pt = pt; a.pb = pb; a.pl = pl; a.pr = pr;
+    thin = !(plan_halo(a, false, 32).ok || plan_halo(a, false, 16).ok || plan_halo(a, true, 32).ok);
+  }
+  if (B * H > 0x7fffffff || W * C > 0x3fffffff || R * ((S * C + 3) / 4 * 4) * F > 0x7fffffff) return t;
+  if (!thin || c.precision != XTC_CUDA_PRECISION_TF32 || F % 4 != 0 || S * C > 1024 || R > 120 ||
+      !(c.variant == 0 && c.tile_m == 0 && c.tile_n == 0 && c.tile_k == 0 && c.split_k == 0))
+    return t;
+  t.OW = (W + pl + pr - S) / sw + 1;
+  if (t.OW <= 0 || t.OW > 65535 || H > 65535) return t;
+  t.KR = (S * C + 3) / 4 * 4;
+  const size_t round = 255;
+  t.p_bytes = (static_cast<size_t>(B * H * t.OW * t.KR) * 4 + round) & ~round;
+  t.v_bytes = (static_cast<size_t>(R * t.KR * F) * 4 + round) & ~round;
+  t.ok = true;
+  return t;
+}
+
 extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, int64_t C, int64_t R,
                                                int64_t S, int64_t F, int stride_h, int stride_w,
                                                int pad_top, int pad_bottom, int pad_left,
@@ -431,6 +525,14 @@ extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, 
       pad_top + pad_bottom + pad_left + pad_right == 0 && c.variant == 0 &&
       c.precision != XTC_CUDA_PRECISION_3XTF32)
     return xtc_cuda_gemm_workspace_bytes(M, F, C, 0, &c, bytes);
+  if (const ThinPlan t = plan_thin(B, H, W, C, R, S, F, stride_h, stride_w, pad_top, pad_bottom, pad_left, pad_right, c); t.ok) {
+    size_t inner = 0;
+    const int rc = xtc_cuda_conv2d_workspace_bytes(B, H, t.OW, t.KR, R, 1, F, stride_h, 1, pad_top,
+                                                   pad_bottom, 0, 0, nullptr, &inner);
+    if (rc != XTC_CUDA_OK) return rc;
+    *bytes = t.p_bytes + t.v_bytes + inner;
+    return XTC_CUDA_OK;
+  }
   if (!conv_names_nothing(c)) return XTC_CUDA_OK;
   ConvArgs a;
   memset(&a, 0, sizeof(a));
@@ -492,6 +594,29 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
                              &c, workspace, workspace_bytes, stream);
   // The tensor-core path needs TMA-addressable operands, a unit or small
   // traversal stride, and corner offsets within the im2col descriptor's range.
+  // Thin inputs: pack filter rows and run the R x 1 layer on the tensor cores, when the caller
+  // brought the workspace for it (xtc_cuda_conv2d_workspace_bytes); without, the layer runs as
+  // it did (the CUDA-core kernel when C is not a multiple of 4).
+  if (const ThinPlan t = plan_thin(B, H, W, C, R, S, F, stride_h, stride_w, pad_top, pad_bottom, pad_left, pad_right, c);
+      t.ok && workspace != nullptr && workspace_bytes >= t.p_bytes + t.v_bytes &&
+      (reinterpret_cast<uintptr_t>(workspace) & 15) == 0 && a16(Y)) {
+    float* P = static_cast<float*>(workspace);
+    float* V = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + t.p_bytes);
+    const int64_t rows = B * H;
+    const int per_row = static_cast<int>(t.OW * (t.KR / 4));
+    // one launch: B*H rows of blocks pack the input, one more row of blocks packs the filter
+    const dim3 pack_grid(static_cast<unsigned>((per_row + 255) / 256),
+                         static_cast<unsigned>((rows < 65534 ? rows : 65534) + 1));
+    conv2d_pack_rows_kernel<<<pack_grid, 256, 0, a.stream>>>(
+        X, P, static_cast<int>(rows), static_cast<int>(W), static_cast<int>(C), static_cast<int>(t.OW),
+        static_cast<int>(t.KR / 4), static_cast<int>(S * C), stride_w, pad_left, Wt, V,
+        static_cast<int>(R * t.KR * F), static_cast<int>(F));
+    XTC_CUDA_CHECK(cudaGetLastError());
+    uint8_t* rest = static_cast<uint8_t*>(workspace) + t.p_bytes + t.v_bytes;
+    return xtc_cuda_conv2d_nhwc_f32(P, V, Y, B, H, t.OW, t.KR, R, 1, F, stride_h, 1, pad_top, pad_bottom,
+                                    0, 0, flags, relu_threshold, nullptr, rest,
+                                    workspace_bytes - t.p_bytes - t.v_bytes, stream);
+  }
   const bool tc_ok = c.precision == XTC_CUDA_PRECISION_TF32 && C % 4 == 0 && F % 4 == 0 &&
                      a16(X) && a16(Wt) && stride_h <= 8 && stride_w <= 8 && pad_top <= 127 &&
                      pad_left <= 127 && pad_right <= 127 && pad_bottom <= 127 && S <= 120 &&
