@@ -264,25 +264,29 @@ int launch_pair(const LaunchArgs& a) {
     configured_smem = smem;
   }
   const int tiles = p.tiles_m * p.tiles_n;
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  int pairs = tiles < max_pairs ? tiles : max_pairs;
   p.group_n = panel_columns(pairs, 2 * BM, BN, p.tiles_n);
   // Split tail: the tiles of a last round that would leave at least half of the
-  // pairs idle are cut along K, one piece per pair (see gemm_tf32_pair.cuh).
+  // pairs idle are cut along K, one piece per pair (see gemm_tf32_pair.cuh).  A problem of
+  // fewer tiles than half the pairs (few rows, long K: 256 x 3072 x 8192 is 12 tiles) is
+  // such a round as a whole.
   const int rem = tiles % pairs;
-  const int split = rem > 0 ? pairs / rem : 0;
+  const bool whole = tiles * 2 <= max_pairs;
+  const int split = whole ? max_pairs / tiles : (rem > 0 ? pairs / rem : 0);
   // (each piece keeps at least 1024 of K: parking and re-reading a 256 x BN accumulator
   // costs more than a shorter piece saves)
   const int max_split = static_cast<int>(a.K / 1024);
-  if (a.pair_tail != nullptr && tiles > pairs && split >= 2 && max_split >= 2 &&
-      pairs <= sm_count(dev) / 2) {
+  if (a.pair_tail != nullptr && (whole || tiles > pairs) && split >= 2 && max_split >= 2 &&
+      max_pairs <= sm_count(dev) / 2) {
     p.tail_split = split < max_split ? split : max_split;
     if (p.tail_split > p.k_blocks) p.tail_split = p.k_blocks;
-    p.tail_tiles = rem;
-    p.tail_first = tiles - rem;
+    p.tail_tiles = whole ? tiles : rem;
+    p.tail_first = tiles - p.tail_tiles;
     p.sk_flags = static_cast<int*>(a.pair_tail);
     p.sk_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a.pair_tail) +
                                              pair_tail_flag_bytes(sm_count(dev) / 2));
     if (p.tail_split < 2) p.tail_split = 0;
+    else if (whole) pairs = tiles * p.tail_split;  // every piece on a pair of its own, all resident
   }
   const int threads =
       ((p.n_extra > 0 && a.copier_warps) || p.mc_dst != nullptr) ? PAIR_THREADS_BCAST : PAIR_THREADS;
@@ -446,16 +450,50 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
   // step is the epilogue and HBM, and the per-tile hand-offs of a CTA pair only cost
   // (100352x256x64: 33 us with pairs, 26 us with 128x256 tiles, at the HBM floor of 20 us;
   // 100352x64x256: 29 - 31 us against 24 us).
-  const bool skinny = K <= 256 && N <= 256;
+  const bool skinny = K <= 256;
+  // Few rows and a long K (a handful of token rows against a weight matrix): the step streams B
+  // from HBM once and no tile order gives the operands any reuse, so the cost model below, which
+  // counts tensor clocks, does not rank the shapes.  Measured instead (B200, us, M x N x K):
+  //   256 x 3072 x 8192: pairs 256x128 35.4 | pairs 256x256 49.9 | 128x128 in 2 pieces 45.1
+  //   256 x 8192 x 3072: pairs 256x128 29.2 | pairs 256x256 37.9 | 128x128 32.4
+  //   256 x 2048 x 8192: 128x128 in 4 pieces 24.5 | pairs 256x128 30.1
+  //   128 x 4096 x 8192: 128x128 in 4 pieces 29.4;  128 x 8192 x 4096: 128x64 31.7, 128x128 in 2 33.0
+  if (M <= 256 && K >= 2048 && N >= 1024) {
+    if (pair_ok && M > 128 && N >= 3072) return {256, 128, 64, 1};  // the pair kernel cuts K itself
+    const int64_t tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    int split = 1;
+    if (cluster_cap != nullptr && N % 4 == 0)
+      while (split < 8 && tiles * split * 2 <= sms && tiles <= cluster_cap[split * 2] &&
+             K / (split * 2) >= 1024)
+        split *= 2;
+    return {128, 128, 64, split};
+  }
   for (const Cand& c : cands) {
     if (c.tm == 256 && (!pair_ok || skinny)) continue;
     const int64_t tiles = ((M + c.tm - 1) / c.tm) * ((N + c.tn - 1) / c.tn);
     const int64_t slots = c.tm == 256 ? sms / 2 : sms;
     const int64_t full = tiles / slots, rem = tiles % slots;
     double rounds = static_cast<double>(full);
-    if (rem) rounds += (c.tm == 256 && full >= 1 && rem * 2 <= slots) ? 1.0 / static_cast<double>(slots / rem) : 1.0;
-    const int tile_k = c.tm == 256 ? (K >= 128 ? 64 : 32) : (c.tn == 64 && K >= 128 ? 64 : 32);
-    double t = rounds * ksteps * c.clk + fixed;
+    double tail_cost = 0.0;
+    if (rem) {
+      // the pair kernel cuts a last (or only) round that fills at most half of the pairs along
+      // K, at least 1024 per piece; one pair sums the parked pieces of a tile, about 2.3 us per
+      // piece of 256 x 256
+      int64_t pieces = (c.tm == 256 && split_ok && rem * 2 <= slots) ? slots / rem : 1;
+      if (pieces > K / 1024) pieces = K / 1024;
+      if (pieces >= 2) {
+        rounds += 1.0 / static_cast<double>(pieces);
+        tail_cost = (1.0 + 2.3 * static_cast<double>(pieces) * c.tn / 256.0) * clk_per_us;
+      } else {
+        rounds += 1.0;
+      }
+    }
+    // K per stage: 64 halves the barrier traffic; 256 x 256 pair tiles on few rows of tiles get
+    // 32 (six stages instead of three hide the HBM latency: 512 x 4096 x 8192 61.8 us against
+    // 68.2 us, 1024 x 4096 x 4096 53.0 us against 54.7 us)
+    const int tile_k = c.tm == 256 ? (K >= 128 && !(c.tn == 256 && M <= 1024) ? 64 : 32)
+                                   : ((c.tn == 64 || skinny) && K >= 128 ? 64 : 32);
+    double t = rounds * ksteps * c.clk + fixed + tail_cost;
     int split = 1;
     const int64_t kblocks = (K + tile_k - 1) / tile_k;
     if (cluster_cap != nullptr && c.tm == 128 && c.tn <= 128 && N % 4 == 0) {
