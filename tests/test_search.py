@@ -226,6 +226,25 @@ def test_conv_search_on_gpu_confirms_the_shipped_c3_schedule(tmp_path):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("operator,name", [
+    ("conv2d", "ResNet18_01"),    # 7x7 stride 2 on 3 channels: the packed thin-input form
+    ("conv2d", "SqueezeNet_03"),  # 16 channels, resident weights
+    ("conv2d", "MobilNet_09"),    # 7x7 pixels, K = 9216: split over clusters
+    ("matmul", "Gemma2B_QK"),     # 256 rows, K = 8192: few tiles, long K
+    ("matmul", "AlexNet_FC8"),    # one row
+])
+def test_named_layers_with_the_default_schedule_on_gpu(operator, name):
+    """Layers of the reference's tables (artifacts/operations.py) compiled with nothing named
+    and validated against the NumPy semantics of the graph."""
+    exp = Exploration(ExplorationConfig(operator=operator, op_name=name, peak_flops=1e15))
+    impl = Backend(exp.graph)
+    module = impl.get_compiler(shared_lib=False).compile(impl.get_scheduler().schedule())
+    results, code, msg = module.get_evaluator(validate=True, repeat=2, number=2, min_repeat_ms=0).evaluate()
+    assert code == 0, msg
+    assert all(t > 0 for t in results)
+
+
+@pytest.mark.gpu
 def test_iterative_search_and_database_on_gpu(tmp_path):
     from xtc_b200.search import read_db
 

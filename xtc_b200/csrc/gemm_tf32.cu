@@ -2,6 +2,7 @@
 #include <mutex>
 
 #include "gemm_tf32_pair.cuh"
+#include "gemm_thin_rows.cuh"
 
 namespace xtc {
 
@@ -365,6 +366,42 @@ int launch_simt(const LaunchArgs& a) {
   return XTC_CUDA_OK;
 }
 
+// A handful of rows (M <= 8): the matrix-vector kernel of gemm_thin_rows.cuh.
+template <int MT>
+int launch_thin_rows_mt(const LaunchArgs& a) {
+  ThinRowsParams p;
+  memset(&p, 0, sizeof(p));
+  p.A = a.A; p.B = a.B; p.C = a.C;
+  p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
+  p.lda = a.lda; p.ldb = a.ldb; p.ldc = a.ldc;
+  p.a_t = a.a_t; p.relu = a.relu; p.thr = a.thr;
+  const size_t smem = thin_rows_smem(MT, a.K);
+  auto kernel = gemm_thin_rows_kernel<MT>;
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  static thread_local int configured_dev = -1;
+  static thread_local size_t configured_smem = 0;
+  if (configured_dev != dev || configured_smem < smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(smem)));
+    configured_dev = dev;
+    configured_smem = smem;
+  }
+  const unsigned strips = static_cast<unsigned>((a.N + THIN_COLS - 1) / THIN_COLS);
+  XTC_CUDA_CHECK(launch_overlapped_clustered(kernel, strips * THIN_KSPLIT, THIN_KSPLIT, THIN_THREADS,
+                                             smem, a.stream, p));
+  return XTC_CUDA_OK;
+}
+int thin_rows_mt(int64_t M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
+int launch_thin_rows(const LaunchArgs& a) {
+  switch (thin_rows_mt(a.M)) {
+    case 1: return launch_thin_rows_mt<1>(a);
+    case 2: return launch_thin_rows_mt<2>(a);
+    case 4: return launch_thin_rows_mt<4>(a);
+    default: return launch_thin_rows_mt<8>(a);
+  }
+}
+
 bool tma_addressable(const void* p, int64_t ld) {
   return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld % 4) == 0;
 }
@@ -650,10 +687,15 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
     c.tile_m = 2 * BM;
     a.mcast = mcast;
   }
-  if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
-
   // Nothing named by the caller: the library picks kernel, tile and split itself.
   const bool full_auto = is_full_auto(c);
+  // at most 8 rows: a matrix-vector product per row, bound by reading B once
+  if (full_auto && M <= 8 && !b_t && n_extra == 0 && mcast == nullptr && N % 4 == 0 &&
+      tma_addressable(B, ldb) && tma_addressable(C, ldc) &&
+      thin_rows_smem(thin_rows_mt(M), K) <= 200 * 1024 && (N + THIN_COLS - 1) / THIN_COLS <= 65535)
+    return launch_thin_rows(a);
+  if (c.precision == XTC_CUDA_PRECISION_FP32_SIMT || !tma_ok) return launch_simt(a);
+
   if (full_auto) {
     int caps[9] = {};
     for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
