@@ -78,8 +78,11 @@ struct AutoChoice {
 };
 // `cluster_cap[s]` (s = 2, 4, 8; indexable to 8) = clusters of s single-CTA GEMM blocks the
 // device runs at once (cluster_capacity), NULL = do not consider a split inside a cluster.
+// `pair_tail_ok` = the CTA-pair kernel may cut the tiles of a partly idle round along K (the
+// GEMM's pair kernel does, given a workspace; the convolution's does not).
 AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
-                               bool split_ok, const int* cluster_cap = nullptr);
+                               bool split_ok, const int* cluster_cap = nullptr,
+                               bool pair_tail_ok = true);
 int cluster_capacity(int dev, int size);
 // Pieces (8, 4, 2, or 1 = do not split) a cluster split of `k_blocks` K stages runs with when
 // `want` were asked for: the largest power of two not above `want` whose pieces, of

@@ -548,7 +548,8 @@ extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, 
   int caps[9] = {};
   for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
   const AutoChoice pick =
-      choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sms, true, true, F % 4 == 0 ? caps : nullptr);
+      choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sms, true, true, F % 4 == 0 ? caps : nullptr,
+                          false);
   *bytes = conv_split_in_cluster(M, F, pick, dev) ? 0 : conv_split_bytes(M, F, pick);
   return XTC_CUDA_OK;
 }
@@ -678,7 +679,7 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     int caps[9] = {};
     for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
     AutoChoice pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), true,
-                                          a16(Y) && F % 4 == 0 ? caps : nullptr);
+                                          a16(Y) && F % 4 == 0 ? caps : nullptr, false);
     const size_t need = conv_split_bytes(M, F, pick);
     if (need > 0 && c.split_k == 0 && a16(Y) && conv_split_in_cluster(M, F, pick, dev)) {
       a.split_k = pick.split_k;
@@ -690,7 +691,7 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
       a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
                                             ((tiles * 4 + 255) & ~static_cast<size_t>(255)));
     } else if (need > 0) {
-      pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), false);
+      pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), false, nullptr, false);
     }
     tile_m = pick.tile_m;
     tile_n = pick.tile_n;

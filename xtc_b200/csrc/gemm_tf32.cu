@@ -474,7 +474,7 @@ int cluster_capacity(int dev, int size) {
 // Other splits go through a workspace (`split_ok`), which costs 3 us + 1.15 us per piece
 // for the reduction pass.
 AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
-                               bool split_ok, const int* cluster_cap) {
+                               bool split_ok, const int* cluster_cap, bool pair_tail_ok) {
   struct Cand { int tm, tn; double clk; };
   // on a tie the earlier candidate wins: one CTA per tile before CTA pairs
   static const Cand cands[] = {{128, 64, 96.0}, {128, 128, 128.0}, {128, 256, 192.0},
@@ -496,7 +496,8 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
   //   256 x 2048 x 8192: 128x128 in 4 pieces 24.5 | pairs 256x128 30.1
   //   128 x 4096 x 8192: 128x128 in 4 pieces 29.4;  128 x 8192 x 4096: 128x64 31.7, 128x128 in 2 33.0
   if (M <= 256 && K >= 2048 && N >= 1024) {
-    if (pair_ok && M > 128 && N >= 3072) return {256, 128, 64, 1};  // the pair kernel cuts K itself
+    if (pair_ok && pair_tail_ok && M > 128 && N >= 3072)
+      return {256, 128, 64, 1};  // the pair kernel cuts K itself
     const int64_t tiles = ((M + 127) / 128) * ((N + 127) / 128);
     int split = 1;
     if (cluster_cap != nullptr && N % 4 == 0)
@@ -516,7 +517,7 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
       // the pair kernel cuts a last (or only) round that fills at most half of the pairs along
       // K, at least 1024 per piece; one pair sums the parked pieces of a tile, about 2.3 us per
       // piece of 256 x 256
-      int64_t pieces = (c.tm == 256 && split_ok && rem * 2 <= slots) ? slots / rem : 1;
+      int64_t pieces = (c.tm == 256 && split_ok && pair_tail_ok && rem * 2 <= slots) ? slots / rem : 1;
       if (pieces > K / 1024) pieces = K / 1024;
       if (pieces >= 2) {
         rounds += 1.0 / static_cast<double>(pieces);
