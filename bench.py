@@ -8,7 +8,10 @@ one run of the compiled graph ("weak": the work per GPU is the whole graph).
 Launched by torch.distributed.run (any world size, 1 included): workload c5, the
 row-sharded 65536x8192x8192 matmul; one step = every rank computes its row block and
 the blocks are exchanged; the total work is fixed ("strong"), so the values at
-1, 2, 4 and 8 ranks are one curve.  Prints ONE JSON line on rank 0.
+1, 2, 4 and 8 ranks are one curve.  By default the exchange of a step (peer-to-peer
+copies, then a barrier) runs on a second stream while the next step's product is
+computed; every step's exchange has completed when the timed region ends.  Prints
+ONE JSON line on rank 0.
 
   value     graph throughput with inputs resident in device memory
   e2e       the same through host buffers: pinned host -> device copies of the
@@ -686,16 +689,24 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
                         configs.compile_config(ccfg, precision=args.precision).plan, dev)
         peer_op = None
         if args.exchange != "nccl":
-            from xtc_b200.dist import PeerStoreMatmul
+            from xtc_b200.dist import PeerStoreMatmul, PipelinedPeerMatmul
             gemm_cfg = dict(module.plan.steps[-1].config)
-            op = peer_op = PeerStoreMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
-                                           config=gemm_cfg,
-                                           exchange=args.exchange)
-            how = ("one multicast store per vector through an NVLink multicast object (NVLS)"
-                   if peer_op.exchange == "multimem" else "one 128-bit store per peer")
-            sharding = (f"rows of A and C split over {world} ranks, B replicated; copier warps of the GEMM "
-                        f"write each C tile into every rank's C over NVLink, {how} (fused all-gather)"
-                        if world > 1 else "one rank holds all rows (no exchange)")
+            if args.exchange in ("pipeline", "auto"):
+                op = peer_op = PipelinedPeerMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
+                                                   config=gemm_cfg)
+                sharding = (f"rows of A and C split over {world} ranks, B replicated; each rank's rows go to "
+                            "every peer's C by peer-to-peer copies (copy engines over NVLink) while the next "
+                            "step's GEMM runs (exchange one step behind, two C buffers)"
+                            if world > 1 else "one rank holds all rows (no exchange)")
+            else:
+                op = peer_op = PeerStoreMatmul(dev, a_blk.data_ptr(), b.data_ptr(), M, N, K, world, rank,
+                                               config=gemm_cfg,
+                                               exchange=args.exchange)
+                how = ("one multicast store per vector through an NVLink multicast object (NVLS)"
+                       if peer_op.exchange == "multimem" else "one 128-bit store per peer")
+                sharding = (f"rows of A and C split over {world} ranks, B replicated; copier warps of the GEMM "
+                            f"write each C tile into every rank's C over NVLink, {how} (fused all-gather)"
+                            if world > 1 else "one rank holds all rows (no exchange)")
         else:
             from xtc_b200.dist import NcclRows
             nccl_rows = NcclRows(dev, world, rank) if world > 1 else None
@@ -708,6 +719,8 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         h2d = a_blk.numel() * 4
         d2h = rows * N * 4
         launches = 1 if (args.chunks <= 1 or args.exchange != "nccl") else args.chunks
+        if world > 1 and args.exchange in ("pipeline", "auto"):
+            launches = 2  # the GEMM and the one-warp barrier; the copies are the copy engines'
         exchange_bytes = rows * N * 4 * (world - 1)  # the rank's block of C, to every other rank
     elif workload == "c3":
         sh = BatchSharded(32, world, rank)
@@ -780,7 +793,9 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         pin_a = torch.from_numpy(host_a).pin_memory()
         pin_c = torch.empty(rows, N).pin_memory()
         loop = peer_op.host_loop()
-        e2e_api = "PeerStoreMatmul.host_loop(): submit / wait (xtc_cuda_memcpy_*, events, xtc_cuda_gemm_f32_bcast)"
+        e2e_api = (f"{type(peer_op).__name__}.host_loop(): submit / wait (xtc_cuda_memcpy_*, events, "
+                   + ("xtc_cuda_gemm_f32 + peer copies + xtc_cuda_peer_barrier)"
+                      if args.exchange in ("pipeline", "auto") else "xtc_cuda_gemm_f32_bcast)"))
 
         def e2e_run(n: int) -> None:
             for _ in range(n):
@@ -911,10 +926,11 @@ def main() -> None:
     ap.add_argument("--unfused-transpose", action="store_true",
                     help="c4: run the transpose as its own kernel instead of reading A transposed")
     ap.add_argument("--chunks", type=int, default=1, help="row chunks overlapped with the exchange (N>1)")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "multimem", "peer", "nccl"],
-                    help="c5 at N>1: fused all-gather by one store per peer (peer), by NVLink multicast "
-                         "stores (multimem), the faster of the two as measured (auto = peer), or GEMM "
-                         "followed by an NCCL all-gather (nccl)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "multimem", "peer", "pipeline", "nccl"],
+                    help="c5 at N>1: the exchange one step behind the product, by peer-to-peer copies on "
+                         "the copy engines (pipeline; what auto picks: the fastest as measured on 2 and "
+                         "8 GPUs), the all-gather fused into the GEMM by one store per peer (peer) or by "
+                         "NVLink multicast stores (multimem), or GEMM followed by an NCCL all-gather (nccl)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-e2e", action="store_true",

@@ -211,6 +211,18 @@ int xtc_cuda_allgather_rows(xtc_cuda_comm* comm, void* c, int64_t rows_per_rank,
                             int64_t row_bytes, int64_t row_lo, int64_t row_hi, void* stream);
 int xtc_cuda_comm_destroy(xtc_cuda_comm* comm);
 
+/* A stream-ordered barrier between up to 8 GPUs of a box (one process each) that costs one
+ * warp: every rank holds an array of 8 ints (from xtc_cuda_malloc, zeroed once) and maps the
+ * peers' arrays with xtc_cuda_ipc_import.  The call stores `epoch` (increasing by one per
+ * barrier) into slot my_rank of every peer's array, after everything `stream` did before,
+ * peer-to-peer copies included, and makes `stream` wait until the local slots of all
+ * peer_ranks have reached it (a bounded wait, about 2 s: on giving up the kernel records
+ * XTC_CUDA_ERR_DEVICE_TIMEOUT's status and returns).  What follows on `stream` may read what the
+ * peers wrote into this GPU's memory before their barrier.  No reference counterpart (same
+ * remark as the other multi-GPU calls). */
+int xtc_cuda_peer_barrier(int* local_flags, int* const* peer_flags, const int* peer_ranks,
+                          int n_peers, int my_rank, int epoch, void* stream);
+
 /* The 3xTF32 GEMM for callers that must not allocate device memory.  This entry
  * point has no counterpart in the reference.
  *

@@ -287,6 +287,13 @@ def test_row_exchange_entry_points_check_their_arguments(cuda_lib):
     assert cuda_lib.xtc_cuda_allgather_rows(None, 1, 4, 16, 0, 4, None) == capi.ERR_INVALID
     assert "NULL communicator" in capi.last_error()
     assert cuda_lib.xtc_cuda_comm_destroy(None) == capi.OK
+    # the one-warp barrier: no peers is a no-op, more than 7 or a rank outside [0, 8) is refused
+    flags = (ctypes.c_void_p * 8)()
+    ranks = (ctypes.c_int * 8)(*range(1, 9))
+    assert cuda_lib.xtc_cuda_peer_barrier(None, flags, ranks, 0, 0, 1, None) == capi.OK
+    assert cuda_lib.xtc_cuda_peer_barrier(None, flags, ranks, 8, 0, 1, None) == capi.ERR_INVALID
+    assert cuda_lib.xtc_cuda_peer_barrier(None, flags, ranks, 2, 0, 1, None) == capi.ERR_INVALID
+    assert "NULL argument" in capi.last_error()
 
 
 def test_counters_library_exports_every_declared_symbol(cuda_lib):

@@ -45,7 +45,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     from oracle import xtc_oracle as xo
     from xtc_b200 import capi, configs
     from xtc_b200.backends.cuda.module import PlanHandle
-    from xtc_b200.dist import NcclRows, PeerStoreMatmul, RowShardedMatmul, chunk_ranges
+    from xtc_b200.dist import NcclRows, PeerStoreMatmul, PipelinedPeerMatmul, RowShardedMatmul, chunk_ranges
     from xtc_b200.runtimes.cuda import CudaDevice
 
     torch.cuda.set_device(rank)
@@ -137,6 +137,24 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         dist.barrier()
         assert np.array_equal(host_c.numpy(), single[rank * rows:(rank + 1) * rows])
         assert np.array_equal(op.result(), single), "peers' blocks arrived although no stream was current"
+        loop.close()
+        op.close()
+        assert dev.status() == 0
+        # ---- the exchange one step behind the product: peer copies on a second stream --------
+        op = PipelinedPeerMatmul(dev, a_blk.data_ptr(), b_dev.data_ptr(), m, n, k, world, rank, config=pair_cfg)
+        for _ in range(5):
+            op.step(stream)
+        assert np.array_equal(op.result(), single), "the last step's C, complete on every rank"
+        dist.barrier()
+        loop = op.host_loop()
+        host_c.fill_(float("nan"))
+        a_blk.zero_()
+        for _ in range(3):
+            loop.submit(host_a.data_ptr(), host_c.data_ptr())
+        loop.wait()
+        dist.barrier()
+        assert np.array_equal(host_c.numpy(), single[rank * rows:(rank + 1) * rows])
+        assert np.array_equal(op.result(), single)
         loop.close()
         op.close()
         assert dev.status() == 0

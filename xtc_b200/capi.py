@@ -140,6 +140,9 @@ SIGNATURES: dict[str, tuple] = {
         c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p],
     ),
     "xtc_cuda_comm_destroy": (c_int, [c_void_p]),
+    "xtc_cuda_peer_barrier": (
+        c_int, [c_void_p, POINTER(c_void_p), POINTER(c_int), c_int, c_int, c_int, c_void_p],
+    ),
     "xtc_cuda_gemm_f32_3xtf32_noalloc": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_float, c_void_p],

@@ -319,6 +319,9 @@ class PeerStoreMatmul:
             with self._on_stream(stream):
                 self._dist.all_reduce(self._flag, group=self.group)
 
+    def drain(self) -> None:
+        """The exchange is part of the step's kernel: nothing runs behind the step's stream."""
+
     def host_loop(self) -> "ShardedHostLoop":
         """Overlapped executor of this step on host batches (see ShardedHostLoop)."""
         return ShardedHostLoop(self)
@@ -358,8 +361,178 @@ class PeerStoreMatmul:
             self.workspace = None
 
 
+class PipelinedPeerMatmul:
+    """Row-sharded matmul whose exchange runs one step behind the product.
+
+    Where the exchange takes longer than the product (65536 x 8192 x 8192 on 8 GPUs: every
+    GPU computes for 1.5 ms and has to receive 1.88 GB), fusing the two into one kernel cannot
+    beat the link, and the fused kernel's stores reach 590 - 665 GB/s where a peer copy by the
+    copy engines reaches 770.  Here a step is the plain GEMM into this rank's rows of one of
+    TWO full-size C buffers; the rows then travel to every peer's copy of that buffer with one
+    peer-to-peer ``xtc_cuda_memcpy_d2d`` per peer (CUDA IPC mappings, copy engines, no SM) on a
+    second stream while the next step's GEMM runs, in a rotation (rank r sends to r+1, r+2,
+    ...) that has every GPU receive from one peer at a time.  ``xtc_cuda_peer_barrier`` after
+    the copies (one warp that writes a flag into every peer's memory and waits for theirs) says
+    "every peer's rows of this step have landed"; a library collective in that place wants SM
+    resources of its own and delays the next GEMM launch by 0.3 - 0.6 ms.
+
+    Throughput per step is then max(product, exchange) instead of their fused sum;
+    ``result_of(step)`` is complete after ``wait()`` (or, stream-ordered, after the
+    barrier of that step on the exchange stream).  Step i + 2 reuses the buffer of step i:
+    a consumer must have read a step's C before submitting the step after next.
+    """
+
+    def __init__(self, device: Any, a_ptr: int, b_ptr: int, m: int, n: int, k: int, world: int,
+                 rank: int, group: Any = None, config: dict | None = None) -> None:
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from . import capi
+
+        assert m % world == 0, f"M ({m}) must be divisible by the number of ranks ({world})"
+        self.device, self.lib = device, device.lib
+        self.world, self.rank, self.group = world, rank, group
+        self.m, self.n, self.k = m, n, k
+        self.rows = m // world
+        self.a_ptr, self.b_ptr = int(a_ptr), int(b_ptr)
+        self.cfg = capi.GemmConfig(**(config or {}))
+        self.exchange = "none" if world == 1 else "pipelined peer copies"
+        self.offset = rank * self.rows * n * 4
+        self.block_bytes = self.rows * n * 4
+        self.buffers = [device.memory_allocate(m * n * 4) for _ in range(2)]
+        self.imported: list[Any] = []
+        # peers[b][j] = buffer b of rank (rank + 1 + j) % world, mapped here
+        self.peers: list[list[int]] = [[], []]
+        for b in range(2):
+            handle = ctypes.create_string_buffer(64)
+            capi.check(self.lib.xtc_cuda_ipc_export(self.buffers[b], handle))
+            handles: list[Any] = [None] * world
+            if world > 1:
+                dist.all_gather_object(handles, handle.raw, group=group)
+            for j in range(1, world):
+                r = (rank + j) % world
+                ptr = ctypes.c_void_p()
+                capi.check(self.lib.xtc_cuda_ipc_import(ctypes.create_string_buffer(handles[r], 64),
+                                                        ctypes.byref(ptr)))
+                self.imported.append(ptr)
+                self.peers[b].append(ptr.value)
+        # the barrier's flags: 8 ints per rank, each rank's array mapped by all the others
+        self.flags = device.memory_allocate(256)
+        device.memory_fill_zero(self.flags, 256)
+        device.synchronize()
+        handle = ctypes.create_string_buffer(64)
+        capi.check(self.lib.xtc_cuda_ipc_export(self.flags, handle))
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle.raw, group=group)
+        peer_flags, peer_ranks = [], []
+        for j in range(1, world):
+            r = (rank + j) % world
+            ptr = ctypes.c_void_p()
+            capi.check(self.lib.xtc_cuda_ipc_import(ctypes.create_string_buffer(handles[r], 64),
+                                                    ctypes.byref(ptr)))
+            self.imported.append(ptr)
+            peer_flags.append(ptr.value)
+            peer_ranks.append(r)
+        self.peer_flags = (ctypes.c_void_p * max(world - 1, 1))(*peer_flags)
+        self.peer_ranks = (ctypes.c_int * max(world - 1, 1))(*peer_ranks)
+        ws = ctypes.c_size_t(0)
+        capi.check(self.lib.xtc_cuda_gemm_workspace_bytes(self.rows, n, k, 0, ctypes.byref(self.cfg),
+                                                          ctypes.byref(ws)))
+        self.ws_bytes = ws.value
+        self.workspace = device.memory_allocate(ws.value) if ws.value else None
+        if self.workspace is not None:
+            device.memory_fill_zero(self.workspace, ws.value)
+            device.synchronize()
+        if world > 1:
+            dist.barrier(group=group)  # every rank's flags are zero and mapped before the first step
+
+        def make(fn: Any) -> Any:
+            h = ctypes.c_void_p()
+            capi.check(fn(ctypes.byref(h)))
+            return h
+
+        self.s_copy = make(self.lib.xtc_cuda_stream_create)
+        self.ev_gemm = [make(self.lib.xtc_cuda_event_create) for _ in range(2)]
+        self.ev_sent = [make(self.lib.xtc_cuda_event_create) for _ in range(2)]
+        self.steps = 0
+        self._dist, self._check = dist, capi.check
+
+    def step(self, stream: int | None = None) -> None:
+        """Enqueue one step: the GEMM on `stream`, its exchange on the copy stream behind it."""
+        lib, ck = self.lib, self._check
+        b = self.steps & 1
+        if self.steps >= 2:
+            # the rows of step i - 2 have left this buffer
+            ck(lib.xtc_cuda_stream_wait_event(stream, self.ev_sent[b]))
+        rc = lib.xtc_cuda_gemm_f32(self.a_ptr, self.b_ptr, self.buffers[b].value + self.offset, self.rows,
+                                   self.n, self.k, self.k, self.n, self.n, 0, 0.0, ctypes_byref(self.cfg),
+                                   self.workspace, self.ws_bytes, stream)
+        if rc:
+            ck(rc)
+        if self.world > 1:
+            ck(lib.xtc_cuda_event_record(self.ev_gemm[b], stream))
+            ck(lib.xtc_cuda_stream_wait_event(self.s_copy, self.ev_gemm[b]))
+            src = self.buffers[b].value + self.offset
+            for peer in self.peers[b]:
+                ck(lib.xtc_cuda_memcpy_d2d(peer + self.offset, src, self.block_bytes, self.s_copy))
+            ck(lib.xtc_cuda_peer_barrier(self.flags, self.peer_flags, self.peer_ranks, self.world - 1,
+                                         self.rank, self.steps + 1, self.s_copy))
+        ck(lib.xtc_cuda_event_record(self.ev_sent[b], self.s_copy if self.world > 1 else stream))
+        self.steps += 1
+
+    @property
+    def c_local(self) -> Any:
+        """The full-size C of the step enqueued last."""
+        return self.buffers[(self.steps - 1) & 1 if self.steps else 0]
+
+    @property
+    def c_block(self) -> int:
+        """This rank's rows in the C of the step enqueued last."""
+        return self.c_local.value + self.offset
+
+    def drain(self) -> None:
+        """Returns when the exchange of every step enqueued so far has completed here."""
+        self._check(self.lib.xtc_cuda_stream_synchronize(self.s_copy))
+
+    def host_loop(self) -> "ShardedHostLoop":
+        """Overlapped executor of this step on host batches (see ShardedHostLoop)."""
+        return ShardedHostLoop(self)
+
+    def result(self) -> Any:
+        """The full C of the step enqueued last as a NumPy array (synchronises)."""
+        import numpy as np
+
+        self.device.synchronize()
+        out = np.empty((self.m, self.n), np.float32)
+        self.device.memory_copy_from(self.c_local, out, out.nbytes)
+        return out
+
+    def close(self) -> None:
+        if self.s_copy is None:
+            return
+        self.device.synchronize()
+        if self.world > 1:
+            self._dist.barrier(group=self.group)
+        for ptr in self.imported:
+            self.lib.xtc_cuda_ipc_release(ptr)
+        self.imported = []
+        for buf in self.buffers + [self.flags]:
+            self.device.memory_free(buf)
+        self.buffers = []
+        if self.workspace is not None:
+            self.device.memory_free(self.workspace)
+            self.workspace = None
+        for ev in self.ev_gemm + self.ev_sent:
+            self.lib.xtc_cuda_event_destroy(ev)
+        self.lib.xtc_cuda_stream_destroy(self.s_copy)
+        self.s_copy = None
+
+
 class ShardedHostLoop:
-    """Runs a PeerStoreMatmul step on a sequence of host batches.
+    """Runs a PeerStoreMatmul (or PipelinedPeerMatmul) step on a sequence of host batches.
 
     ``submit(host_a, host_c)`` copies this rank's block of A in from host memory, runs the
     fused GEMM + exchange, and copies this rank's block of C back out; the copy-in of step
@@ -413,6 +586,7 @@ class ShardedHostLoop:
 
         if self.submitted:
             self._check(self.lib.xtc_cuda_event_synchronize(self.ev_out))
+        self.op.drain()
         if self.op.device.status() != 0:
             raise capi.XtcCudaError(capi.ERR_DEVICE_TIMEOUT, "a kernel's bounded wait gave up")
 
