@@ -552,6 +552,28 @@ def other_configs(torch, dev, args, peaks: dict) -> dict:
 
     guarded("c5_n1_tf32", lambda: c5("tf32"))
     guarded("c5_n1_3xtf32", lambda: c5("3xtf32"))
+
+    # a few layers of the reference's operation tables with nothing scheduled (the library's
+    # own choice of kernel), through the evaluator's timing loop: one image / one token row
+    def named_layers():
+        from xtc_b200.backends.cuda import Backend
+        from xtc_b200.search import Exploration, ExplorationConfig
+
+        out = {}
+        for operator, name in (("conv2d", "ResNet18_01"), ("conv2d", "Yolo9000_18"), ("matmul", "AlexNet_FC7"),
+                               ("matmul", "Gemma2B_QK"), ("matmul", "Llama3_In")):
+            exp = Exploration(ExplorationConfig(operator=operator, op_name=name, peak_flops=1e15))
+            impl = Backend(exp.graph)
+            module = impl.get_compiler(shared_lib=False).compile(impl.get_scheduler().schedule())
+            times, code, msg = module.get_evaluator(repeat=3, number=50, min_repeat_ms=0).evaluate()
+            if code != 0:
+                out[name] = {"error": msg}
+                continue
+            sec = min(times)
+            out[name] = {"us": sec * 1e6, "tflops": 2.0 * exp.fma_count() / sec / 1e12}
+        return out
+
+    guarded("named_layers_default_schedule", named_layers)
     return extra
 
 

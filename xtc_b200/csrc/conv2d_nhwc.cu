@@ -97,8 +97,9 @@ conv2d_pack_rows_kernel(const float* __restrict__ X, float* __restrict__ P, int 
     }
     return;
   }
-  // blockIdx.y walks the B*H input rows, blockIdx.x * 256 + threadIdx.x the OW * KR4 groups of
-  // four packed values of one row: all index arithmetic stays in 32 bits
+  // blockIdx.y walks the B*H input rows four at a time, blockIdx.x * 256 + threadIdx.x the
+  // OW * KR4 groups of four packed values of one row: all index arithmetic stays in 32 bits, and
+  // a thread has the loads of its four rows in flight before the first store
   const int per_row = OW * KR4;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= per_row) return;
@@ -106,16 +107,23 @@ conv2d_pack_rows_kernel(const float* __restrict__ X, float* __restrict__ P, int 
   const int k0 = (i - ow * KR4) * 4;
   const int row_len = W * C;
   const int e0 = (ow * sw - pl) * C + k0;  // element k of the packed pixel is element e0 + k of the row
-  for (int row = blockIdx.y; row < rows; row += gridDim.y - 1) {
-    const float* xr = X + static_cast<int64_t>(row) * row_len;
-    float v[4];
+  bool ok[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int e = e0 + j;
-      v[j] = (k0 + j < valid && e >= 0 && e < row_len) ? __ldg(xr + e) : 0.f;
+  for (int j = 0; j < 4; ++j) ok[j] = k0 + j < valid && e0 + j >= 0 && e0 + j < row_len;
+  constexpr int ROWS = 4;
+  for (int row0 = blockIdx.y * ROWS; row0 < rows; row0 += (gridDim.y - 1) * ROWS) {
+    float v[ROWS][4];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float* xr = X + static_cast<int64_t>(row0 + r) * row_len + e0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[r][j] = (ok[j] && row0 + r < rows) ? __ldg(xr + j) : 0.f;
     }
-    reinterpret_cast<float4*>(P)[static_cast<int64_t>(row) * per_row + i] =
-        make_float4(v[0], v[1], v[2], v[3]);
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+      if (row0 + r < rows)
+        reinterpret_cast<float4*>(P)[static_cast<int64_t>(row0 + r) * per_row + i] =
+            make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
   }
 }
 
@@ -605,9 +613,10 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     float* V = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + t.p_bytes);
     const int64_t rows = B * H;
     const int per_row = static_cast<int>(t.OW * (t.KR / 4));
-    // one launch: B*H rows of blocks pack the input, one more row of blocks packs the filter
+    // one launch: a row of blocks per four input rows packs the input, one more packs the filter
+    const int64_t row_groups = (rows + 3) / 4;
     const dim3 pack_grid(static_cast<unsigned>((per_row + 255) / 256),
-                         static_cast<unsigned>((rows < 65534 ? rows : 65534) + 1));
+                         static_cast<unsigned>((row_groups < 65534 ? row_groups : 65534) + 1));
     conv2d_pack_rows_kernel<<<pack_grid, 256, 0, a.stream>>>(
         X, P, static_cast<int>(rows), static_cast<int>(W), static_cast<int>(C), static_cast<int>(t.OW),
         static_cast<int>(t.KR / 4), static_cast<int>(S * C), stride_w, pad_left, Wt, V,
