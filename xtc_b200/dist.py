@@ -343,6 +343,8 @@ class PeerStoreMatmul:
         for ptr in self.imported:
             self.lib.xtc_cuda_ipc_release(ptr)
         self.imported = []
+        if self.world > 1:
+            self._dist.barrier(group=self.group)  # nobody frees a C that a peer still has mapped
         if self._symm is not None:
             # drop the multicast binding while every rank is still alive (all ranks are past
             # the barrier above, none has exited)
@@ -519,6 +521,8 @@ class PipelinedPeerMatmul:
         for ptr in self.imported:
             self.lib.xtc_cuda_ipc_release(ptr)
         self.imported = []
+        if self.world > 1:
+            self._dist.barrier(group=self.group)  # nobody frees memory that a peer still has mapped
         for buf in self.buffers + [self.flags]:
             self.device.memory_free(buf)
         self.buffers = []
