@@ -147,6 +147,12 @@ int xtc_cuda_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64
                       void* stream);
 int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int flags,
                                   const xtc_cuda_gemm_config* cfg, size_t* bytes);
+/* The tile, K stage and split the library picks for a TF32 product of this shape when the
+ * caller names nothing (16-byte aligned operands assumed; products of at most 8 rows run on the
+ * matrix-vector kernel instead, which has no such parameters): a starting point for a search
+ * over xtc_cuda_gemm_config, as the reference's strategies start from default_schedule
+ * (src/xtc/search/strategies.py:95-98).  Host arithmetic plus cached device queries. */
+int xtc_cuda_gemm_default_config(int64_t M, int64_t N, int64_t K, xtc_cuda_gemm_config* out);
 
 /* xtc_cuda_gemm_f32 whose epilogue also writes every output tile to the same
  * position of n_extra (<= 7) further buffers with the pitch ldc: the copies of C

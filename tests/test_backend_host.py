@@ -296,6 +296,18 @@ def test_row_exchange_entry_points_check_their_arguments(cuda_lib):
     assert "NULL argument" in capi.last_error()
 
 
+def test_default_gemm_config_is_a_legal_config(cuda_lib):
+    """xtc_cuda_gemm_default_config: host arithmetic, callable without a device; what it returns
+    is a configuration the GEMM entry point accepts (legal tile, K stage and split)."""
+    for shape in ((4096, 4096, 4096), (512, 1024, 256), (256, 3072, 8192), (100352, 64, 256), (7, 9, 11)):
+        c = capi.GemmConfig()
+        capi.check(cuda_lib.xtc_cuda_gemm_default_config(*shape, ctypes.byref(c)))
+        assert c.tile_m in (128, 256) and c.tile_n in (64, 128, 256) and c.tile_k in (32, 64), shape
+        assert c.split_k >= 0 and (c.tile_m == 128 or c.split_k == 0)
+    assert cuda_lib.xtc_cuda_gemm_default_config(0, 4, 4, ctypes.byref(capi.GemmConfig())) == capi.ERR_INVALID
+    assert cuda_lib.xtc_cuda_gemm_default_config(4, 4, 4, None) == capi.ERR_INVALID
+
+
 def test_counters_library_exports_every_declared_symbol(cuda_lib):
     """include/xtc_cuda_counters.h against the built CUPTI module and its ctypes binding."""
     from xtc_b200.runtimes import counters as gc

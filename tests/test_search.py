@@ -35,6 +35,17 @@ def test_strategy_space_is_legal_and_maps_one_to_one():
         assert strat.is_legal(strat.default_schedule(level))
 
 
+def test_o3_default_schedule_is_the_library_choice():
+    """default_schedule(3) asks the kernel library what it would run for the product
+    (xtc_cuda_gemm_default_config, host arithmetic) and returns it as a legal sample."""
+    for dims in ((4096, 4096, 4096), (256, 3072, 8192), (1000, 1104, 1200)):
+        st = Strategies.create("cuda_gemm", matmul_graph(*dims))
+        sample = st.default_schedule(3)
+        assert st.is_legal(sample)
+        assert sample == (st.library_default() or [256, 256, 32, 0, 1, 1])
+    assert Strategies.create("cuda_gemm", matmul_graph(4096, 4096, 4096)).default_schedule(3)[:3] == [256, 256, 64]
+
+
 def test_strategy_targets_the_contraction_of_a_fused_graph():
     graph = matmul_graph(256, 256, 256, relu=True)
     strat = Strategies.create("cuda_gemm", graph)

@@ -147,6 +147,7 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_float, c_void_p],
     ),
+    "xtc_cuda_gemm_default_config": (c_int, [c_int64, c_int64, c_int64, POINTER(GemmConfig)]),
     "xtc_cuda_gemm_workspace_bytes": (
         c_int, [c_int64, c_int64, c_int64, c_int, POINTER(GemmConfig), POINTER(c_size_t)],
     ),

@@ -109,14 +109,35 @@ class StrategyCudaGemm:
         return space[: max(num, 0)]
 
     def default_schedule(self, opt_level: int = 2) -> list[int]:
-        """O0: smallest tiles, shallow pipeline; O3: the widest tile, deepest pipeline."""
+        """O0: smallest tiles, shallow pipeline; O2: a wide tile, deepest pipeline; O3: what the
+        library itself would pick for this product (xtc_cuda_gemm_default_config), where that is
+        a point of this space."""
         if opt_level <= 0:
             return [128, 64, 32, 2, 0, 1]
         if opt_level == 1:
             return [128, 128, 32, 0, 0, 1]
         if opt_level == 2 or self._is_conv:
             return [128, 256 if not self._is_conv else 64, 32 if not self._is_conv else 64, 0, 1, 1]
-        return [256, 256, 32, 0, 1, 1]
+        return self.library_default() or [256, 256, 32, 0, 1, 1]
+
+    def library_default(self) -> list[int] | None:
+        """The library's own choice for this matmul as a sample, or None (no library built, a
+        convolution, or a choice outside this space)."""
+        if self._is_conv:
+            return None
+        try:
+            import ctypes
+
+            from .. import capi
+
+            m, n, k = (int(v) for v in self._op.dims.values())
+            cfg = capi.GemmConfig()
+            if capi.load().xtc_cuda_gemm_default_config(m, n, k, ctypes.byref(cfg)) != capi.OK:
+                return None
+        except Exception:  # the search must not depend on the kernel library being present
+            return None
+        sample = [cfg.tile_m, cfg.tile_n, cfg.tile_k, 0, 1, max(cfg.split_k, 1)]
+        return sample if self.is_legal(sample) else None
 
     # -- sample -> scheduler calls ---------------------------------------------------
     def generate(self, scheduler: Any, sample: list[int]) -> None:
