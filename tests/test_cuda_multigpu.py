@@ -146,6 +146,24 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
             op.step(stream)
         assert np.array_equal(op.result(), single), "the last step's C, complete on every rank"
         dist.barrier()
+        # every step's own data: A is scaled by a power of two before each step (exact), the
+        # steps are enqueued back to back, and the two buffers still held must carry the last
+        # two steps' products on every rank (a flag that overtook its rows would show here)
+        scales = [2.0, 0.5, 4.0, 0.25, 8.0, 1.0]
+        a_keep = a_blk.clone()
+        for sc in scales:
+            a_blk.copy_(a_keep * sc)
+            op.step(stream)
+        op.drain()
+        torch.cuda.synchronize()
+        last = np.empty((m, n), np.float32)
+        dev.memory_copy_from(op.buffers[(op.steps - 1) & 1], last, last.nbytes)
+        prev = np.empty((m, n), np.float32)
+        dev.memory_copy_from(op.buffers[(op.steps - 2) & 1], prev, prev.nbytes)
+        assert np.array_equal(last, single * np.float32(scales[-1]))
+        assert np.array_equal(prev, single * np.float32(scales[-2]))
+        a_blk.copy_(a_keep)
+        dist.barrier()
         loop = op.host_loop()
         host_c.fill_(float("nan"))
         a_blk.zero_()
