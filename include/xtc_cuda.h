@@ -115,7 +115,11 @@ typedef struct xtc_cuda_gemm_config {
   int32_t variant;   /* conv2d: 0 = auto; 1 = im2col fetch per filter tap;
                         2 = resident weights + halo tiles (stride 1 only);
                         3 = the same with two filter taps per MMA (at most 64
-                        filters, filter rows of two taps or more).
+                        filters, filter rows of two taps or more);
+                        4 = resident weights with a sliding input window: a run of
+                        consecutive tiles per CTA, the input through a ring of
+                        128-position chunks (stride 1, at most 128 filters, a halo
+                        run of at most 256 positions).
                         GEMM with tile_m = 256: 2 = store C without the L2
                         evict-first hint (the default hints it)                   */
   int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off unless

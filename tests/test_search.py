@@ -80,7 +80,8 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
     assert strat.node_name == "conv"
     space = list(strat.exhaustive())
     assert len(space) == len({tuple(s) for s in space}) > 100
-    assert {s[0] for s in space} == {1, 2, 3}
+    assert {s[0] for s in space} == {1, 2, 3, 4}
+    assert [s for s in space if s[0] == 4] == [[4, 128, 64, 32, 0, 0, 1]]  # the sliding input window
     resident = [s for s in space if s[0] == 2]
     assert {(s[1], s[3]) for s in resident} == {(128, 16), (128, 32), (256, 32)}
     assert {(s[1], s[3]) for s in space if s[0] == 3} == {(128, 16), (128, 32)}  # two taps per MMA
@@ -90,7 +91,7 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
         sch = Backend(graph).get_scheduler(strict=True)
         strat.generate(sch, s)
         cfg = sch.schedule().node_configs()["conv"]
-        assert cfg.get("variant", 0) == (s[0] if s[0] in (2, 3) else 0)
+        assert cfg.get("variant", 0) == (s[0] if s[0] in (2, 3, 4) else 0)
         assert (cfg["tile_m"], cfg["tile_k"], cfg.get("stages", 0)) == (s[1], s[3], s[4])
         assert cfg.get("split_k", 1) == s[6] and cfg.get("epilogue", 0) == (2 if s[5] else 0)
         if s[0] == 1:
@@ -105,6 +106,9 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
     assert all(s[0] == 1 for s in big.exhaustive())
     half = Strategies.create("cuda_conv", conv2d_graph(1, 28, 28, 128, 3, 3, 64, 1, 1))
     assert {(s[1], s[3]) for s in half.exhaustive() if s[0] == 2} >= {(256, 32)}
+    # a halo run of more than 256 positions (112-wide rows) does not go through the ring
+    wide = Strategies.create("cuda_conv", conv2d_graph(1, 112, 112, 32, 3, 3, 32, 1, 1))
+    assert not wide.sliding_window_fits() and 4 not in {s[0] for s in wide.exhaustive()}
     with pytest.raises(ValueError):
         Strategies.create("cuda_conv", matmul_graph(128, 128, 128))
 
@@ -219,7 +223,7 @@ def test_conv_search_on_gpu_confirms_the_shipped_c3_schedule(tmp_path):
                                         repeat=3, number=20, min_repeat_ms=5,
                                         explore_dir=str(tmp_path / "x")))
     space = list(exp.strategy.exhaustive())
-    resident = [s for s in space if s[0] in (2, 3)]
+    resident = [s for s in space if s[0] in (2, 3, 4)]
     im2col = [s for s in exp.strategy.sample(len(space), seed=3) if s[0] == 1][:16]
     shipped = [2, 128, 64, 32, 0, 0, 1]
     assert shipped in resident

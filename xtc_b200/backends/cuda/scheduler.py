@@ -19,7 +19,9 @@ mapping side is new: for a contraction node (matmul / conv2d)
                            (conv2d: split(c, ...), the im2col kernels)
   pack_at(_, 1)            conv2d filter bank packed on chip  -> resident weights + halo tiles;
                            the first tile of c is then the channel slab of a stage (16 or 32),
-                           tile(s, {s1: 2}) puts two neighbouring filter taps into one MMA
+                           tile(s, {s1: 2}) puts two neighbouring filter taps into one MMA;
+                           pack_at(_, 0) as well keeps the input window on chip across
+                           consecutive tiles (a run of tiles per CTA, the input through a ring)
   tile rows 256                                               -> CTA pairs (two SMs per MMA)
 
 Values the kernels do not implement are snapped to the nearest legal value
@@ -256,6 +258,9 @@ class CudaNodeScheduler:
                 cfg["variant"] = 3
             elif s_tiles and strict and s_tiles[0] != 1:
                 raise ScheduleError(f"{self.node_name}: taps per MMA = {s_tiles[0]} is not 1 or 2")
+            elif any(0 in idx for idx in self.packed_buffers.values()):
+                # pack_at(_, 0) too: the input window stays on chip from one tile to the next
+                cfg["variant"] = 4
         return cfg
 
     def node_schedule(self, strict: bool = False) -> CudaNodeSchedule:

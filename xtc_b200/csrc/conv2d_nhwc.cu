@@ -8,6 +8,7 @@
 // 4) run on a direct CUDA-core kernel.
 #include "conv2d_halo_pair.cuh"
 #include "conv2d_halo_taps.cuh"
+#include "conv2d_halo_slide.cuh"
 #include "gemm_tf32_pair.cuh"
 
 #ifdef XTC_TRACE
@@ -355,6 +356,90 @@ int dispatch_conv_halo_bn(const ConvArgs& a, const HaloPlan& h, bool pair) {
   return h.slab == 16 ? launch_conv_halo<BN, false, 16>(a, h) : launch_conv_halo<BN, false, 32>(a, h);
 }
 
+// The sliding-window form of the resident-weights kernel (conv2d_halo_slide.cuh): stride 1,
+// at most 128 filters, a halo run of at most 256 positions, the filter bank beside five
+// 16 KB ring slots.
+struct SlidePlan {
+  bool ok = false;
+  int bn = 0, nslab = 0, nblk = 0, smem = 0;
+};
+SlidePlan plan_slide(const ConvArgs& a) {
+  SlidePlan s;
+  if (a.sh != 1 || a.sw != 1 || a.F > 128 || a.R * a.S < 2) return s;  // two threads share the taps
+  const int64_t Wp = a.W + a.pl + a.pr;
+  const int64_t P = BM + (a.R - 1) * Wp + (a.S - 1);
+  if (P > 2 * SLIDE_CHUNK || a.pl > 127 || a.pt > 127 || a.pr > 127 || a.pb > 127) return s;
+  s.bn = a.F <= 64 ? 64 : 128;
+  s.nblk = static_cast<int>((a.C + 31) / 32);
+  s.nslab = s.nblk;
+  const int64_t wbytes = a.R * a.S * s.nblk * s.bn * 128;
+  const int64_t total = 1024 + wbytes + (SLIDE_SLOTS + 1) * SLIDE_SLOT_BYTES + 1024;
+  if (total > 232448) return s;
+  s.smem = static_cast<int>(total);
+  s.ok = true;
+  return s;
+}
+
+template <int BN>
+int launch_conv_slide(const ConvArgs& a, const SlidePlan& h) {
+  encode_im2col_fn enc = get_encode_im2col();
+  XTC_REQUIRE(enc != nullptr, "cuTensorMapEncodeIm2col is not available from this driver");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  const int64_t Hp = a.H + a.pt + a.pb, Wp = a.W + a.pl + a.pr;
+  CUtensorMap tmX, tmW;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W),
+                        static_cast<cuuint64_t>(a.H), static_cast<cuuint64_t>(a.B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(a.C) * 4, static_cast<cuuint64_t>(a.W * a.C) * 4,
+                           static_cast<cuuint64_t>(a.H * a.W * a.C) * 4};
+  int lower[2] = {-a.pl, -a.pt};
+  int upper[2] = {a.pr, a.pb};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  // one copy = 128 consecutive positions of the zero-padded image grid, 32 channels
+  CUresult r = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.X), dims, strides,
+                   lower, upper, 32, SLIDE_CHUNK, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  XTC_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeIm2col (sliding halo) failed (%d)", static_cast<int>(r));
+  int rc;
+  if ((rc = make_tmap_2d(&tmW, a.Wt, a.R * a.S * a.C, a.F, a.F, 32, 32,
+                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)))
+    return rc;
+  ConvHaloParams p;
+  memset(&p, 0, sizeof(p));
+  p.Y = a.Y;
+  p.status = device_status_word(dev);
+  XTC_REQUIRE(p.status != nullptr, "conv2d: device status word unavailable");
+  p.Q = a.B * Hp * Wp;
+  p.tiles = static_cast<int>((p.Q + BM - 1) / BM);
+  p.Hp = static_cast<int>(Hp);
+  p.Wp = static_cast<int>(Wp);
+  p.OH = static_cast<int>(a.OH);
+  p.OW = static_cast<int>(a.OW);
+  p.F = static_cast<int>(a.F);
+  p.nslab = h.nslab;
+  p.nblk = h.nblk;
+  p.C = static_cast<int>(a.C);
+  p.taps = static_cast<int>(a.R * a.S);
+  p.S = static_cast<int>(a.S);
+  p.pad_left = a.pl;
+  p.pad_top = a.pt;
+  p.relu = a.relu;
+  p.relu_threshold = a.thr;
+  auto kernel = conv2d_halo_slide_kernel<BN>;
+  static thread_local int configured_dev = -1;
+  static thread_local int configured_smem = 0;
+  if (configured_dev != dev || configured_smem < h.smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem));
+    configured_dev = dev;
+    configured_smem = h.smem;
+  }
+  const int slots = sm_count(dev);
+  const int grid = p.tiles < slots ? p.tiles : slots;
+  XTC_CUDA_CHECK(launch_overlapped(kernel, grid, SLIDE_THREADS, h.smem, a.stream, tmX, tmW, p));
+  return XTC_CUDA_OK;
+}
+
 int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h, bool pair, bool taps = false) {
   if (taps)
     return h.slab == 16 ? launch_conv_halo<64, false, 16, true>(a, h)
@@ -644,7 +729,14 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     XTC_CUDA_CHECK(cudaGetLastError());
     return XTC_CUDA_OK;
   }
-  XTC_REQUIRE(c.variant >= 0 && c.variant <= 3, "conv2d: unknown variant %d", c.variant);
+  XTC_REQUIRE(c.variant >= 0 && c.variant <= 4, "conv2d: unknown variant %d", c.variant);
+  if (c.variant == 4) {
+    const SlidePlan sp = plan_slide(a);
+    if (sp.ok) return sp.bn == 64 ? launch_conv_slide<64>(a, sp) : launch_conv_slide<128>(a, sp);
+    set_error("conv2d: the sliding-window variant (4) needs stride 1, at most 128 filters, a halo run of "
+              "at most 256 positions and a filter bank that fits beside five 16 KB ring slots");
+    return XTC_CUDA_ERR_UNSUPPORTED;
+  }
   if (c.variant == 3) {
     // Resident weights with two filter taps per MMA (only when asked for: see the numbers in
     // conv2d_halo_taps.cuh).

@@ -176,6 +176,9 @@ class StrategyCudaConv:
                  32 only for pairs), stages; tile_n, tma_store and split_k do not apply
       variant 3  the same with two neighbouring filter taps per MMA (at most 64 filters, filter
                  rows of two taps or more, one CTA per tile)
+      variant 4  resident weights with a sliding input window: a run of consecutive tiles per
+                 CTA, the input through a ring of 128-position chunks (at most 128 filters, a
+                 halo run of at most 256 positions); no other parameter applies
       variant 1  implicit GEMM, one im2col fetch per filter tap: the GEMM kernels' tile_m /
                  tile_n / tile_k / stages / epilogue, and split_k = 2, 4, 8 pieces of the
                  reduction in one thread-block cluster (one CTA per tile, tile_n <= 128)
@@ -216,8 +219,19 @@ class StrategyCudaConv:
         room = SMEM_BUDGET - bank - (1024 if taps else 0)  # the two-tap kernel exchanges rows
         return max(min(room // stage, 8), 0) if room >= 2 * stage else 0
 
+    def sliding_window_fits(self) -> bool:
+        """Whether the sliding-window kernel takes this layer (conv2d_halo_slide.cuh)."""
+        if self._stride != (1, 1) or self._f > 128 or self._r * self._s < 2 or self._c % 4 or self._f % 4:
+            return False
+        run = 128 + (self._r - 1) * self._in_w + self._s - 1
+        bank = self._r * self._s * -(-self._c // 32) * (64 if self._f <= 64 else 128) * 128
+        return run <= 256 and bank + 5 * 16384 + 2048 <= SMEM_BUDGET + 2048
+
     def is_legal(self, sample: list[int]) -> bool:
         variant, tm, tn, tk, st, tma, split = sample
+        if variant == 4:
+            return (self.sliding_window_fits() and tm == 128 and tk == 32 and st == 0 and tma == 0
+                    and split == 1 and tn == (64 if self._f <= 64 else 128))
         if variant in (2, 3):
             fit = self.resident_stages(tm, tk, variant == 3) if tm in (128, 256) and tk in (16, 32) else 0
             return (fit >= 2 and (st == 0 or 2 <= st <= fit) and tma == 0 and split == 1
@@ -236,6 +250,8 @@ class StrategyCudaConv:
             s = [variant, tm, tn_res, slab, st, 0, 1]
             if self.is_legal(s):
                 yield s
+        if self.is_legal([4, 128, min(tn_res, 128), 32, 0, 0, 1]):
+            yield [4, 128, min(tn_res, 128), 32, 0, 0, 1]
         for tm, tn, tk, st, tma, split in itertools.product(g.tile_m, g.tile_n, g.tile_k, g.stages,
                                                             (0, 1), (1, 2, 4, 8)):
             s = [1, tm, tn, tk, st, tma, split]
@@ -257,10 +273,12 @@ class StrategyCudaConv:
         variant, tm, tn, tk, st, tma, split = (int(v) for v in sample)
         b, h, w, f, r, s, c = list(self._op.dims)
         target = scheduler.node(self.node_name) if hasattr(scheduler, "node") else scheduler
-        if variant in (2, 3):
+        if variant in (2, 3, 4):
             target.pack_at(b, 1)  # the filter bank stays packed on chip
             if variant == 3:
                 target.tile(s, {f"{s}1": 2})  # two neighbouring taps per MMA
+            if variant == 4:
+                target.pack_at(w, 0)  # and the input window, from one tile to the next
         elif split > 1:
             piece = -(-self._c // split)
             target.split(c, {f"{c}_s{i}": i * piece for i in range(split)})
