@@ -183,6 +183,8 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap tmIn,
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (TT_STAGES + 2) * TT_TILE_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  // every element is read once and written once: both sides are marked evict-first in L2
+  const uint64_t once = l2_policy_evict_first();
   auto coords = [&](long long t, int& c0, int& r0, int& i0, int& i1) {
     const long long tc = t % p.tiles_c; t /= p.tiles_c;
     const long long tr = t % p.tiles_r; t /= p.tiles_r;
@@ -195,7 +197,7 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap tmIn,
     int c0, r0, i0, i1;
     coords(t, c0, r0, i0, i1);
     mbar_arrive_expect_tx(&full[stage], TT_TILE_BYTES);
-    tma_load_4d(in_tiles + stage * (TT * TT), &tmIn, &full[stage], c0, r0, i0, i1);
+    tma_load_4d_hint(in_tiles + stage * (TT * TT), &tmIn, &full[stage], c0, r0, i0, i1, once);
   };
 
   if (tid == 0) {
@@ -238,7 +240,7 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap tmIn,
     if (tid == 0) {
       int c0, r0, i0, i1;
       coords(t, c0, r0, i0, i1);
-      tma_store_4d(&tmOut, dst, r0, c0, i0, i1);
+      tma_store_4d_hint(&tmOut, dst, r0, c0, i0, i1, once);
       tma_store_commit();
       const long long next = t + TT_STAGES * step;
       if (next < p.total) load(next, stage);
