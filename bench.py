@@ -490,8 +490,10 @@ def launch_floor_us(torch, dev) -> float:
     return total / 400 * 1e6
 
 
-def other_configs(torch, dev, args, peaks: dict) -> dict:
-    """Every other configuration, device-resident: the metric is per graph."""
+def other_configs(torch, dev, args, peaks: dict, heavy: bool) -> dict:
+    """Every other configuration, device-resident: the metric is per graph.  heavy = False:
+    the short steps (measured before anything has run the chip into its power cap); heavy =
+    True: c5 on one GPU, seconds of tensor work."""
     tf32_burst, _ = tf32_denominator(peaks, False)
     tf32_sus, _ = tf32_denominator(peaks, True)
     extra: dict = {}
@@ -524,9 +526,12 @@ def other_configs(torch, dev, args, peaks: dict) -> dict:
                         "frac_of_bound": floor / (r["seconds"] * 1e6)}
         return out
 
-    guarded("c1", c1)
-    guarded("c3", lambda: tensor_entry("c3", bench_graph_device(torch, dev, "c3", max(args.steps, 200), args.warmup)))
-    guarded("c4", lambda: tensor_entry("c4", bench_graph_device(torch, dev, "c4", max(args.steps, 50), args.warmup)))
+    if not heavy:
+        guarded("c1", c1)
+    if not heavy:
+        guarded("c3", lambda: tensor_entry("c3", bench_graph_device(torch, dev, "c3", max(args.steps, 200), args.warmup)))
+    if not heavy:
+        guarded("c4", lambda: tensor_entry("c4", bench_graph_device(torch, dev, "c4", max(args.steps, 50), args.warmup)))
 
     def hbm_entry(name):
         r = bench_graph_device(torch, dev, name, max(args.steps, 100), args.warmup)
@@ -534,7 +539,7 @@ def other_configs(torch, dev, args, peaks: dict) -> dict:
         return {"gbs": gbs, "us": r["seconds"] * 1e6, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                 "peak": peaks["hbm_gbs"], "bytes": r["cfg"].bytes}
 
-    for name in ("c4a", "relu512", "pad512"):
+    for name in (() if heavy else ("c4a", "relu512", "pad512")):
         guarded(name, lambda name=name: hbm_entry(name))
 
     # c5 on one GPU, device-resident: TF32 and 3xTF32 (seconds-long tensor work: sustained peak)
@@ -570,10 +575,11 @@ def other_configs(torch, dev, args, peaks: dict) -> dict:
             out[name] = {"us": sec * 1e6, "tflops": 2.0 * exp.fma_count() / sec / 1e12}
         return out
 
-    guarded("named_layers_default_schedule", named_layers)
-    # the seconds-long runs last: the chip stays at its power-capped clock for a while after them
-    guarded("c5_n1_tf32", lambda: c5("tf32"))
-    guarded("c5_n1_3xtf32", lambda: c5("3xtf32"))
+    if not heavy:
+        guarded("named_layers_default_schedule", named_layers)
+    else:
+        guarded("c5_n1_tf32", lambda: c5("tf32"))
+        guarded("c5_n1_3xtf32", lambda: c5("3xtf32"))
     return extra
 
 
@@ -626,6 +632,18 @@ def run_single(args) -> None:
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    # Order: everything short first, while the chip still clocks as it did for the headline;
+    # then the runs that take it into the power cap (the cuBLAS yardstick, this kernel for a
+    # second or more, c5 on one GPU), after which it stays at the capped clock for a while.
+    extra = not args.no_extra and workload == "c2"
+    if extra:
+        line["other_configs"] = other_configs(torch, dev, args, peaks, heavy=False)
+        try:
+            yard = cublas_tf32(torch)
+            line["tf32_cublas"] = yard
+            line["roofline"]["frac_of_cublas_tf32_burst"] = line["roofline"]["achieved"] / yard["burst_tflops"]
+        except Exception as e:
+            line["tf32_cublas"] = {"error": str(e)}
     # ---- the same kernel for a second or more: sustained clocks ---------------
     if not args.no_extra and cfg.flops:
         seg = sustained_segment(torch, info, 1.2, ClockSampler(0))
@@ -635,20 +653,13 @@ def run_single(args) -> None:
         line["sustained"] = {"steps": seg["steps"], "seconds": seg["seconds"],
                              "ms_per_step": seg["sec_per_step"] * 1e3, "clocks": seg["clocks"],
                              "roofline": sus}
+        if "sustained_tflops" in line.get("tf32_cublas", {}):
+            line["sustained"]["roofline"]["frac_of_cublas_tf32_sustained"] = (
+                line["value_sustained"] / line["tf32_cublas"]["sustained_tflops"])
     del info
     torch.cuda.empty_cache()
-    # ---- the other configurations and the cuBLAS TF32 yardstick ----------------
-    if not args.no_extra and workload == "c2":
-        line["other_configs"] = other_configs(torch, dev, args, peaks)
-        try:
-            yard = cublas_tf32(torch)
-            line["tf32_cublas"] = yard
-            line["roofline"]["frac_of_cublas_tf32_burst"] = line["roofline"]["achieved"] / yard["burst_tflops"]
-            if "sustained" in line:
-                line["sustained"]["roofline"]["frac_of_cublas_tf32_sustained"] = (
-                    line["value_sustained"] / yard["sustained_tflops"])
-        except Exception as e:
-            line["tf32_cublas"] = {"error": str(e)}
+    if extra:
+        line["other_configs"].update(other_configs(torch, dev, args, peaks, heavy=True))
     # ---- CPU baseline ---------------------------------------------------------
     if not args.no_cpu:
         base = time_cpu(workload, 3, 1)
