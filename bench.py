@@ -278,8 +278,8 @@ def time_device_steps(torch, fn, steps: int, warmup: int, barrier=None):
         barrier()
     # An event between two launches costs a few microseconds of stream time, which is
     # not negligible next to a 10-30 us step: record one every `stride` steps (at most
-    # 16 segments) and report each segment's average step time.
-    stride = max(1, -(-steps // 16))
+    # 16 segments, 4 for short runs) and report each segment's average step time.
+    stride = max(1, -(-steps // (16 if steps > 64 else 4)))
     marks = list(range(0, steps, stride)) + [steps]
     evs = [torch.cuda.Event(enable_timing=True) for _ in marks]
     torch.cuda.synchronize()
@@ -766,7 +766,8 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         n_sets = 8
         xs = [x.clone() for _ in range(n_sets)]
         ys = [torch.empty(cfg.output_shape, device="cuda") for _ in range(n_sets)]
-        step = lambda i: handle.run([xs[i % n_sets].data_ptr(), w.data_ptr(), ys[i % n_sets].data_ptr()], stream)
+        ptr_sets = [[xs[i].data_ptr(), w.data_ptr(), ys[i].data_ptr()] for i in range(n_sets)]
+        step = lambda i: handle.run(ptr_sets[i % n_sets], stream)
         total_flops = configs.build("c3").flops
         local_cfg = cfg
         h2d = x.numel() * 4 + w.numel() * 4
