@@ -394,6 +394,7 @@ class PipelinedPeerMatmul:
         from . import capi
 
         assert m % world == 0, f"M ({m}) must be divisible by the number of ranks ({world})"
+        assert 1 <= world <= 8, f"the barrier's flag array has 8 slots: {world} ranks do not fit"
         self.device, self.lib = device, device.lib
         self.world, self.rank, self.group = world, rank, group
         self.m, self.n, self.k = m, n, k
