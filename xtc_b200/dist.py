@@ -388,7 +388,6 @@ class PipelinedPeerMatmul:
                  rank: int, group: Any = None, config: dict | None = None) -> None:
         import ctypes
 
-        import torch
         import torch.distributed as dist
 
         from . import capi
