@@ -267,12 +267,17 @@ def pinned_like(dev, arr: np.ndarray) -> np.ndarray:
     return out
 
 
-def time_device_steps(torch, fn, steps: int, warmup: int, barrier=None):
+def time_device_steps(torch, fn, steps: int, warmup: int, barrier=None, many=None):
     """W warm-up calls, then K calls bracketed by synchronize (+ barrier); returns
     (total seconds, list of average seconds per call of each timed segment), both
-    from events on the current stream."""
-    for i in range(warmup):
-        fn(i)
+    from events on the current stream.  `many(first, count)`, when given, issues the
+    steps first .. first + count - 1 from one host call (xtc_cuda_plan_run_sets): a step
+    of a few microseconds is shorter than a call from Python."""
+    if many is not None:
+        many(0, warmup)
+    else:
+        for i in range(warmup):
+            fn(i)
     torch.cuda.synchronize()
     if barrier:
         barrier()
@@ -285,11 +290,16 @@ def time_device_steps(torch, fn, steps: int, warmup: int, barrier=None):
     torch.cuda.synchronize()
     evs[0].record()
     nxt = 1
-    for i in range(steps):
-        fn(warmup + i)
-        if i + 1 == marks[nxt]:
-            evs[nxt].record()
-            nxt += 1
+    if many is not None:
+        for j in range(len(marks) - 1):
+            many(warmup + marks[j], marks[j + 1] - marks[j])
+            evs[j + 1].record()
+    else:
+        for i in range(steps):
+            fn(warmup + i)
+            if i + 1 == marks[nxt]:
+                evs[nxt].record()
+                nxt += 1
     torch.cuda.synchronize()
     if barrier:
         barrier()
@@ -323,14 +333,20 @@ def bench_graph_device(torch, dev, name: str, steps: int, warmup: int, precision
         sets.append(([t.data_ptr() for t in ins] + [out.data_ptr()], ins, out))
     stream = torch.cuda.current_stream().cuda_stream
 
+    table = handle.pointer_sets([s[0] for s in sets])
+
     def step(i: int) -> None:
         handle.run(sets[i % n_sets][0], stream)
 
+    def many(first: int, count: int) -> None:
+        handle.run_sets(table, first, count, stream)
+
     # every buffer set is visited once before timing (first visits record the CUDA graph)
-    total, per = time_device_steps(torch, step, steps, max(warmup, n_sets))
+    total, per = time_device_steps(torch, step, steps, max(warmup, n_sets), many=many)
     assert dev.status() == 0, "a kernel reported a bounded-wait timeout"
     info = {"cfg": cfg, "plan": plan, "seconds": total / steps, "per_step": per,
-            "n_sets": n_sets, "set_bytes": set_bytes, "handle": handle, "sets": sets, "step": step}
+            "n_sets": n_sets, "set_bytes": set_bytes, "handle": handle, "sets": sets, "step": step,
+            "many": many}
     return info
 
 
@@ -458,8 +474,7 @@ def sustained_segment(torch, info: dict, seconds: float, sampler: ClockSampler) 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
-    for i in range(count):
-        info["step"](i)
+    info["many"](0, count)
     e1.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
@@ -485,7 +500,9 @@ def launch_floor_us(torch, dev) -> float:
                   torch.zeros(128, 64, device="cuda"))
     ptrs = [da.data_ptr(), db.data_ptr(), dc.data_ptr()]
     stream = torch.cuda.current_stream().cuda_stream
-    total, _ = time_device_steps(torch, lambda i: handle.run(ptrs, stream), 400, 20)
+    table = handle.pointer_sets([ptrs])
+    total, _ = time_device_steps(torch, None, 400, 20,
+                                 many=lambda first, count: handle.run_sets(table, first, count, stream))
     handle.close()
     return total / 400 * 1e6
 
@@ -763,11 +780,16 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         x_all, w_np = configs.inputs("c3")
         x = torch.from_numpy(x_all[sh.lo:sh.hi]).cuda()
         w = torch.from_numpy(w_np).cuda()
-        n_sets = 8
+        # enough buffer sets that a step never finds its input in L2, whatever the shard's size
+        n_sets = int(min(max(8, math.ceil(3 * L2_BYTES / (2 * x.numel() * 4))), 64))
         xs = [x.clone() for _ in range(n_sets)]
         ys = [torch.empty(cfg.output_shape, device="cuda") for _ in range(n_sets)]
         ptr_sets = [[xs[i].data_ptr(), w.data_ptr(), ys[i].data_ptr()] for i in range(n_sets)]
+        table = handle.pointer_sets(ptr_sets)
         step = lambda i: handle.run(ptr_sets[i % n_sets], stream)
+        # a shard's step is a few microseconds: issue the steps from C, not one call each
+        step_many = lambda first, count: handle.run_sets(table, first, count, stream)
+        step_many(0, n_sets)  # every set visited once before the warm-up proper
         total_flops = configs.build("c3").flops
         local_cfg = cfg
         h2d = x.numel() * 4 + w.numel() * 4
@@ -780,7 +802,8 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
 
     if rank == 0:
         sampler.start()
-    total, per = time_device_steps(torch, step, args.steps, args.warmup, barrier)
+    total, per = time_device_steps(torch, step, args.steps, args.warmup, barrier,
+                                   many=step_many if workload == "c3" else None)
     clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([total], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -812,10 +835,13 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
         assert checks["all_ranks_ok"], f"gathered rows differ from the recomputation: {checks}"
 
     # compute-only time of the local block (no exchange), for the roofline line
-    comp_total, comp_per = time_device_steps(
-        torch, lambda i: handle.run(
-            [a_blk.data_ptr(), b.data_ptr(), c_blk.data_ptr()], stream)
-        if workload == "c5" else step(i), max(3, min(args.steps, 10)), 1, barrier)
+    if workload == "c5":
+        comp_total, comp_per = time_device_steps(
+            torch, lambda i: handle.run([a_blk.data_ptr(), b.data_ptr(), c_blk.data_ptr()], stream),
+            max(3, min(args.steps, 10)), 1, barrier)
+    else:
+        comp_total, comp_per = time_device_steps(torch, step, max(3, args.steps), 1, barrier,
+                                                 many=step_many)
     kernel_sec = statistics.median(comp_per)
     t = torch.tensor([kernel_sec], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -902,7 +928,8 @@ def run_sharded(args, rank: int, world: int, local_rank: int) -> None:
                        "kernel_config": module.plan.steps[-1].config,
                        "inputs": "the configuration's seeded inputs (each rank draws its own rows)",
                        "l2": "per-rank operands (>= 0.5 GB) exceed the 126 MB L2"
-                             if workload == "c5" else "inputs rotate over 8 buffer sets"},
+                             if workload == "c5" else
+                             f"inputs rotate over {n_sets} buffer sets (> 126 MB L2 in total)"},
             "roofline": roofline_of(local_cfg, kernel_sec, peaks, workload, sustained=True,
                                     precision=args.precision),
             "compute_only_ms": kernel_sec * 1e3,

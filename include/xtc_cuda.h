@@ -379,6 +379,14 @@ int xtc_cuda_plan_destroy(xtc_cuda_plan* plan);
  * io pointers is seen and replayed with one graph launch afterwards (the
  * reference pays a host call per node instead, evaluate_perf.c:99-103). */
 int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* stream);
+/* `count` runs back to back on `stream`, issued from one host call: run j uses the
+ * pointer set io_sets[((first + j) % n_sets) * (n_inputs + n_outputs) ...].  For a
+ * caller whose step is shorter than a host call from its own language (a few
+ * microseconds from Python): the reference's timing loop issues its `number` calls
+ * from C for the same reason (src/xtc/csrcs/runtimes/host/evaluate_perf.c:99-103).
+ * Several sets let the caller rotate buffers so that no run finds its inputs in L2. */
+int xtc_cuda_plan_run_sets(xtc_cuda_plan* plan, void* const* io_sets, int n_sets, int first,
+                           int count, void* stream);
 /* enabled = 0 turns graph replay off (every run issues its launches directly);
  * 1 turns it on.  Default: on for plans of two or more launches, off for a plan
  * that is a single kernel (its runs then overlap back to back through programmatic

@@ -296,6 +296,16 @@ def test_row_exchange_entry_points_check_their_arguments(cuda_lib):
     assert "NULL argument" in capi.last_error()
 
 
+def test_plan_run_sets_checks_its_arguments(cuda_lib):
+    """xtc_cuda_plan_run_sets refuses a missing plan or table and an empty or negative
+    rotation before anything is launched."""
+    table = (ctypes.c_void_p * 3)()
+    assert cuda_lib.xtc_cuda_plan_run_sets(None, table, 1, 0, 1, None) == capi.ERR_INVALID
+    assert "NULL plan" in capi.last_error()
+    fake = ctypes.c_void_p(1)  # never dereferenced: the table is checked first
+    assert cuda_lib.xtc_cuda_plan_run_sets(fake, None, 1, 0, 1, None) == capi.ERR_INVALID
+
+
 def test_default_gemm_config_is_a_legal_config(cuda_lib):
     """xtc_cuda_gemm_default_config: host arithmetic, callable without a device; what it returns
     is a configuration the GEMM entry point accepts (legal tile, K stage and split)."""

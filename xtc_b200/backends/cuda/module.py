@@ -65,6 +65,21 @@ class PlanHandle:
         if rc:
             capi.check(rc)
 
+    def pointer_sets(self, sets: list[list[int]]) -> ctypes.Array:
+        """The flat pointer table ``run_sets`` takes: one row of device pointers per set."""
+        n_io = self.plan.n_inputs + self.plan.n_outputs
+        assert sets and all(len(s) == n_io for s in sets)
+        return (c_void_p * (n_io * len(sets)))(*[p for s in sets for p in s])
+
+    def run_sets(self, table: ctypes.Array, first: int, count: int,
+                 stream: int | None = None) -> None:
+        """``count`` runs back to back from one call (``xtc_cuda_plan_run_sets``): run j on
+        row ``(first + j) % n_sets`` of ``table`` (see ``pointer_sets``)."""
+        n_sets = len(table) // (self.plan.n_inputs + self.plan.n_outputs)
+        rc = self.lib.xtc_cuda_plan_run_sets(self.handle, table, n_sets, first, count, stream)
+        if rc:
+            capi.check(rc)
+
     def run_host(self, arrays: list[np.ndarray]) -> None:
         """Host arrays in, host arrays out (copies inside), synchronous."""
         self.device.activate()

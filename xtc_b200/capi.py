@@ -178,6 +178,7 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "xtc_cuda_plan_destroy": (c_int, [c_void_p]),
     "xtc_cuda_plan_run": (c_int, [c_void_p, POINTER(c_void_p), c_void_p]),
+    "xtc_cuda_plan_run_sets": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_void_p]),
     "xtc_cuda_plan_set_graph_mode": (c_int, [c_void_p, c_int]),
     "xtc_cuda_plan_run_host": (c_int, [c_void_p, POINTER(c_void_p)]),
     "xtc_cuda_pipeline_create": (c_int, [POINTER(c_void_p), c_void_p, c_int]),

@@ -511,6 +511,19 @@ extern "C" int xtc_cuda_plan_run(xtc_cuda_plan* plan, void* const* io, void* str
   return XTC_CUDA_OK;
 }
 
+extern "C" int xtc_cuda_plan_run_sets(xtc_cuda_plan* plan, void* const* io_sets, int n_sets, int first,
+                                      int count, void* stream) {
+  XTC_REQUIRE(plan && io_sets, "plan_run_sets: NULL plan or io_sets");
+  XTC_REQUIRE(n_sets >= 1 && first >= 0 && count >= 0,
+              "plan_run_sets: %d sets, first %d, count %d", n_sets, first, count);
+  const size_t n_io = static_cast<size_t>(plan->n_inputs + plan->n_outputs);
+  for (int j = 0; j < count; ++j) {
+    const size_t set = (static_cast<size_t>(first) + static_cast<size_t>(j)) % static_cast<size_t>(n_sets);
+    if (int rc = xtc_cuda_plan_run(plan, io_sets + set * n_io, stream)) return rc;
+  }
+  return XTC_CUDA_OK;
+}
+
 extern "C" int xtc_cuda_plan_run_host(xtc_cuda_plan* plan, void* const* io) {
   XTC_REQUIRE(plan && io, "plan_run_host: NULL plan or io");
   const int n_io = plan->n_inputs + plan->n_outputs;
