@@ -482,21 +482,24 @@ def sustained_segment(torch, info: dict, seconds: float, sampler: ClockSampler) 
             "sec_per_step": e0.elapsed_time(e1) * 1e-3 / count}
 
 
-def launch_floor_us(torch, dev) -> float:
-    """Seconds per run of the smallest tensor-core GEMM (one 128 x 64 tile, one K stage) back
-    to back: what a launch of these kernels costs before any work (prologue, barriers, tensor
-    memory allocation, one TMA round trip, epilogue)."""
+def one_tile_gemm_us(torch, dev, k: int) -> float:
+    """Microseconds per run, back to back, of a GEMM that is ONE 128 x 64 tile on one SM with a K
+    of `k`, issued from C.  k = 32 (one K stage): what a launch of these kernels costs before
+    any work (prologue, barriers, tensor memory allocation, one TMA round trip, epilogue).  A
+    longer K adds only the time ONE SM needs to pull its operands into shared memory."""
     import xtc_b200.graphs.xtc.op as O
     from xtc_b200.backends.cuda import Backend
     from xtc_b200.backends.cuda.module import PlanHandle
 
-    a = O.tensor((128, 32), "float32", name="A")
-    b = O.tensor((32, 64), "float32", name="B")
+    a = O.tensor((128, k), "float32", name="A")
+    b = O.tensor((k, 64), "float32", name="B")
     with O.graph(name="floor") as gb:
         O.matmul(a, b, name="C")
     module = Backend(gb.graph).get_compiler(shared_lib=False).compile(None)
+    # one CTA whatever k: name the tile and turn the library's K split off
+    module.plan.steps[-1].config.update(tile_m=128, tile_n=64, tile_k=64, split_k=1)
     handle = PlanHandle(module.plan, dev)
-    da, db, dc = (torch.zeros(128, 32, device="cuda"), torch.zeros(32, 64, device="cuda"),
+    da, db, dc = (torch.zeros(128, k, device="cuda"), torch.zeros(k, 64, device="cuda"),
                   torch.zeros(128, 64, device="cuda"))
     ptrs = [da.data_ptr(), db.data_ptr(), dc.data_ptr()]
     stream = torch.cuda.current_stream().cuda_stream
@@ -533,14 +536,29 @@ def other_configs(torch, dev, args, peaks: dict, heavy: bool) -> dict:
     def c1():
         r = bench_graph_device(torch, dev, "c1", max(args.steps, 400), args.warmup)
         out = tensor_entry("c1", r)
-        floor = launch_floor_us(torch, dev)
         c = r["cfg"]
         # c1 is 0.27 GFLOP over 3.7 MB: neither the tensor pipe (0.3 us) nor HBM (0.6 us)
-        # bounds it; the applicable floor is what a launch of these kernels costs
-        out["bound"] = {"kind": "launch", "launch_floor_us": floor,
+        # bounds it.  What does: the cost of a launch of these kernels (a one-tile, one-stage
+        # GEMM back to back) plus the time one SM needs to pull the operands of its piece
+        # into shared memory, at the rate a one-tile GEMM with a long K shows
+        floor = one_tile_gemm_us(torch, dev, 32)
+        k_long = 1024
+        fill_rate = (128 + 64) * (k_long - 32) * 4 / (one_tile_gemm_us(torch, dev, k_long) - floor)  # B/us
+        m, k = c.input_shapes[0]
+        n = c.input_shapes[1][1]
+        kc = r["plan"].steps[-1].config  # the schedule the configuration ships
+        pieces = max(1, kc.get("split_k", 1))
+        rows = 128  # per CTA, also for a 256-row tile of a CTA pair
+        cols = kc["tile_n"] // (2 if kc["tile_m"] == 256 else 1)
+        cta_bytes = (rows + cols) * (k / pieces) * 4
+        bound = floor + cta_bytes / fill_rate
+        out["bound"] = {"kind": "launch + one SM's operand fill", "launch_floor_us": floor,
+                        "sm_fill_gbs": fill_rate * 1e-3, "operand_bytes_per_cta": cta_bytes,
+                        "tile": [kc["tile_m"], kc["tile_n"]], "k_pieces": pieces,
+                        "bound_us": bound,
                         "tensor_us": c.flops / (tf32_burst * 1e12) * 1e6,
                         "hbm_us": c.bytes / (peaks["hbm_gbs"] * 1e9) * 1e6,
-                        "frac_of_bound": floor / (r["seconds"] * 1e6)}
+                        "frac_of_bound": bound / (r["seconds"] * 1e6)}
         return out
 
     if not heavy:

@@ -341,6 +341,25 @@ __device__ __forceinline__ float4 ld_shared_cluster_f4(uint32_t cluster_addr) {
                : "memory");
   return v;
 }
+// Sums, in piece order, the float4 at the same shared-memory offset of the first PIECES CTAs of
+// the cluster, for two offsets at once: all 2 * PIECES reads are issued before the first add.
+template <int PIECES>
+__device__ __forceinline__ void sum_cluster_pieces(uint32_t addr_a, uint32_t addr_b, float4& sum_a,
+                                                   float4& sum_b) {
+  float4 va[PIECES], vb[PIECES];
+#pragma unroll
+  for (int piece = 0; piece < PIECES; ++piece) {
+    va[piece] = ld_shared_cluster_f4(map_to_cta(addr_a, piece));
+    vb[piece] = ld_shared_cluster_f4(map_to_cta(addr_b, piece));
+  }
+  sum_a = make_float4(0.f, 0.f, 0.f, 0.f);
+  sum_b = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int piece = 0; piece < PIECES; ++piece) {
+    sum_a.x += va[piece].x; sum_a.y += va[piece].y; sum_a.z += va[piece].z; sum_a.w += va[piece].w;
+    sum_b.x += vb[piece].x; sum_b.y += vb[piece].y; sum_b.z += vb[piece].z; sum_b.w += vb[piece].w;
+  }
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
                    : "memory");
