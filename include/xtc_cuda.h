@@ -123,7 +123,7 @@ typedef struct xtc_cuda_gemm_config {
                         GEMM with tile_m = 256: 2 = store C without the L2
                         evict-first hint (the default hints it)                   */
   int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off unless
-                        the whole config is zero, when the library decides.  2, 4 or 8
+                        the whole config is zero, when the library decides.  2 to 8
                         pieces of a tile at most 128 columns wide, N a multiple of 4, C
                         16-byte aligned, all clusters resident at once: the pieces are
                         the CTAs of one thread-block cluster and are summed through
@@ -131,7 +131,7 @@ typedef struct xtc_cuda_gemm_config {
                         Any other split needs the workspace of
                         xtc_cuda_gemm_workspace_bytes, zeroed before its
                         first use (the kernel leaves its counters zero again).
-                        conv2d (im2col kernels, tile_m = 128): 2, 4 or 8 = the cluster
+                        conv2d (im2col kernels, tile_m = 128): 2 to 8 = the cluster
                         form under the same conditions, else the layer runs unsplit.
                         With tile_m = 256: 0 = when the last round of tiles would leave
                         CTA pairs idle, share the K blocks of the last tiles out evenly

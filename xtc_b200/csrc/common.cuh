@@ -76,7 +76,7 @@ int sm_count(int dev);
 struct AutoChoice {
   int tile_m, tile_n, tile_k, split_k;
 };
-// `cluster_cap[s]` (s = 2, 4, 8; indexable to 8) = clusters of s single-CTA GEMM blocks the
+// `cluster_cap[s]` (s = 2 .. 8) = clusters of s single-CTA GEMM blocks the
 // device runs at once (cluster_capacity), NULL = do not consider a split inside a cluster.
 // `pair_tail_ok` = the CTA-pair kernel may cut the tiles of a partly idle round along K (the
 // GEMM's pair kernel does, given a workspace; the convolution's does not).
@@ -84,11 +84,11 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
                                bool split_ok, const int* cluster_cap = nullptr,
                                bool pair_tail_ok = true);
 int cluster_capacity(int dev, int size);
-// Pieces (8, 4, 2, or 1 = do not split) a cluster split of `k_blocks` K stages runs with when
-// `want` were asked for: the largest power of two not above `want` whose pieces, of
+// Pieces (8 down to 2, or 1 = do not split) a cluster split of `k_blocks` K stages runs with
+// when `want` were asked for: the largest count not above `want` whose pieces, of
 // ceil(k_blocks / pieces) stages each, are all non-empty.
 inline int cluster_pieces(int k_blocks, int want) {
-  for (int s = 8; s >= 2; s >>= 1) {
+  for (int s = 8; s >= 2; --s) {
     if (s > want) continue;
     const int per = (k_blocks + s - 1) / s;
     if ((s - 1) * per < k_blocks) return s;

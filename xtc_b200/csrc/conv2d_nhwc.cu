@@ -32,7 +32,7 @@ struct ConvArgs {
   int split_k = 1;            // im2col kernel, one CTA per tile: CTAs sharing a tile along K
   float* partials = nullptr;  // [split][tile][128][tile_n]
   int* counters = nullptr;    // [tile], zeroed once
-  bool cluster_k = false;     // 2, 4 or 8 pieces summed inside a thread-block cluster (no workspace)
+  bool cluster_k = false;     // 2 to 8 pieces summed inside a thread-block cluster (no workspace)
 };
 
 __global__ void __launch_bounds__(256)
@@ -204,9 +204,9 @@ int launch_conv_tc(const ConvArgs& a) {
   p.partials = a.partials;
   p.tile_counters = a.counters;
   if (p.split_k > 1) p.chunk_kblocks = p.split_kblocks;
-  p.cluster_k = in_cluster && (p.split_k == 2 || p.split_k == 4 || p.split_k == 8);
+  p.cluster_k = in_cluster && p.split_k >= 2 && p.split_k <= 8;
   XTC_REQUIRE(p.cluster_k || !in_cluster || p.split_k == 1,
-              "conv2d: the cluster split needs 2, 4 or 8 pieces, got %d", p.split_k);
+              "conv2d: the cluster split needs 2 to 8 pieces, got %d", p.split_k);
   p.relu = a.relu;
   p.relu_threshold = a.thr;
   p.status = device_status_word(dev);
@@ -547,11 +547,11 @@ static size_t conv_split_bytes(int64_t M, int64_t F, const AutoChoice& pick) {
   return ((tiles * 4 + 255) & ~static_cast<size_t>(255)) +
          static_cast<size_t>(pick.split_k) * tiles * BM * pick.tile_n * 4;
 }
-// A split the im2col launcher reduces inside a thread-block cluster (no workspace): 2, 4 or
-// 8 pieces of a tile at most 128 filters wide, with every cluster resident at once.
+// A split the im2col launcher reduces inside a thread-block cluster (no workspace): 2 to 8
+// pieces of a tile at most 128 filters wide, with every cluster resident at once.
 static bool conv_split_in_cluster(int64_t M, int64_t F, const AutoChoice& pick, int dev) {
   if (pick.tile_m != BM || pick.tile_n > 128 || F % 4 != 0) return false;
-  if (pick.split_k != 2 && pick.split_k != 4 && pick.split_k != 8) return false;
+  if (pick.split_k < 2 || pick.split_k > 8) return false;
   const int64_t tiles = ((M + BM - 1) / BM) * ((F + pick.tile_n - 1) / pick.tile_n);
   return tiles <= cluster_capacity(dev, pick.split_k);
 }
@@ -639,7 +639,7 @@ extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, 
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
   int caps[9] = {};
-  for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+  for (int sz = 2; sz <= 8; ++sz) caps[sz] = cluster_capacity(dev, sz);
   const AutoChoice pick =
       choose_tf32_default(M, F, R * S * ((C + 31) / 32 * 32), sms, true, true, F % 4 == 0 ? caps : nullptr,
                           false);
@@ -778,7 +778,7 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     // (split-K only with the zeroed workspace xtc_cuda_conv2d_workspace_bytes asks for)
     const int64_t kpad = R * S * ((C + 31) / 32 * 32);
     int caps[9] = {};
-    for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+    for (int sz = 2; sz <= 8; ++sz) caps[sz] = cluster_capacity(dev, sz);
     AutoChoice pick = choose_tf32_default(M, F, kpad, sm_count(dev), a16(Y), true,
                                           a16(Y) && F % 4 == 0 ? caps : nullptr, false);
     const size_t need = conv_split_bytes(M, F, pick);

@@ -172,9 +172,9 @@ int launch_tc(const LaunchArgs& a) {
   p.partials = a.partials;
   p.tile_counters = a.counters;
   if (p.split_k > 1) p.chunk_kblocks = p.split_kblocks;
-  p.cluster_k = in_cluster && (p.split_k == 2 || p.split_k == 4 || p.split_k == 8);
+  p.cluster_k = in_cluster && p.split_k >= 2 && p.split_k <= 8;
   XTC_REQUIRE(p.cluster_k || !in_cluster || p.split_k == 1,
-              "gemm: the cluster split needs 2, 4 or 8 pieces, got %d", p.split_k);
+              "gemm: the cluster split needs 2 to 8 pieces, got %d", p.split_k);
 
   auto kernel = gemm_tf32_kernel<BN, KSPANS, A_MODE, B_MN, SPLIT3, TMA_STORE>;
   const int smem = L::total(stages, TMA_STORE);
@@ -466,11 +466,12 @@ int cluster_capacity(int dev, int size) {
 // 256x256 pair tile, 128 for 128x128, 192 for 128x256, 96 for 256x128 and 128x64), times
 // the K steps, times the rounds of tiles over the SMs (the split tail of the pair kernel
 // shortens a last round that is at most half full), plus a fixed 6 us; single-CTA
-// candidates with few tiles may split K.  Tiles up to 128 columns wide split into 2, 4 or
-// 8 pieces inside a thread-block cluster while all clusters fit on the device at once
-// (`cluster_cap[s]`, NULL = no cluster split): 1 us + 1 us per 64 tile columns + 0.1 us per
-// piece for the reduction through distributed shared memory (512x256x1024: 10.0 us
-// unsplit, 7.6 us in 4 pieces; 256x256x4096: 29.1 us unsplit, 9.6 us in 8 pieces).
+// candidates with few tiles may split K.  Tiles up to 128 columns wide split into 2 to 8
+// pieces inside a thread-block cluster while all clusters fit on the device at once
+// (`cluster_cap[s]`, NULL = no cluster split): 1 us + 1 us per 64 tile columns + 0.25 us per
+// piece for the reduction through distributed shared memory (512x256x1024: 10.1 us
+// unsplit, 7.9 us in 4 pieces, 8.2 us in 6; 256x256x4096: 29.1 us unsplit, 9.9 us in 8
+// pieces; 512x512x8192: 23.5 us in 4 pieces, 19.5 us in 6).
 // Other splits go through a workspace (`split_ok`), which costs 3 us + 1.15 us per piece
 // for the reduction pass.
 AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pair_ok,
@@ -500,10 +501,13 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
       return {256, 128, 64, 1};  // the pair kernel cuts K itself
     const int64_t tiles = ((M + 127) / 128) * ((N + 127) / 128);
     int split = 1;
-    if (cluster_cap != nullptr && N % 4 == 0)
-      while (split < 8 && tiles * split * 2 <= sms && tiles <= cluster_cap[split * 2] &&
-             K / (split * 2) >= 1024)
-        split *= 2;
+    if (cluster_cap != nullptr && N % 4 == 0) {
+      // the most pieces that leave every cluster resident and 768 of K to a piece
+      // (169 x 1024 x 4608: 16.9 us in 4 pieces, 14.9 us in 6; 289 x 1024 x 9216: 25.8 us in 4, 23.0 in 5)
+      const int kblocks = static_cast<int>((K + 63) / 64);
+      for (int s = 2; s <= 8 && tiles * s <= sms && K / s >= 768; ++s)
+        if (tiles <= cluster_cap[s] && cluster_pieces(kblocks, s) == s) split = s;
+    }
     return {128, 128, 64, split};
   }
   for (const Cand& c : cands) {
@@ -536,8 +540,11 @@ AutoChoice choose_tf32_default(int64_t M, int64_t N, int64_t K, int sms, bool pa
     int split = 1;
     const int64_t kblocks = (K + tile_k - 1) / tile_k;
     if (cluster_cap != nullptr && c.tm == 128 && c.tn <= 128 && N % 4 == 0) {
-      for (int s = 2; s <= 8 && tiles <= cluster_cap[s] && tiles * s <= slots && s <= kblocks; s *= 2) {
-        const double ts = ksteps * c.clk / s + fixed + (1.0 + c.tn / 64.0 + 0.1 * s) * clk_per_us;
+      for (int s = 2; s <= 8 && tiles <= cluster_cap[s] && tiles * s <= slots && s <= kblocks; ++s) {
+        if (cluster_pieces(static_cast<int>(kblocks), s) != s) continue;  // an empty last piece
+        // the longest piece sets the pace: ceil(kblocks / s) stages of tile_k
+        const double piece_steps = static_cast<double>((kblocks + s - 1) / s) * (tile_k / 8);
+        const double ts = piece_steps * c.clk + fixed + (1.0 + c.tn / 64.0 + 0.25 * s) * clk_per_us;
         if (ts < t) { t = ts; split = s; }
       }
     }
@@ -612,7 +619,7 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
   if (is_full_auto(c)) {  // size for what the library would pick itself (see gemm_impl)
     int caps[9] = {};
-    for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+    for (int sz = 2; sz <= 8; ++sz) caps[sz] = cluster_capacity(dev, sz);
     const AutoChoice pick = choose_tf32_default(M, N, K, sms, true, true, caps);
     c.tile_m = pick.tile_m;
     c.tile_n = pick.tile_n;
@@ -628,7 +635,7 @@ extern "C" int xtc_cuda_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, in
     const TfShape s = resolve_tf32_shape(M, N, K, c, sms);
     // a split the launcher reduces inside a cluster needs nothing (assuming, as the launcher
     // checks, a 16-byte aligned C with a pitch that is a multiple of 4)
-    const bool in_cluster = c.variant != 1 && (s.split_k == 2 || s.split_k == 4 || s.split_k == 8) &&
+    const bool in_cluster = c.variant != 1 && s.split_k >= 2 && s.split_k <= 8 &&
                             s.tile_n <= 128 && N % 4 == 0 && s.tiles <= cluster_capacity(dev, s.split_k);
     if (s.split_k > 1 && !in_cluster)  // tile counters, then the partial tiles [split][tile][128][tile_n]
       *bytes = align256(static_cast<size_t>(s.tiles) * 4) +
@@ -644,7 +651,7 @@ extern "C" int xtc_cuda_gemm_default_config(int64_t M, int64_t N, int64_t K, xtc
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
   int caps[9] = {};
-  for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+  for (int sz = 2; sz <= 8; ++sz) caps[sz] = cluster_capacity(dev, sz);
   const AutoChoice pick = choose_tf32_default(M, N, K, sms, true, true, caps);
   out->tile_m = pick.tile_m;
   out->tile_n = pick.tile_n;
@@ -717,7 +724,7 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
 
   if (full_auto) {
     int caps[9] = {};
-    for (int sz = 2; sz <= 8; sz *= 2) caps[sz] = cluster_capacity(dev, sz);
+    for (int sz = 2; sz <= 8; ++sz) caps[sz] = cluster_capacity(dev, sz);
     const AutoChoice pick = choose_tf32_default(M, N, K, sm_count(dev), tma_addressable(C, ldc), true,
                                                 tma_addressable(C, ldc) && n_extra == 0 ? caps : nullptr);
     c.tile_m = pick.tile_m;
@@ -744,10 +751,10 @@ static int gemm_impl(const float* A, const float* B, float* C, int64_t M, int64_
   int tile_n = c.tile_n ? c.tile_n : shp.tile_n;
   if (c.precision == XTC_CUDA_PRECISION_3XTF32 && c.tile_n == 0 && tile_n > 128) tile_n = 128;
   const int tile_k = c.tile_k ? c.tile_k : 32;
-  // 2, 4 or 8 pieces of tiles up to 128 columns wide are reduced inside a thread-block cluster
+  // 2 to 8 pieces of tiles up to 128 columns wide are reduced inside a thread-block cluster
   // (variant = 1 keeps the workspace form)
   const bool cluster_split = shp.split_k > 1 && n_extra == 0 && c.variant != 1 &&
-                             (shp.split_k == 2 || shp.split_k == 4 || shp.split_k == 8) &&
+                             shp.split_k >= 2 && shp.split_k <= 8 &&
                              shp.tile_n <= 128 && tma_addressable(C, ldc) && N % 4 == 0 &&
                              c.precision == XTC_CUDA_PRECISION_TF32 &&
                              shp.tiles <= cluster_capacity(dev, shp.split_k);

@@ -70,9 +70,9 @@ struct GemmParams {
   float* partials;
   int* tile_counters;
   // Split-K inside a thread-block cluster (cluster_k = 1; split_k is the cluster size,
-  // 2, 4 or 8; one work item per CTA): the CTAs of a cluster hold the K pieces of one
+  // 2 to 8; one work item per CTA): the CTAs of a cluster hold the K pieces of one
   // tile, park their accumulators in their own shared memory (the operand ring is free
-  // by then) and each sums 128 / split_k rows of the tile over all pieces through
+  // by then) and each sums ceil(128 / split_k) rows of the tile over all pieces through
   // distributed shared memory, in piece order.  No workspace, no pass through L2.
   int cluster_k;
   // Split tail of the CTA-pair kernel (gemm_tf32_pair.cuh): the tail_tiles tiles of
@@ -548,7 +548,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
-      const int rows_own = BM / p.split_k;
+      const int rows_own = (BM + p.split_k - 1) / p.split_k;  // the last piece may own fewer
       const int rank = static_cast<int>(cluster_ctarank());  // = this CTA's piece
       const uint32_t red_base = smem_u32(ring);
       // Two float4 of the tile per thread and round, all their pieces requested before the first
@@ -557,16 +557,28 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int total = rows_own * (BN / 4);
       constexpr int STRIDE = EPI_WARPS * 32;
       for (int i = (warp - 2) * 32 + lane; i < total; i += 2 * STRIDE) {
-        const int i2 = i + STRIDE < total ? i + STRIDE : i;  // the last odd round repeats its item
-        const int qa = i / rows_own, qb = i2 / rows_own;
-        const int row_a = rank * rows_own + (i - qa * rows_own);
-        const int row_b = rank * rows_own + (i2 - qb * rows_own);
+        // items ia and ib; a row past the tile (128 does not divide by 3, 5, 6 or 7) or the
+        // missing partner of a last odd round is replaced by the other item, whose store
+        // then happens once
+        int ia = i, ib = i + STRIDE < total ? i + STRIDE : i;
+        const bool ok_a = rank * rows_own + ia % rows_own < BM;
+        const bool ok_b = rank * rows_own + ib % rows_own < BM;
+        if (!ok_a && !ok_b) continue;
+        if (!ok_a) ia = ib;
+        if (!ok_b) ib = ia;
+        const int qa = ia / rows_own, qb = ib / rows_own;
+        const int row_a = rank * rows_own + (ia - qa * rows_own);
+        const int row_b = rank * rows_own + (ib - qb * rows_own);
         const uint32_t addr_a = red_base + static_cast<uint32_t>(qa * BM + row_a) * 16u;
         const uint32_t addr_b = red_base + static_cast<uint32_t>(qb * BM + row_b) * 16u;
         float4 acc_a, acc_b;
         switch (p.split_k) {  // fixed piece order: bit-reproducible
           case 2: sum_cluster_pieces<2>(addr_a, addr_b, acc_a, acc_b); break;
+          case 3: sum_cluster_pieces<3>(addr_a, addr_b, acc_a, acc_b); break;
           case 4: sum_cluster_pieces<4>(addr_a, addr_b, acc_a, acc_b); break;
+          case 5: sum_cluster_pieces<5>(addr_a, addr_b, acc_a, acc_b); break;
+          case 6: sum_cluster_pieces<6>(addr_a, addr_b, acc_a, acc_b); break;
+          case 7: sum_cluster_pieces<7>(addr_a, addr_b, acc_a, acc_b); break;
           default: sum_cluster_pieces<8>(addr_a, addr_b, acc_a, acc_b); break;
         }
         if (p.relu) {
@@ -579,7 +591,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (grow_a < p.M && gcol_a < p.N)  // N is a multiple of 4 in this mode
           *reinterpret_cast<float4*>(p.C + static_cast<size_t>(grow_a) * p.ldc + gcol_a) = acc_a;
         const int grow_b = m0 + row_b, gcol_b = n0 + 4 * qb;
-        if (i2 != i && grow_b < p.M && gcol_b < p.N)
+        if (ib != ia && grow_b < p.M && gcol_b < p.N)
           *reinterpret_cast<float4*>(p.C + static_cast<size_t>(grow_b) * p.ldc + gcol_b) = acc_b;
       }
     }

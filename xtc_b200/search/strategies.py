@@ -12,7 +12,7 @@ is the shared-memory budget of the pipeline.
 
 Sample layout of ``cuda_gemm`` (also used for conv2d):
     [tile_m, tile_n, tile_k, stages, tma_store, split_k]
-``split_k`` (1, 2, 4, 8) cuts a matmul's reduction into segments that run
+``split_k`` (1 to 8) cuts a matmul's reduction into segments that run
 concurrently, one CTA of a thread-block cluster each (``scheduler.split``).
 """
 
@@ -47,7 +47,7 @@ class StrategyCudaGemm:
     TILE_N = (64, 128, 256)
     TILE_K = (32, 64)
     STAGES = (0, 2, 3, 4, 6)  # 0 = as deep as shared memory allows
-    SPLITS = (1, 2, 4, 8)     # pieces of the reduction (matmul, one CTA per tile, tile_n <= 128)
+    SPLITS = (1, 2, 3, 4, 5, 6, 7, 8)  # pieces of the reduction (one CTA per tile, tile_n <= 128)
 
     def __init__(self, graph: Any, tile_m: tuple[int, ...] | None = None,
                  tile_n: tuple[int, ...] | None = None, tile_k: tuple[int, ...] | None = None,
@@ -180,7 +180,7 @@ class StrategyCudaConv:
                  CTA, the input through a ring of 128-position chunks (at most 128 filters, a
                  halo run of at most 256 positions); no other parameter applies
       variant 1  implicit GEMM, one im2col fetch per filter tap: the GEMM kernels' tile_m /
-                 tile_n / tile_k / stages / epilogue, and split_k = 2, 4, 8 pieces of the
+                 tile_n / tile_k / stages / epilogue, and split_k = 2 to 8 pieces of the
                  reduction in one thread-block cluster (one CTA per tile, tile_n <= 128)
     """
 
@@ -238,7 +238,7 @@ class StrategyCudaConv:
                     and tn == (64 if self._f <= 64 else 128 if self._f <= 128 else 256))
         if variant != 1 or self._c % 4 or self._f % 4:
             return False
-        if not self._gemm.is_legal([tm, tn, tk, st, tma, 1]) or split not in (1, 2, 4, 8):
+        if not self._gemm.is_legal([tm, tn, tk, st, tma, 1]) or split not in StrategyCudaGemm.SPLITS:
             return False
         k_blocks = self._r * self._s * -(-self._c // tk)
         return split == 1 or (tm == 128 and tn <= 128 and split <= k_blocks)
@@ -253,7 +253,7 @@ class StrategyCudaConv:
         if self.is_legal([4, 128, min(tn_res, 128), 32, 0, 0, 1]):
             yield [4, 128, min(tn_res, 128), 32, 0, 0, 1]
         for tm, tn, tk, st, tma, split in itertools.product(g.tile_m, g.tile_n, g.tile_k, g.stages,
-                                                            (0, 1), (1, 2, 4, 8)):
+                                                            (0, 1), StrategyCudaGemm.SPLITS):
             s = [1, tm, tn, tk, st, tma, split]
             if self.is_legal(s):
                 yield s
