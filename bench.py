@@ -596,10 +596,19 @@ def other_configs(torch, dev, args, peaks: dict, heavy: bool) -> dict:
         from xtc_b200.backends.cuda import Backend
         from xtc_b200.search import Exploration, ExplorationConfig
 
+        from xtc_b200 import artifacts
+
         out = {}
-        for operator, name in (("conv2d", "ResNet18_01"), ("conv2d", "Yolo9000_18"), ("matmul", "AlexNet_FC7"),
-                               ("matmul", "Gemma2B_QK"), ("matmul", "Llama3_In")):
-            exp = Exploration(ExplorationConfig(operator=operator, op_name=name, peak_flops=1e15))
+        layers = [(operator, name, None) for operator, name in (
+            ("conv2d", "ResNet18_01"), ("conv2d", "Yolo9000_18"), ("matmul", "AlexNet_FC7"),
+            ("matmul", "Gemma2B_QK"), ("matmul", "Llama3_In"))]
+        # the reference's ResNet layers at the batch of c3 (its table holds one image each)
+        for name in ("ResNet18_02", "ResNet18_06", "ResNet18_09"):
+            dims = artifacts.operation_dims("conv2d", name)
+            layers.append(("conv2d", f"{name}_batch32", [32] + dims[1:]))
+        for operator, name, dims in layers:
+            exp = Exploration(ExplorationConfig(operator=operator, op_name=None if dims else name, dims=dims,
+                                                peak_flops=1e15))
             impl = Backend(exp.graph)
             module = impl.get_compiler(shared_lib=False).compile(impl.get_scheduler().schedule())
             times, code, msg = module.get_evaluator(repeat=3, number=50, min_repeat_ms=0).evaluate()

@@ -119,7 +119,14 @@ typedef struct xtc_cuda_gemm_config {
                         4 = resident weights with a sliding input window: a run of
                         consecutive tiles per CTA, the input through a ring of
                         128-position chunks (stride 1, at most 128 filters, a halo
-                        run of at most 256 positions).
+                        run of at most 256 positions);
+                        5 = streamed weights beside halo tiles, for filter banks that
+                        do not fit in shared memory: CTA pairs, 128 filters per work
+                        item, a pipeline stage = one 32-channel halo slab + the
+                        weights of every tap (stride 1, C and F multiples of 4, 2 to
+                        32 taps, two such stages in shared memory; `stages` applies).
+                        With nothing named the library takes it where the whole bank
+                        does not fit one CTA and the layer has work for most pairs.
                         GEMM with tile_m = 256: 2 = store C without the L2
                         evict-first hint (the default hints it)                   */
   int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off unless

@@ -80,8 +80,10 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
     assert strat.node_name == "conv"
     space = list(strat.exhaustive())
     assert len(space) == len({tuple(s) for s in space}) > 100
-    assert {s[0] for s in space} == {1, 2, 3, 4}
+    assert {s[0] for s in space} == {1, 2, 3, 4, 5}
     assert [s for s in space if s[0] == 4] == [[4, 128, 64, 32, 0, 0, 1]]  # the sliding input window
+    # streamed weights: two stages of a halo slab + nine taps' weights fit, not three
+    assert [s for s in space if s[0] == 5] == [[5, 256, 128, 32, 0, 0, 1], [5, 256, 128, 32, 2, 0, 1]]
     resident = [s for s in space if s[0] == 2]
     assert {(s[1], s[3]) for s in resident} == {(128, 16), (128, 32), (256, 32)}
     assert {(s[1], s[3]) for s in space if s[0] == 3} == {(128, 16), (128, 32)}  # two taps per MMA
@@ -91,7 +93,10 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
         sch = Backend(graph).get_scheduler(strict=True)
         strat.generate(sch, s)
         cfg = sch.schedule().node_configs()["conv"]
-        assert cfg.get("variant", 0) == (s[0] if s[0] in (2, 3, 4) else 0)
+        assert cfg.get("variant", 0) == (s[0] if s[0] in (2, 3, 4, 5) else 0)
+        if s[0] == 5:  # the kernel has one tile shape: only the pipeline depth is a parameter
+            assert cfg == ({"variant": 5, "stages": s[4]} if s[4] else {"variant": 5})
+            continue
         assert (cfg["tile_m"], cfg["tile_k"], cfg.get("stages", 0)) == (s[1], s[3], s[4])
         assert cfg.get("split_k", 1) == s[6] and cfg.get("epilogue", 0) == (2 if s[5] else 0)
         if s[0] == 1:
@@ -102,8 +107,9 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
     # a strided layer, or a bank too large to keep on chip, has only the im2col kernels
     strided = Strategies.create("cuda_conv", conv2d_graph(1, 28, 28, 128, 3, 3, 64, 2, 2))
     assert {s[0] for s in strided.exhaustive()} == {1} and strided.default_schedule(3)[0] == 1
+    assert strided.streamed_stages() == 0
     big = Strategies.create("cuda_conv", conv2d_graph(1, 14, 14, 256, 3, 3, 256, 1, 1))
-    assert all(s[0] == 1 for s in big.exhaustive())
+    assert {s[0] for s in big.exhaustive()} == {1, 5}  # im2col, or streamed weights beside halo tiles
     half = Strategies.create("cuda_conv", conv2d_graph(1, 28, 28, 128, 3, 3, 64, 1, 1))
     assert {(s[1], s[3]) for s in half.exhaustive() if s[0] == 2} >= {(256, 32)}
     # a halo run of more than 256 positions (112-wide rows) does not go through the ring

@@ -17,6 +17,7 @@ mapping side is new: for a contraction node (matmul / conv2d)
                                                                  operand idx into the GEMM
   split(k, {n segments})   matmul reduction cut into segments -> split-K over n CTAs per tile
                            (conv2d: split(c, ...), the im2col kernels)
+  pack_at(_, 0)            conv2d input window packed on chip, alone -> streamed weights + halo tiles
   pack_at(_, 1)            conv2d filter bank packed on chip  -> resident weights + halo tiles;
                            the first tile of c is then the channel slab of a stage (16 or 32),
                            tile(s, {s1: 2}) puts two neighbouring filter taps into one MMA;
@@ -261,6 +262,11 @@ class CudaNodeScheduler:
             elif any(0 in idx for idx in self.packed_buffers.values()):
                 # pack_at(_, 0) too: the input window stays on chip from one tile to the next
                 cfg["variant"] = 4
+        elif self.op_name == "conv2d" and any(0 in idx for idx in self.packed_buffers.values()):
+            # pack_at(_, 0) alone: a tile's input window is packed on chip once per channel slab
+            # and read by every filter tap, the weights stream beside it (CTA pairs, 128 filters)
+            cfg = {k: v for k, v in cfg.items() if k not in ("tile_m", "tile_n", "tile_k", "split_k", "epilogue")}
+            cfg["variant"] = 5
         return cfg
 
     def node_schedule(self, strict: bool = False) -> CudaNodeSchedule:

@@ -77,6 +77,10 @@ struct ConvHaloParams {
   int stages;
   int relu;
   float relu_threshold;
+  // streamed-weights kernel (conv2d_halo_stream.cuh) only
+  int ntiles_n;           // filter tiles of 128
+  int wts_offset;         // where a stage's weights start (the halo slab rounded up to 1024 bytes)
+  int wts_tx;             // bytes of weights one CTA fetches per stage: taps * 64 * 128
 };
 
 constexpr int HALO_THREADS = 224;  // producer, two MMA issuers, four epilogue warps

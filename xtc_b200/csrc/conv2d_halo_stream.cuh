@@ -1,0 +1,274 @@
+// Halo-tile convolution with STREAMED weights, for layers whose filter bank does not fit in
+// shared memory (3x3x128 -> 128 and deeper): stride 1, CTA pairs (conv2d_halo_pair.cuh).
+//
+// The im2col kernels fetch a tile's pixels once per filter tap: for a 3x3 filter 1.2 MB of
+// pixels and 1.2 MB of weights go through one SM's shared memory per 128 x 128 tile of
+// 256 input channels, and that fill rate, not the tensor pipe, sets their pace.  Here a pipeline
+// stage is one 32-channel slab: the halo run of the tile's positions (one im2col-mode TMA copy,
+// 128 + (R-1)*Wp + (S-1) pixel rows of 128 bytes, read by every tap at its own row offset) and
+// the weights of ALL taps for those 32 channels and this CTA's 64 filters (two 3-D TMA copies of
+// taps x 32 x 32 floats).  Two CTAs share one 256 x 128 MMA (cta_group::2): each owns 128
+// consecutive positions and half of the 128 filters of the tile, so a 3x3 stage is 32 KB of
+// pixels and 72 KB of weights per CTA for 36 MMAs of 256 x 128 x 8, and the tensor pipe is
+// the bound again.  Work items are (position tile, filter tile) pairs; like the other halo
+// kernels this one computes every position of the padded grid and stores the valid ones.
+//
+// Stage layout: [halo slab, rounded up to 1024 bytes][filter group 0: taps x 4 KB][group 1:
+// taps x 4 KB]; a tap's block is 32 k-rows of 32 filters, the MN-major operand layout of
+// conv2d_halo.cuh, and the two groups of a tap lie taps * 4096 bytes apart (the descriptor's
+// leading-dimension offset).
+//
+// Barriers (no multicast anywhere):
+//   full[s]      leader only; both CTAs' copies of a stage report to it.
+//   empty[s]     one per CTA; the leader commits to both.
+//   acc_full[a]  one per CTA; the leader commits to both.
+//   acc_empty[a] leader only, 8 arrivals (4 epilogue warps of each CTA).
+#pragma once
+#include "conv2d_halo.cuh"
+
+namespace xtc {
+
+constexpr int STREAM_BN = 128;
+
+template <bool DUAL>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HALO_THREADS, 1)
+conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
+                          const __grid_constant__ CUtensorMap tmW, const ConvHaloParams p) {
+  using namespace dev;
+  constexpr int BN = STREAM_BN;
+  constexpr int HALF = BN / 2;
+  constexpr int NACC = DUAL ? 2 : 1;  // accumulators per tile, one per issuing thread
+  constexpr uint32_t TMEM_COLS = 2 * NACC * BN;
+  static_assert(TMEM_COLS <= 512, "accumulators do not fit in TMEM");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(p.stages) * p.stage_bytes);
+  uint64_t* full = bars;           // [stages]
+  uint64_t* empty = bars + 8;      // [stages]
+  uint64_t* acc_full = bars + 16;  // [2]
+  uint64_t* acc_empty = bars + 18; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmX);
+    prefetch_tmap(&tmW);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], NACC);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], NACC);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  grid_dependency_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int plane = p.Hp * p.Wp;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------ producer --------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * 4096u;
+      for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs) {
+        const int ptile = tile / p.ntiles_n;
+        const int ntile = tile - ptile * p.ntiles_n;
+        long long q0 = static_cast<long long>(ptile) * (2 * BM) + static_cast<long long>(rank) * BM;
+        if (q0 >= p.Q) q0 = 0;  // nothing of this half is stored; fetch something valid
+        const int img = static_cast<int>(q0 / plane);
+        const int rem = static_cast<int>(q0 - static_cast<long long>(img) * plane);
+        const int ih = rem / p.Wp - p.pad_top;
+        const int iw = rem % p.Wp - p.pad_left;
+        const int f0 = ntile * BN + static_cast<int>(rank) * HALF;
+        for (int slab = 0; slab < p.nslab; ++slab) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
+            failed = true;
+            break;
+          }
+          if (leader)
+            mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(2 * (p.stage_tx + p.wts_tx)));
+          uint8_t* dst = ring + static_cast<size_t>(stage) * p.stage_bytes;
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          tma_load_im2col_4d_pair(dst, &tmX, bar, slab * 32, iw, ih, img, 0, 0);
+#pragma unroll
+          for (int g = 0; g < HALF / 32; ++g)
+            tma_load_3d_pair(dst + p.wts_offset + g * group_bytes, &tmW, bar, f0 + g * 32, slab * 32, 0);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp <= 2) {
+    // ------------------------ MMA issuers (leader CTA) ------------------------
+    // Warps 1 and 2 share the taps of every slab (see conv2d_halo.cuh on why two).
+    const int w = warp - 1;
+    if (lane == 0 && leader && w < NACC) {
+      constexpr uint32_t idesc = umma_idesc_tf32(2 * BM, BN, false, true);
+      const int t0 = DUAL ? (w == 0 ? 0 : (p.taps + 1) / 2) : 0;
+      const int t1 = DUAL ? (w == 0 ? (p.taps + 1) / 2 : p.taps) : p.taps;
+      const int r0 = t0 / p.S, s0 = t0 - r0 * p.S;
+      const uint32_t a_hi = umma_desc_hi(1024, static_cast<uint32_t>(UMMA_SWIZZLE_128B));
+      const uint32_t b_hi = umma_desc_hi(512, static_cast<uint32_t>(UMMA_SWIZZLE_128B_BASE32B));
+      const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * 4096u;
+      const uint32_t row_step = static_cast<uint32_t>(p.Wp) * 8u;
+      const uint32_t a_first = static_cast<uint32_t>(r0) * row_step;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_DRAIN);
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (acc * NACC + w) * BN;
+        for (int slab = 0; slab < p.nslab; ++slab) {
+          if (!mbar_wait(&full[stage], phase)) {
+            atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * p.stage_bytes);
+          uint32_t a_row = umma_desc_lo(sA, 16) + a_first;
+          uint32_t b_lo = umma_desc_lo(sA + static_cast<uint32_t>(p.wts_offset) +
+                                           static_cast<uint32_t>(t0) * 4096u, group_bytes);
+          uint32_t first = slab == 0 ? 0u : 1u;
+          for (int tap = t0, s = s0; tap < t1; ++tap) {
+            const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * 8u;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              umma_tf32_pair(d_tmem, umma_desc_pack(a_lo + kk * 2, a_hi),
+                             umma_desc_pack(b_lo + kk * 64, b_hi), idesc, first | (kk != 0));
+            }
+            first = 1u;
+            b_lo += 4096u >> 4;
+            if (++s == p.S) {
+              s = 0;
+              a_row += row_step;
+            }
+          }
+          const uint32_t e = smem_u32(&empty[stage]);
+          tc_commit_pair(map_to_cta(e, 0));
+          tc_commit_pair(map_to_cta(e, 1));
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!failed) {
+          const uint32_t f = smem_u32(&acc_full[acc]);
+          tc_commit_pair(map_to_cta(f, 0));
+          tc_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    // --------------------------- epilogue (both CTAs) --------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const bool vec_ok = (p.F % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0);
+    const bool wide_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 31) == 0);
+    int local = 0;
+    for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase)) {
+        if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const int ptile = tile / p.ntiles_n;
+      const int n0 = (tile - ptile * p.ntiles_n) * BN;
+      const long long q = static_cast<long long>(ptile) * (2 * BM) + static_cast<long long>(rank) * BM +
+                          quad * 32 + lane;
+      const int img = static_cast<int>(q / plane);
+      const int rem = static_cast<int>(q - static_cast<long long>(img) * plane);
+      const int oh = rem / p.Wp;
+      const int ow = rem - oh * p.Wp;
+      const bool valid = q < p.Q && oh < p.OH && ow < p.OW;
+      float* dst = p.Y + ((static_cast<long long>(img) * p.OH + oh) * p.OW + ow) * p.F + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + lane_base + acc * NACC * BN + c * 32, r);
+        if (DUAL) {
+          uint32_t r2[32];
+          tmem_ld_32x32(tmem_base + lane_base + (acc * NACC + 1) * BN + c * 32, r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+        } else {
+          tmem_ld_wait();
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), p.relu_threshold));
+        }
+        if (valid) {
+          const int col0 = c * 32;
+          if (wide_ok && n0 + col0 + 32 <= p.F) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) st_global_f8(dst + col0 + 8 * j, r + 8 * j);
+          } else if (vec_ok && n0 + col0 + 32 <= p.F) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              reinterpret_cast<float4*>(dst + col0)[j] =
+                  make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                              __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (n0 + col0 + i < p.F) dst[col0 + i] = __uint_as_float(r[i]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+    }
+  }
+
+  if (failed) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace xtc

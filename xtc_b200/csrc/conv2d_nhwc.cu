@@ -9,6 +9,7 @@
 #include "conv2d_halo_pair.cuh"
 #include "conv2d_halo_taps.cuh"
 #include "conv2d_halo_slide.cuh"
+#include "conv2d_halo_stream.cuh"
 #include "gemm_tf32_pair.cuh"
 
 #ifdef XTC_TRACE
@@ -440,6 +441,109 @@ int launch_conv_slide(const ConvArgs& a, const SlidePlan& h) {
   return XTC_CUDA_OK;
 }
 
+// The streamed-weights form (conv2d_halo_stream.cuh): stride 1, CTA pairs, a stage = one
+// 32-channel halo slab + the weights of every tap for this CTA's 64 filters; at least two stages.
+struct StreamPlan {
+  bool ok = false;
+  int P = 0, stages = 0, stage_bytes = 0, wts_offset = 0, wts_tx = 0, nslab = 0, smem = 0;
+};
+StreamPlan plan_stream(const ConvArgs& a) {
+  StreamPlan s;
+  if (a.sh != 1 || a.sw != 1 || a.C % 4 != 0 || a.F % 4 != 0) return s;
+  const int64_t taps = a.R * a.S;
+  if (taps < 2 || taps > 32) return s;  // a single tap is a plain GEMM: nothing to share
+  const int64_t Wp = a.W + a.pl + a.pr;
+  const int64_t P = BM + (a.R - 1) * Wp + (a.S - 1);
+  if (P > 1024 || a.pl > 127 || a.pt > 127 || a.pr > 127 || a.pb > 127) return s;
+  s.P = static_cast<int>(P);
+  s.wts_offset = static_cast<int>((P * 128 + 1023) / 1024 * 1024);
+  s.wts_tx = static_cast<int>(taps * (STREAM_BN / 2) * 128);
+  s.stage_bytes = s.wts_offset + s.wts_tx;
+  const int64_t fixed = 1024 + 1024;  // alignment slack, barriers
+  const int64_t stages = (232448 - fixed) / s.stage_bytes;
+  if (stages < 2) return s;
+  s.stages = static_cast<int>(stages > 4 ? 4 : stages);
+  s.nslab = static_cast<int>((a.C + 31) / 32);
+  s.smem = static_cast<int>(fixed + static_cast<int64_t>(s.stages) * s.stage_bytes);
+  s.ok = true;
+  return s;
+}
+
+int launch_conv_stream(const ConvArgs& a, const StreamPlan& h) {
+  encode_im2col_fn enc = get_encode_im2col();
+  encode_tiled_fn enc_tiled = get_encode_tiled();
+  XTC_REQUIRE(enc != nullptr && enc_tiled != nullptr,
+              "cuTensorMapEncodeIm2col / Tiled are not available from this driver");
+  int dev = 0;
+  XTC_CUDA_CHECK(cudaGetDevice(&dev));
+  const int64_t Hp = a.H + a.pt + a.pb, Wp = a.W + a.pl + a.pr;
+  CUtensorMap tmX, tmW;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W),
+                        static_cast<cuuint64_t>(a.H), static_cast<cuuint64_t>(a.B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(a.C) * 4, static_cast<cuuint64_t>(a.W * a.C) * 4,
+                           static_cast<cuuint64_t>(a.H * a.W * a.C) * 4};
+  int lower[2] = {-a.pl, -a.pt};
+  int upper[2] = {a.pr, a.pb};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.X), dims, strides,
+                   lower, upper, 32, static_cast<cuuint32_t>(h.P), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  XTC_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeIm2col (streamed halo) failed (%d)", static_cast<int>(r));
+  // the filter as [tap][channel][filter]: one copy = every tap x 32 channels x 32 filters
+  const int taps = static_cast<int>(a.R * a.S);
+  cuuint64_t wdims[3] = {static_cast<cuuint64_t>(a.F), static_cast<cuuint64_t>(a.C),
+                         static_cast<cuuint64_t>(taps)};
+  cuuint64_t wstrides[2] = {static_cast<cuuint64_t>(a.F) * 4, static_cast<cuuint64_t>(a.C * a.F) * 4};
+  cuuint32_t wbox[3] = {32, 32, static_cast<cuuint32_t>(taps)};
+  r = enc_tiled(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(a.Wt), wdims, wstrides, wbox,
+                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  XTC_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (streamed weights) failed (%d)", static_cast<int>(r));
+
+  ConvHaloParams p;
+  memset(&p, 0, sizeof(p));
+  p.Y = a.Y;
+  p.status = device_status_word(dev);
+  XTC_REQUIRE(p.status != nullptr, "conv2d: device status word unavailable");
+  p.Q = a.B * Hp * Wp;
+  p.ntiles_n = static_cast<int>((a.F + STREAM_BN - 1) / STREAM_BN);
+  const int64_t tiles = (p.Q + 2 * BM - 1) / (2 * BM) * p.ntiles_n;
+  XTC_REQUIRE(tiles < (1ll << 31), "conv2d: %lld work items", static_cast<long long>(tiles));
+  p.tiles = static_cast<int>(tiles);
+  p.Hp = static_cast<int>(Hp);
+  p.Wp = static_cast<int>(Wp);
+  p.OH = static_cast<int>(a.OH);
+  p.OW = static_cast<int>(a.OW);
+  p.F = static_cast<int>(a.F);
+  p.nslab = h.nslab;
+  p.nblk = h.nslab;
+  p.C = static_cast<int>(a.C);
+  p.taps = taps;
+  p.S = static_cast<int>(a.S);
+  p.pad_left = a.pl;
+  p.pad_top = a.pt;
+  p.stage_bytes = h.stage_bytes;
+  p.stage_tx = h.P * 128;
+  p.wts_offset = h.wts_offset;
+  p.wts_tx = h.wts_tx;
+  p.stages = a.stages >= 2 && a.stages < h.stages ? a.stages : h.stages;
+  p.relu = a.relu;
+  p.relu_threshold = a.thr;
+  auto kernel = conv2d_halo_stream_kernel<true>;  // plan_stream wants two taps or more
+  static thread_local int configured_dev = -1;
+  static thread_local int configured_smem = 0;
+  if (configured_dev != dev || configured_smem < h.smem) {
+    XTC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h.smem));
+    configured_dev = dev;
+    configured_smem = h.smem;
+  }
+  const int slots = sm_count(dev) / 2;
+  const int grid = (p.tiles < slots ? p.tiles : slots) * 2;
+  XTC_CUDA_CHECK(launch_overlapped(kernel, grid, HALO_THREADS, h.smem, a.stream, tmX, tmW, p));
+  return XTC_CUDA_OK;
+}
+
 int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h, bool pair, bool taps = false) {
   if (taps)
     return h.slab == 16 ? launch_conv_halo<64, false, 16, true>(a, h)
@@ -729,7 +833,15 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     XTC_CUDA_CHECK(cudaGetLastError());
     return XTC_CUDA_OK;
   }
-  XTC_REQUIRE(c.variant >= 0 && c.variant <= 4, "conv2d: unknown variant %d", c.variant);
+  XTC_REQUIRE(c.variant >= 0 && c.variant <= 5, "conv2d: unknown variant %d", c.variant);
+  if (c.variant == 5) {
+    const StreamPlan sp = plan_stream(a);
+    if (sp.ok) return launch_conv_stream(a, sp);
+    set_error("conv2d: the streamed-weights variant (5) needs stride 1, channels and filters that are "
+              "multiples of 4, 2 to 32 filter taps and two stages of one halo slab plus the taps' weights "
+              "in shared memory");
+    return XTC_CUDA_ERR_UNSUPPORTED;
+  }
   if (c.variant == 4) {
     const SlidePlan sp = plan_slide(a);
     if (sp.ok) return sp.bn == 64 ? launch_conv_slide<64>(a, sp) : launch_conv_slide<128>(a, sp);
@@ -758,6 +870,20 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     const HaloPlan h16 = plan_halo(a, false, 16);
     const bool narrow = c.tile_k == 16 || (c.tile_k != 32 && !h1.ok);
     if (narrow && h16.ok) h1 = h16;
+    // Nothing named and no room for the whole filter bank beside one CTA's stages: stream the
+    // weights with the halo slabs (conv2d_halo_stream.cuh) where there is work for most CTA pairs
+    // and most positions of the padded grid are outputs.  Measured against the im2col kernels
+    // (us, batch 32): 28x28x128 -> 128 17.3 / 23.6, 14x14x256 -> 256 16.8 / 21.4, 56x56x64 -> 128
+    // 26.9 / 36.5 (half a bank per CTA of a pair), 28x28x128 -> 256 27.3 / 31.0; but 7x7x512 ->
+    // 512 27.7 / 26.0 (49 of 81 positions are outputs) and 8x14x14x256 -> 256 16.0 / 12.1 (16
+    // work items).
+    if (c.variant == 0 && c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m == 0 && c.tile_n == 0 &&
+        c.tile_k == 0 && c.split_k == 0 && !h1.ok) {
+      const StreamPlan sp = plan_stream(a);
+      const int64_t grid_positions = (a.H + a.pt + a.pb) * (a.W + a.pl + a.pr);
+      const int64_t items = (a.B * grid_positions + 2 * BM - 1) / (2 * BM) * ((a.F + STREAM_BN - 1) / STREAM_BN);
+      if (sp.ok && items >= 40 && a.OH * a.OW * 10 >= grid_positions * 7) return launch_conv_stream(a, sp);
+    }
     const HaloPlan h2 = plan_halo(a, true, 32);
     // the pair kernel when asked for (tile_m = 256) or when only half a filter bank fits
     const bool pair = c.tile_m == 2 * BM || (c.tile_m == 0 && !h1.ok && h2.ok);

@@ -179,6 +179,9 @@ class StrategyCudaConv:
       variant 4  resident weights with a sliding input window: a run of consecutive tiles per
                  CTA, the input through a ring of 128-position chunks (at most 128 filters, a
                  halo run of at most 256 positions); no other parameter applies
+      variant 5  streamed weights beside halo tiles, for filter banks that do not fit in shared
+                 memory: CTA pairs, 128 filters per tile, a stage = one 32-channel halo slab + every
+                 tap's weights (2 to 32 taps, two such stages must fit); only ``stages`` applies
       variant 1  implicit GEMM, one im2col fetch per filter tap: the GEMM kernels' tile_m /
                  tile_n / tile_k / stages / epilogue, and split_k = 2 to 8 pieces of the
                  reduction in one thread-block cluster (one CTA per tile, tile_n <= 128)
@@ -227,8 +230,24 @@ class StrategyCudaConv:
         bank = self._r * self._s * -(-self._c // 32) * (64 if self._f <= 64 else 128) * 128
         return run <= 256 and bank + 5 * 16384 + 2048 <= SMEM_BUDGET + 2048
 
+    def streamed_stages(self) -> int:
+        """Stages of the streamed-weights kernel that fit (0 = it does not take this layer)."""
+        taps = self._r * self._s
+        if self._stride != (1, 1) or self._c % 4 or self._f % 4 or not 2 <= taps <= 32:
+            return 0
+        run = 128 + (self._r - 1) * self._in_w + self._s - 1
+        if run > 1024:
+            return 0
+        stage = -(-run * 128 // 1024) * 1024 + taps * 64 * 128
+        fit = SMEM_BUDGET // stage
+        return min(fit, 4) if fit >= 2 else 0
+
     def is_legal(self, sample: list[int]) -> bool:
         variant, tm, tn, tk, st, tma, split = sample
+        if variant == 5:
+            fit = self.streamed_stages()
+            return (fit >= 2 and tm == 256 and tn == 128 and tk == 32 and tma == 0 and split == 1
+                    and (st == 0 or 2 <= st <= fit))
         if variant == 4:
             return (self.sliding_window_fits() and tm == 128 and tk == 32 and st == 0 and tma == 0
                     and split == 1 and tn == (64 if self._f <= 64 else 128))
@@ -252,6 +271,9 @@ class StrategyCudaConv:
                 yield s
         if self.is_legal([4, 128, min(tn_res, 128), 32, 0, 0, 1]):
             yield [4, 128, min(tn_res, 128), 32, 0, 0, 1]
+        for st in (0, 2, 3):
+            if self.is_legal([5, 256, 128, 32, st, 0, 1]):
+                yield [5, 256, 128, 32, st, 0, 1]
         for tm, tn, tk, st, tma, split in itertools.product(g.tile_m, g.tile_n, g.tile_k, g.stages,
                                                             (0, 1), StrategyCudaGemm.SPLITS):
             s = [1, tm, tn, tk, st, tma, split]
@@ -273,6 +295,8 @@ class StrategyCudaConv:
         variant, tm, tn, tk, st, tma, split = (int(v) for v in sample)
         b, h, w, f, r, s, c = list(self._op.dims)
         target = scheduler.node(self.node_name) if hasattr(scheduler, "node") else scheduler
+        if variant == 5:
+            target.pack_at(w, 0)  # the input window packed once per slab; the weights stream
         if variant in (2, 3, 4):
             target.pack_at(b, 1)  # the filter bank stays packed on chip
             if variant == 3:
