@@ -87,9 +87,9 @@ def random_config(rng: random.Random, conv: bool) -> GemmConfig:
         cfg.tile_k = rng.choice([0, 32, 64])
         cfg.stages = rng.choice([0, 0, 2, 3, 4])
         cfg.epilogue = rng.choice([0, 1, 2])
-        cfg.split_k = rng.choice([0, 0, 1, 2, 3, 4])
+        cfg.split_k = rng.choice([0, 0, 1, 2, 3, 4, 5, 6, 7, 8])
         if conv:
-            cfg.variant = rng.choice([0, 1, 2])
+            cfg.variant = rng.choice([0, 1, 2, 3, 4, 5])
     cfg.precision = rng.choice([0, 0, 0, 2] if conv else [0, 0, 0, 1, 2])
     return cfg
 
