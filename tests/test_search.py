@@ -110,6 +110,13 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
     assert strided.streamed_stages() == 0
     big = Strategies.create("cuda_conv", conv2d_graph(1, 14, 14, 256, 3, 3, 256, 1, 1))
     assert {s[0] for s in big.exhaustive()} == {1, 5}  # im2col, or streamed weights beside halo tiles
+    # one image is 2 work items: the library keeps it on the im2col kernels; 32 images are 64
+    assert not big.library_streams() and big.default_schedule(3)[0] == 1
+    batch = Strategies.create("cuda_conv", conv2d_graph(32, 14, 14, 256, 3, 3, 256, 1, 1))
+    assert batch.library_streams() and batch.default_schedule(3) == [5, 256, 128, 32, 0, 0, 1]
+    assert batch.default_schedule(2)[0] == 1
+    deep = Strategies.create("cuda_conv", conv2d_graph(32, 7, 7, 512, 3, 3, 512, 1, 1))
+    assert deep.streamed_stages() >= 2 and not deep.library_streams()  # 49 of 81 grid positions are outputs
     half = Strategies.create("cuda_conv", conv2d_graph(1, 28, 28, 128, 3, 3, 64, 1, 1))
     assert {(s[1], s[3]) for s in half.exhaustive() if s[0] == 2} >= {(256, 32)}
     # a halo run of more than 256 positions (112-wide rows) does not go through the ring

@@ -242,6 +242,17 @@ class StrategyCudaConv:
         fit = SMEM_BUDGET // stage
         return min(fit, 4) if fit >= 2 else 0
 
+    def library_streams(self) -> bool:
+        """Whether the library, with nothing named, runs this layer on the streamed-weights kernel
+        (the rule of ``xtc_cuda_conv2d_nhwc_f32``: no room for the whole filter bank beside one
+        CTA's stages, work for most CTA pairs or at most two channel slabs, and most positions of
+        the padded grid are outputs)."""
+        if self.streamed_stages() < 2 or self.resident_stages(128, 32) or self.resident_stages(128, 16):
+            return False
+        grid = ((self._h - 1) * self._stride[0] + self._r) * self._in_w
+        items = -(-self._b * grid // 256) * -(-self._f // 128)
+        return (items >= 40 or -(-self._c // 32) <= 2) and self._h * self._w * 10 >= grid * 7
+
     def is_legal(self, sample: list[int]) -> bool:
         variant, tm, tn, tk, st, tma, split = sample
         if variant == 5:
@@ -289,6 +300,8 @@ class StrategyCudaConv:
         resident = [2, 128, 64 if self._f <= 64 else 128 if self._f <= 128 else 256, 32, 0, 0, 1]
         if opt_level >= 2 and self.is_legal(resident):
             return resident
+        if opt_level >= 3 and self.library_streams():
+            return [5, 256, 128, 32, 0, 0, 1]  # what the library picks itself for such a layer
         return [1, 128, 64 if self._f <= 64 else 128, 32, 2 if opt_level <= 0 else 0, 1, 1]
 
     def generate(self, scheduler: Any, sample: list[int]) -> None:
