@@ -3,12 +3,13 @@
 // Such a product reads B once and does two flops per element read: HBM bounds it, a tensor
 // core tile of 128 rows would be 1/16 used at best, and the tile kernels' K loop per SM cannot
 // pull B fast enough (1 x 4096 x 4096: 23 us on the tile kernels, 67 MB = 10 us of HBM time).
-// Here every CTA streams a [K / 8, 64] block of B with plain 128-bit loads, four in flight per
-// thread, and multiplies in fp32 on the CUDA cores (more exact than TF32, so every tolerance of
-// the tensor-core path holds).  The eight K pieces of a column strip are the CTAs of one
-// thread-block cluster: each reduces its 16 row lanes in shared memory, then the CTA of rank 0
-// adds the eight partial rows in rank order through distributed shared memory and stores C.  No
-// workspace, no atomics, the same bits on every run.
+// Here every CTA streams a [K / 8, 64] block of B (128 columns wide when N >= 8192: fewer,
+// longer runs per row of B) with plain 128-bit loads, four in flight per thread, and multiplies
+// in fp32 on the CUDA cores (more exact than TF32, so every tolerance of the tensor-core path
+// holds).  The eight K pieces of a column strip are the CTAs of one thread-block cluster: each
+// reduces its 16 (or 8) row lanes in shared memory, then the CTA of rank 0 adds the eight
+// partial rows in rank order through distributed shared memory and stores C.  No workspace, no
+// atomics, the same bits on every run.
 //
 // Needs B row-major ([K, N], not the transposed form), N a multiple of 4, B and C 16-byte
 // aligned with pitches that are multiples of 4; A may have either layout.
@@ -18,8 +19,8 @@
 namespace xtc {
 
 constexpr int THIN_THREADS = 256;
-constexpr int THIN_COLS = 64;      // columns per CTA: 16 lanes of float4
-constexpr int THIN_ROW_LANES = 16;  // rows of B in flight per load round
+constexpr int THIN_COLS = 64;       // columns per CTA: 16 lanes of float4 and 16 row lanes, or
+constexpr int THIN_COLS_WIDE = 128;  // 32 lanes of float4 and 8 row lanes (N >= 8192: longer runs per row)
 constexpr int THIN_KSPLIT = 8;      // CTAs per cluster, one K piece each
 
 struct ThinRowsParams {
@@ -33,12 +34,13 @@ struct ThinRowsParams {
   float thr;
 };
 
-template <int MT>
+template <int MT, int COLS>
 __global__ void __launch_bounds__(THIN_THREADS)
 gemm_thin_rows_kernel(const ThinRowsParams p) {
+  constexpr int ROW_LANES = THIN_THREADS * 4 / COLS;  // rows of B in flight per load round
   using namespace dev;
   extern __shared__ float thin_smem[];
-  // [k in piece][MT] values of A, then [row lane][MT][THIN_COLS] partial sums, of which row
+  // [k in piece][MT] values of A, then [row lane][MT][COLS] partial sums, of which row
   // lane 0's block ends up holding the CTA's partial rows
   const uint32_t piece = cluster_ctarank();
   const int strip = blockIdx.x / THIN_KSPLIT;
@@ -58,9 +60,11 @@ gemm_thin_rows_kernel(const ThinRowsParams p) {
   }
   __syncthreads();
 
-  const int cl = threadIdx.x & 15;   // column group
-  const int rl = threadIdx.x >> 4;   // row lane
-  const int col = strip * THIN_COLS + cl * 4;
+  constexpr int COL_GROUPS = COLS / 4;
+  static_assert(COL_GROUPS * ROW_LANES == THIN_THREADS, "one float4 column group and row lane per thread");
+  const int cl = threadIdx.x % COL_GROUPS;   // column group
+  const int rl = threadIdx.x / COL_GROUPS;   // row lane
+  const int col = strip * COLS + cl * 4;
   const bool col_ok = col < p.N;     // N is a multiple of 4: a group is inside or outside
   float acc[MT][4];
 #pragma unroll
@@ -68,14 +72,17 @@ gemm_thin_rows_kernel(const ThinRowsParams p) {
   if (col_ok) {
     const float* bp = p.B + static_cast<long long>(k0) * p.ldb + col;
     int k = rl;
-    for (; k + 3 * THIN_ROW_LANES < kn; k += 4 * THIN_ROW_LANES) {
-      float4 b[4];
+    // loads in flight per thread: with 4 or 8 rows of A a CTA holds 32 - 64 KB of shared memory,
+    // fewer CTAs fit an SM, and each thread has to keep more of HBM's latency covered itself
+    constexpr int DEPTH = MT >= 4 ? 8 : 4;
+    for (; k + (DEPTH - 1) * ROW_LANES < kn; k += DEPTH * ROW_LANES) {
+      float4 b[DEPTH];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        b[u] = __ldcs(reinterpret_cast<const float4*>(bp + static_cast<long long>(k + u * THIN_ROW_LANES) * p.ldb));
+      for (int u = 0; u < DEPTH; ++u)
+        b[u] = __ldcs(reinterpret_cast<const float4*>(bp + static_cast<long long>(k + u * ROW_LANES) * p.ldb));
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float* ar = a_s + (k + u * THIN_ROW_LANES) * MT;
+      for (int u = 0; u < DEPTH; ++u) {
+        const float* ar = a_s + (k + u * ROW_LANES) * MT;
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           const float a = ar[m];
@@ -86,7 +93,7 @@ gemm_thin_rows_kernel(const ThinRowsParams p) {
         }
       }
     }
-    for (; k < kn; k += THIN_ROW_LANES) {
+    for (; k < kn; k += ROW_LANES) {
       const float4 b = __ldcs(reinterpret_cast<const float4*>(bp + static_cast<long long>(k) * p.ldb));
       const float* ar = a_s + k * MT;
 #pragma unroll
@@ -102,18 +109,18 @@ gemm_thin_rows_kernel(const ThinRowsParams p) {
   // the 16 row lanes of this CTA, summed in lane order by the threads of row lane 0
 #pragma unroll
   for (int m = 0; m < MT; ++m)
-    *reinterpret_cast<float4*>(red + (static_cast<size_t>(rl) * MT + m) * THIN_COLS + cl * 4) =
+    *reinterpret_cast<float4*>(red + (static_cast<size_t>(rl) * MT + m) * COLS + cl * 4) =
         make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
   __syncthreads();
   if (rl == 0) {
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-      float4 s = *reinterpret_cast<const float4*>(red + static_cast<size_t>(m) * THIN_COLS + cl * 4);
-      for (int r = 1; r < THIN_ROW_LANES; ++r) {
-        const float4 v = *reinterpret_cast<const float4*>(red + (static_cast<size_t>(r) * MT + m) * THIN_COLS + cl * 4);
+      float4 s = *reinterpret_cast<const float4*>(red + static_cast<size_t>(m) * COLS + cl * 4);
+      for (int r = 1; r < ROW_LANES; ++r) {
+        const float4 v = *reinterpret_cast<const float4*>(red + (static_cast<size_t>(r) * MT + m) * COLS + cl * 4);
         s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
       }
-      *reinterpret_cast<float4*>(red + static_cast<size_t>(m) * THIN_COLS + cl * 4) = s;
+      *reinterpret_cast<float4*>(red + static_cast<size_t>(m) * COLS + cl * 4) = s;
     }
   }
   cluster_sync_all();  // every piece's partial rows are in place
@@ -122,9 +129,9 @@ gemm_thin_rows_kernel(const ThinRowsParams p) {
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
       if (m >= p.M) break;
-      float4 s = *reinterpret_cast<const float4*>(red + static_cast<size_t>(m) * THIN_COLS + cl * 4);
+      float4 s = *reinterpret_cast<const float4*>(red + static_cast<size_t>(m) * COLS + cl * 4);
       for (uint32_t r = 1; r < THIN_KSPLIT; ++r) {
-        const float4 v = ld_shared_cluster_f4(map_to_cta(mine + static_cast<uint32_t>(m) * THIN_COLS * 4, r));
+        const float4 v = ld_shared_cluster_f4(map_to_cta(mine + static_cast<uint32_t>(m) * COLS * 4, r));
         s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
       }
       if (p.relu) {
@@ -141,7 +148,7 @@ gemm_thin_rows_kernel(const ThinRowsParams p) {
 inline size_t thin_rows_smem(int mt, long long K) {
   const size_t per_piece = static_cast<size_t>((K + THIN_KSPLIT - 1) / THIN_KSPLIT);
   return (((per_piece * mt + 3) & ~static_cast<size_t>(3)) +
-          static_cast<size_t>(THIN_ROW_LANES) * mt * THIN_COLS) * sizeof(float);
+          static_cast<size_t>(THIN_THREADS) * 4 * mt) * sizeof(float);  // row lanes x columns = 4 x threads
 }
 
 }  // namespace xtc
