@@ -495,6 +495,19 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, bool a_mn, 
 
 }  // namespace dev
 
+// Bounded wait (about 2 s) for a flag in global memory that another CTA sets.
+__device__ __forceinline__ bool wait_flag_set(int* flag) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (atomicAdd(flag, 0) != 0) return true;
+    if ((it & 0xff) == 0xff) {
+      const uint64_t now = dev::globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) return false;
+    }
+  }
+}
+
 // Launch with programmatic stream serialisation: the kernel may begin before its
 // predecessor in the stream has drained (see dev::grid_dependency_sync).
 template <typename... KArgs, typename... Args>

@@ -81,6 +81,9 @@ struct ConvHaloParams {
   int ntiles_n;           // filter tiles of 128
   int wts_offset;         // where a stage's weights start (the halo slab rounded up to 1024 bytes)
   int wts_tx;             // bytes of weights one CTA fetches per stage: taps * 64 * 128
+  // the same kernel with the (work item, channel slab) units dealt out evenly to the CTA pairs
+  float* sk_partials;     // NULL = whole work items, round-robin; else [pair][CTA][warp][32 rows x 128 columns]
+  int* sk_flags;          // [pair][CTA][warp]: 1 = that warp's partial is in place (its reader clears it)
 };
 
 constexpr int HALO_THREADS = 224;  // producer, two MMA issuers, four epilogue warps

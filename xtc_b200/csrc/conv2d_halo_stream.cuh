@@ -18,6 +18,17 @@
 // conv2d_halo.cuh, and the two groups of a tap lie taps * 4096 bytes apart (the descriptor's
 // leading-dimension offset).
 //
+// Balance.  With whole work items dealt round-robin, 113 items on 74 CTA pairs are two rounds of
+// which the second is half empty.  Given a workspace, the kernel deals out (work item, channel
+// slab) units instead: pair p takes the contiguous range [p*U/P, (p+1)*U/P) of the U = items x
+// slabs units, so a pair's first and last item may be partial.  The pair that holds an item's
+// slab 0 stores it; every other pair holding some of its slabs does so at the START of its range,
+// writes its raw accumulator to the workspace (per warp: [pair][CTA][warp] blocks of 32 rows,
+// lane-interleaved so that every store is 512 contiguous bytes) and raises that warp's flag; the storing pair reaches that item at the END of its range, waits (bounded, normally not at
+// all) for the flags of the pairs after it, adds their partials in pair order and clears the flags.
+// Same bits on every run; the bits differ from the round-robin form only in where the sum over
+// slabs is cut.  All pairs are resident at once (one CTA per SM, at most SMs / 2 pairs).
+//
 // Barriers (no multicast anywhere):
 //   full[s]      leader only; both CTAs' copies of a stage report to it.
 //   empty[s]     one per CTA; the leader commits to both.
@@ -29,6 +40,43 @@
 namespace xtc {
 
 constexpr int STREAM_BN = 128;
+
+// The segments (work item, slabs [s0, s1)) of one CTA pair, in the order every role of the
+// kernel walks them.
+struct StreamSegments {
+  bool balanced;
+  int item, step, items, nslab;  // round-robin: whole items pair, pair + step, ...
+  long long unit, unit_hi;       // balanced: the pair's range of (item, slab) units
+  __device__ StreamSegments(const ConvHaloParams& p, int pair, int num_pairs)
+      : balanced(p.sk_partials != nullptr), item(pair), step(num_pairs), items(p.tiles), nslab(p.nslab) {
+    const long long units = static_cast<long long>(p.tiles) * p.nslab;
+    const long long q = units / num_pairs, r = units % num_pairs;
+    unit = pair * q + (pair < r ? pair : r);
+    unit_hi = unit + q + (pair < r ? 1 : 0);
+  }
+  __device__ bool next(int& it, int& s0, int& s1) {
+    if (!balanced) {
+      if (item >= items) return false;
+      it = item;
+      s0 = 0;
+      s1 = nslab;
+      item += step;
+      return true;
+    }
+    if (unit >= unit_hi) return false;
+    it = static_cast<int>(unit / nslab);
+    s0 = static_cast<int>(unit - static_cast<long long>(it) * nslab);
+    const long long item_end = static_cast<long long>(it + 1) * nslab;
+    const long long end = item_end < unit_hi ? item_end : unit_hi;
+    s1 = s0 + static_cast<int>(end - unit);
+    unit = end;
+    return true;
+  }
+};
+// Units of pair `pair` when `units` are dealt out evenly to `num_pairs` pairs.
+__device__ __forceinline__ long long stream_units_of(long long units, int num_pairs, int pair) {
+  return units / num_pairs + (pair < units % num_pairs ? 1 : 0);
+}
 
 template <bool DUAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HALO_THREADS, 1)
@@ -91,7 +139,9 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * 4096u;
-      for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs) {
+      StreamSegments segs(p, pair, num_pairs);
+      int tile, s0, s1;
+      while (!failed && segs.next(tile, s0, s1)) {
         const int ptile = tile / p.ntiles_n;
         const int ntile = tile - ptile * p.ntiles_n;
         long long q0 = static_cast<long long>(ptile) * (2 * BM) + static_cast<long long>(rank) * BM;
@@ -101,7 +151,7 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
         const int ih = rem / p.Wp - p.pad_top;
         const int iw = rem % p.Wp - p.pad_left;
         const int f0 = ntile * BN + static_cast<int>(rank) * HALF;
-        for (int slab = 0; slab < p.nslab; ++slab) {
+        for (int slab = s0; slab < s1; ++slab) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_EMPTY);
             failed = true;
@@ -130,7 +180,7 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
       constexpr uint32_t idesc = umma_idesc_tf32(2 * BM, BN, false, true);
       const int t0 = DUAL ? (w == 0 ? 0 : (p.taps + 1) / 2) : 0;
       const int t1 = DUAL ? (w == 0 ? (p.taps + 1) / 2 : p.taps) : p.taps;
-      const int r0 = t0 / p.S, s0 = t0 - r0 * p.S;
+      const int r0 = t0 / p.S, tap_s0 = t0 - r0 * p.S;
       const uint32_t a_hi = umma_desc_hi(1024, static_cast<uint32_t>(UMMA_SWIZZLE_128B));
       const uint32_t b_hi = umma_desc_hi(512, static_cast<uint32_t>(UMMA_SWIZZLE_128B_BASE32B));
       const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * 4096u;
@@ -138,8 +188,9 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
       const uint32_t a_first = static_cast<uint32_t>(r0) * row_step;
       int stage = 0;
       uint32_t phase = 0;
-      int local = 0;
-      for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs, ++local) {
+      StreamSegments segs(p, pair, num_pairs);
+      int tile, s0, s1;
+      for (int local = 0; !failed && segs.next(tile, s0, s1); ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
@@ -149,7 +200,7 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (acc * NACC + w) * BN;
-        for (int slab = 0; slab < p.nslab; ++slab) {
+        for (int slab = s0; slab < s1; ++slab) {
           if (!mbar_wait(&full[stage], phase)) {
             atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_LOAD);
             failed = true;
@@ -160,8 +211,8 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
           uint32_t a_row = umma_desc_lo(sA, 16) + a_first;
           uint32_t b_lo = umma_desc_lo(sA + static_cast<uint32_t>(p.wts_offset) +
                                            static_cast<uint32_t>(t0) * 4096u, group_bytes);
-          uint32_t first = slab == 0 ? 0u : 1u;
-          for (int tap = t0, s = s0; tap < t1; ++tap) {
+          uint32_t first = slab == s0 ? 0u : 1u;  // a segment's first MMA overwrites its accumulator
+          for (int tap = t0, s = tap_s0; tap < t1; ++tap) {
             const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * 8u;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
@@ -196,8 +247,14 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const bool vec_ok = (p.F % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0);
     const bool wide_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.Y) & 31) == 0);
-    int local = 0;
-    for (int tile = pair; tile < p.tiles && !failed; tile += num_pairs, ++local) {
+    // balanced form: the rows of this warp travel on their own (partials and flags per
+    // (pair, CTA, warp)), so no warp waits for another one of its CTA
+    const int my_slab = static_cast<int>(rank) * EPI_WARPS + quad;
+    const long long units = static_cast<long long>(p.tiles) * p.nslab;
+    constexpr int SLAB_FLOATS = 32 * BN;  // 32 rows x BN columns of one warp
+    StreamSegments segs(p, pair, num_pairs);
+    int tile, s0, s1;
+    for (int local = 0; !failed && segs.next(tile, s0, s1); ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase)) {
@@ -206,6 +263,24 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
         break;
       }
       tc_fence_after();
+      const bool stores = s0 == 0;  // this pair holds the item's first slab: it writes the output
+      // the pairs after this one that hold the rest of the item's slabs
+      int helpers = 0;
+      if (stores && s1 < p.nslab) {
+        long long rest = p.nslab - s1;
+        for (int h = pair + 1; rest > 0 && h < num_pairs; ++h, ++helpers)
+          rest -= stream_units_of(units, num_pairs, h);
+        int ok = 1;
+        if (lane == 0)
+          for (int h = 1; h <= helpers && ok; ++h)
+            ok = wait_flag_set(p.sk_flags + (pair + h) * (2 * EPI_WARPS) + my_slab) ? 1 : 0;
+        if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
+          if (lane == 0) atomicCAS(p.status, 0, STATUS_WAIT_TIMEOUT_ACC);
+          failed = true;
+          break;
+        }
+        __threadfence();
+      }
       const int ptile = tile / p.ntiles_n;
       const int n0 = (tile - ptile * p.ntiles_n) * BN;
       const long long q = static_cast<long long>(ptile) * (2 * BM) + static_cast<long long>(rank) * BM +
@@ -230,6 +305,30 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
         } else {
           tmem_ld_wait();
         }
+        if (!stores) {
+          // a later part of an item: the raw sums go to the pair that stores it
+          // (lane-interleaved: each store instruction writes 512 contiguous bytes)
+          float4* parked = reinterpret_cast<float4*>(
+              p.sk_partials + (static_cast<size_t>(pair) * (2 * EPI_WARPS) + my_slab) * SLAB_FLOATS);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            parked[(c * 8 + j) * 32 + lane] =
+                make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          continue;
+        }
+        for (int h = 1; h <= helpers; ++h) {  // pair order: the same bits on every run
+          const float4* parked = reinterpret_cast<const float4*>(
+              p.sk_partials + (static_cast<size_t>(pair + h) * (2 * EPI_WARPS) + my_slab) * SLAB_FLOATS);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = __ldcg(&parked[(c * 8 + j) * 32 + lane]);
+            r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+            r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+            r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+            r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+          }
+        }
         if (p.relu) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -252,6 +351,15 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
               if (n0 + col0 + i < p.F) dst[col0 + i] = __uint_as_float(r[i]);
           }
         }
+      }
+      if (!stores) {  // publish the partial
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicExch(p.sk_flags + pair * (2 * EPI_WARPS) + my_slab, 1);
+      } else if (helpers > 0) {
+        __syncwarp();  // every lane has read the partials
+        if (lane == 0)  // leave the flags as the next launch expects them
+          for (int h = 1; h <= helpers; ++h) p.sk_flags[(pair + h) * (2 * EPI_WARPS) + my_slab] = 0;
       }
       tc_fence_before();
       __syncwarp();

@@ -469,7 +469,44 @@ StreamPlan plan_stream(const ConvArgs& a) {
   return s;
 }
 
-int launch_conv_stream(const ConvArgs& a, const StreamPlan& h) {
+// Workspace of the balanced form of the streamed-weights kernel (see conv2d_halo_stream.cuh):
+// one flag and one 32 x 128 block of partial sums per (CTA pair, CTA, epilogue warp).
+static size_t stream_flag_bytes(int pairs) { return (static_cast<size_t>(pairs) * 8 * 4 + 255) & ~static_cast<size_t>(255); }
+static size_t stream_balance_bytes(int pairs) {
+  return stream_flag_bytes(pairs) + static_cast<size_t>(pairs) * 8 * 32 * STREAM_BN * 4;
+}
+// Whether dealing out (work item, slab) units evenly beats whole items round-robin.  A pair
+// then has up to two partial items, each with an epilogue of its own and a pass over the
+// partial sums, about two slabs' worth of time, so the longest pair's units must shrink by more
+// than that (us, balanced / round-robin: 16x28x28x256 -> 512, 25 units against 32, 44.8 / 47.8;
+// but 32x28x28x128 -> 128, 7 against 8, 19.9 / 17.3 and 32x14x14x256 -> 256, 7 against 8,
+// 20.9 / 16.8).  And every pair must hold two items' worth of units, so that an item is cut
+// once at most: cut into many pieces, the pair that stores an item waits for all the others
+// and sums their partials alone (8x14x14x256 -> 256, 2 units against 8: 20.4 / 16.0).
+static bool stream_balance_pays(int64_t items, int nslab, int pairs) {
+  const int64_t units = items * nslab;
+  if (units < 2ll * nslab * pairs) return false;
+  const int64_t plain = (items + pairs - 1) / pairs * nslab;
+  const int64_t even = (units + pairs - 1) / pairs;
+  return (even + 2) * 100 <= plain * 85;
+}
+
+// Nothing named and no room for the whole filter bank beside one CTA's stages: stream the
+// weights with the halo slabs (conv2d_halo_stream.cuh) where there is work for most CTA pairs
+// (or at most two channel slabs to walk) and most positions of the padded grid are outputs.
+// Measured against the im2col kernels (us, batch 32): 28x28x128 -> 128 17.3 / 23.6, 14x14x256 ->
+// 256 16.8 / 21.4, 56x56x64 -> 128 26.9 / 36.5 (half a bank per CTA of a pair), 28x28x128 -> 256
+// 27.3 / 31.0; 27x27x48 -> 192 (8 work items, two slabs) 8.2 / 10.3; but 7x7x512 -> 512 27.7 /
+// 26.0 (49 of 81 positions are outputs) and 8x14x14x256 -> 256 16.0 / 12.1 (16 work items).
+static bool stream_is_default(const ConvArgs& a, const StreamPlan& sp) {
+  if (!sp.ok) return false;
+  const int64_t grid_positions = (a.H + a.pt + a.pb) * (a.W + a.pl + a.pr);
+  const int64_t items = (a.B * grid_positions + 2 * BM - 1) / (2 * BM) * ((a.F + STREAM_BN - 1) / STREAM_BN);
+  return (items >= 40 || sp.nslab <= 2) && a.OH * a.OW * 10 >= grid_positions * 7;
+}
+
+int launch_conv_stream(const ConvArgs& a, const StreamPlan& h, void* workspace = nullptr,
+                       size_t workspace_bytes = 0) {
   encode_im2col_fn enc = get_encode_im2col();
   encode_tiled_fn enc_tiled = get_encode_tiled();
   XTC_REQUIRE(enc != nullptr && enc_tiled != nullptr,
@@ -539,7 +576,15 @@ int launch_conv_stream(const ConvArgs& a, const StreamPlan& h) {
     configured_smem = h.smem;
   }
   const int slots = sm_count(dev) / 2;
-  const int grid = (p.tiles < slots ? p.tiles : slots) * 2;
+  int grid = (p.tiles < slots ? p.tiles : slots) * 2;
+  if (workspace != nullptr && workspace_bytes >= stream_balance_bytes(slots) &&
+      (reinterpret_cast<uintptr_t>(workspace) & 15) == 0 && stream_balance_pays(p.tiles, p.nslab, slots)) {
+    // every pair of the device, each with an even share of the (item, slab) units; the flags
+    // at the start of the workspace are zero (first use) or were left zero by the last launch
+    p.sk_flags = static_cast<int*>(workspace);
+    p.sk_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + stream_flag_bytes(slots));
+    grid = slots * 2;
+  }
   XTC_CUDA_CHECK(launch_overlapped(kernel, grid, HALO_THREADS, h.smem, a.stream, tmX, tmW, p));
   return XTC_CUDA_OK;
 }
@@ -730,18 +775,35 @@ extern "C" int xtc_cuda_conv2d_workspace_bytes(int64_t B, int64_t H, int64_t W, 
     *bytes = t.p_bytes + t.v_bytes + inner;
     return XTC_CUDA_OK;
   }
-  if (!conv_names_nothing(c)) return XTC_CUDA_OK;
   ConvArgs a;
   memset(&a, 0, sizeof(a));
   a.B = B; a.H = H; a.W = W; a.C = C; a.R = R; a.S = S; a.F = F;
   a.sh = stride_h; a.sw = stride_w;
   a.pt = pad_top; a.pb = pad_bottom; a.pl = pad_left; a.pr = pad_right;
   a.OH = OH; a.OW = OW;
-  if (plan_halo(a, false, 32).ok || plan_halo(a, false, 16).ok || plan_halo(a, true, 32).ok ||
-      plan_halo(a, false, 32, true).ok || plan_halo(a, false, 16, true).ok)
-    return XTC_CUDA_OK;  // resident weights: no workspace
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) sms = sm_count(dev); else cudaGetLastError();
+  // streamed weights (asked for, or the library's own choice): flags and partial sums of the
+  // balanced form, where dealing out (item, slab) units evenly shortens the longest pair
+  auto stream_bytes = [&](const StreamPlan& sp) -> size_t {
+    const int64_t items = (B * (H + pad_top + pad_bottom) * (W + pad_left + pad_right) + 2 * BM - 1) /
+                          (2 * BM) * ((F + STREAM_BN - 1) / STREAM_BN);
+    return stream_balance_pays(items, sp.nslab, sms / 2) ? stream_balance_bytes(sms / 2) : 0;
+  };
+  if (c.variant == 5) {
+    const StreamPlan sp = plan_stream(a);
+    if (sp.ok) *bytes = stream_bytes(sp);
+    return XTC_CUDA_OK;
+  }
+  if (!conv_names_nothing(c)) return XTC_CUDA_OK;
+  if (plan_halo(a, false, 32).ok || plan_halo(a, false, 16).ok)
+    return XTC_CUDA_OK;  // resident weights in one CTA: no workspace
+  if (const StreamPlan sp = plan_stream(a); stream_is_default(a, sp)) {
+    *bytes = stream_bytes(sp);
+    return XTC_CUDA_OK;
+  }
+  if (plan_halo(a, true, 32).ok || plan_halo(a, false, 32, true).ok || plan_halo(a, false, 16, true).ok)
+    return XTC_CUDA_OK;  // resident weights: no workspace
   int caps[9] = {};
   for (int sz = 2; sz <= 8; ++sz) caps[sz] = cluster_capacity(dev, sz);
   const AutoChoice pick =
@@ -836,7 +898,7 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
   XTC_REQUIRE(c.variant >= 0 && c.variant <= 5, "conv2d: unknown variant %d", c.variant);
   if (c.variant == 5) {
     const StreamPlan sp = plan_stream(a);
-    if (sp.ok) return launch_conv_stream(a, sp);
+    if (sp.ok) return launch_conv_stream(a, sp, workspace, workspace_bytes);
     set_error("conv2d: the streamed-weights variant (5) needs stride 1, channels and filters that are "
               "multiples of 4, 2 to 32 filter taps and two stages of one halo slab plus the taps' weights "
               "in shared memory");
@@ -870,22 +932,12 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
     const HaloPlan h16 = plan_halo(a, false, 16);
     const bool narrow = c.tile_k == 16 || (c.tile_k != 32 && !h1.ok);
     if (narrow && h16.ok) h1 = h16;
-    // Nothing named and no room for the whole filter bank beside one CTA's stages: stream the
-    // weights with the halo slabs (conv2d_halo_stream.cuh) where there is work for most CTA pairs
-    // and most positions of the padded grid are outputs.  Measured against the im2col kernels
-    // (us, batch 32): 28x28x128 -> 128 17.3 / 23.6, 14x14x256 -> 256 16.8 / 21.4, 56x56x64 -> 128
-    // 26.9 / 36.5 (half a bank per CTA of a pair), 28x28x128 -> 256 27.3 / 31.0; but 7x7x512 ->
-    // 512 27.7 / 26.0 (49 of 81 positions are outputs) and 8x14x14x256 -> 256 16.0 / 12.1 (16
-    // work items).
+    // nothing named and no room for the whole filter bank beside one CTA's stages: streamed
+    // weights where that pays (stream_is_default), balanced over the pairs given the workspace
     if (c.variant == 0 && c.precision == XTC_CUDA_PRECISION_TF32 && c.tile_m == 0 && c.tile_n == 0 &&
         c.tile_k == 0 && c.split_k == 0 && !h1.ok) {
       const StreamPlan sp = plan_stream(a);
-      const int64_t grid_positions = (a.H + a.pt + a.pb) * (a.W + a.pl + a.pr);
-      const int64_t items = (a.B * grid_positions + 2 * BM - 1) / (2 * BM) * ((a.F + STREAM_BN - 1) / STREAM_BN);
-      // (few work items still pay when there are at most two channel slabs to walk:
-      // 27x27x48 -> 192, 8 items, 8.2 us against 10.3 us)
-      if (sp.ok && (items >= 40 || sp.nslab <= 2) && a.OH * a.OW * 10 >= grid_positions * 7)
-        return launch_conv_stream(a, sp);
+      if (stream_is_default(a, sp)) return launch_conv_stream(a, sp, workspace, workspace_bytes);
     }
     const HaloPlan h2 = plan_halo(a, true, 32);
     // the pair kernel when asked for (tile_m = 256) or when only half a filter bank fits

@@ -69,19 +69,6 @@ struct PairWorkIter {
   }
 };
 
-// Bounded wait (about 2 s) for a flag in global memory that another CTA sets.
-__device__ __forceinline__ bool wait_flag_set(int* flag) {
-  uint64_t t0 = 0;
-  for (uint32_t it = 0;; ++it) {
-    if (atomicAdd(flag, 0) != 0) return true;
-    if ((it & 0xff) == 0xff) {
-      const uint64_t now = dev::globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > 2000000000ull) return false;
-    }
-  }
-}
-
 template <int BN, int KSPANS>
 struct PairSmem {
   static constexpr int BK = 32 * KSPANS;
