@@ -127,6 +127,10 @@ typedef struct xtc_cuda_gemm_config {
                         32 taps, two such stages in shared memory; `stages` applies).
                         With nothing named the library takes it where the whole bank
                         does not fit one CTA and the layer has work for most pairs.
+                        With the workspace xtc_cuda_conv2d_workspace_bytes asks for
+                        (zeroed before its first use; the kernel leaves its flags zero)
+                        large layers are dealt out to the CTA pairs in (work item,
+                        channel slab) units instead of whole work items.
                         GEMM with tile_m = 256: 2 = store C without the L2
                         evict-first hint (the default hints it)                   */
   int32_t split_k;   /* GEMM: CTAs sharing one output tile along K; 0 or 1 = off unless
