@@ -306,6 +306,28 @@ def test_plan_run_sets_checks_its_arguments(cuda_lib):
     assert cuda_lib.xtc_cuda_plan_run_sets(fake, None, 1, 0, 1, None) == capi.ERR_INVALID
 
 
+def test_conv_workspace_of_the_balanced_streamed_kernel(cuda_lib):
+    """xtc_cuda_conv2d_workspace_bytes, callable without a device: a stride-1 layer whose filter
+    bank does not fit in shared memory gets the flags and partial sums of the streamed-weights
+    kernel's balanced form where dealing out (work item, slab) units evenly pays (16x28x28x256 ->
+    512: 25 units for the busiest CTA pair instead of 32), asked for by name or not, and nothing
+    where it does not (one unit in eight saved, or items cut into many pieces)."""
+    def ask(B, H, W, C, F, variant):
+        c = capi.GemmConfig(variant=variant)
+        ws = ctypes.c_size_t(7)
+        capi.check(cuda_lib.xtc_cuda_conv2d_workspace_bytes(B, H, W, C, 3, 3, F, 1, 1, 1, 1, 1, 1,
+                                                            ctypes.byref(c), ctypes.byref(ws)))
+        return ws.value
+
+    pairs = 74  # of a 148-SM device, which is also what the library assumes without one
+    flags = (pairs * 8 * 4 + 255) // 256 * 256
+    want = flags + pairs * 8 * 32 * 128 * 4  # one flag and one 32 x 128 block per (pair, CTA, warp)
+    assert ask(16, 28, 28, 256, 512, 5) == ask(16, 28, 28, 256, 512, 0) == want
+    assert ask(32, 28, 28, 128, 128, 5) == ask(32, 28, 28, 128, 128, 0) == 0  # 7 units against 8
+    assert ask(8, 14, 14, 256, 256, 5) == 0  # 128 units on 74 pairs: every item would be cut in pieces
+    assert ask(32, 56, 56, 64, 64, 0) == 0   # the filter bank fits: resident weights
+
+
 def test_default_gemm_config_is_a_legal_config(cuda_lib):
     """xtc_cuda_gemm_default_config: host arithmetic, callable without a device; what it returns
     is a configuration the GEMM entry point accepts (legal tile, K stage and split)."""
