@@ -124,7 +124,8 @@ typedef struct xtc_cuda_gemm_config {
                         do not fit in shared memory: CTA pairs, 128 filters per work
                         item, a pipeline stage = one 32-channel halo slab + the
                         weights of every tap (stride 1, C and F multiples of 4, 2 to
-                        32 taps, two such stages in shared memory; `stages` applies).
+                        32 taps, two such stages in shared memory; `stages` applies,
+                        tile_k = 16 halves the slabs).
                         With nothing named the library takes it where the whole bank
                         does not fit one CTA and the layer has work for most pairs.
                         With the workspace xtc_cuda_conv2d_workspace_bytes asks for

@@ -82,8 +82,11 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
     assert len(space) == len({tuple(s) for s in space}) > 100
     assert {s[0] for s in space} == {1, 2, 3, 4, 5}
     assert [s for s in space if s[0] == 4] == [[4, 128, 64, 32, 0, 0, 1]]  # the sliding input window
-    # streamed weights: two stages of a halo slab + nine taps' weights fit, not three
-    assert [s for s in space if s[0] == 5] == [[5, 256, 128, 32, 0, 0, 1], [5, 256, 128, 32, 2, 0, 1]]
+    # streamed weights: two stages of a 32-channel halo slab + nine taps' weights fit, not three;
+    # four of 16-channel slabs
+    assert [s for s in space if s[0] == 5] == [[5, 256, 128, 32, 0, 0, 1], [5, 256, 128, 32, 2, 0, 1],
+                                               [5, 256, 128, 16, 0, 0, 1], [5, 256, 128, 16, 2, 0, 1],
+                                               [5, 256, 128, 16, 3, 0, 1], [5, 256, 128, 16, 4, 0, 1]]
     resident = [s for s in space if s[0] == 2]
     assert {(s[1], s[3]) for s in resident} == {(128, 16), (128, 32), (256, 32)}
     assert {(s[1], s[3]) for s in space if s[0] == 3} == {(128, 16), (128, 32)}  # two taps per MMA
@@ -94,8 +97,13 @@ def test_conv_strategy_covers_kernel_variant_slab_and_split():
         strat.generate(sch, s)
         cfg = sch.schedule().node_configs()["conv"]
         assert cfg.get("variant", 0) == (s[0] if s[0] in (2, 3, 4, 5) else 0)
-        if s[0] == 5:  # the kernel has one tile shape: only the pipeline depth is a parameter
-            assert cfg == ({"variant": 5, "stages": s[4]} if s[4] else {"variant": 5})
+        if s[0] == 5:  # the kernel has one tile shape: the slab width and the depth are its parameters
+            want = {"variant": 5}
+            if s[4]:
+                want["stages"] = s[4]
+            if s[3] == 16:
+                want["tile_k"] = 16
+            assert cfg == want
             continue
         assert (cfg["tile_m"], cfg["tile_k"], cfg.get("stages", 0)) == (s[1], s[3], s[4])
         assert cfg.get("split_k", 1) == s[6] and cfg.get("epilogue", 0) == (2 if s[5] else 0)

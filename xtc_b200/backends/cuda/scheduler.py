@@ -223,6 +223,9 @@ class CudaNodeScheduler:
         # for the whole kernel -> the resident-weights / halo-tile convolution, whose
         # pipeline stage is a slab of 16 or 32 channels
         resident = self.op_name == "conv2d" and any(1 in idx for idx in self.packed_buffers.values())
+        # pack_at(_, 0) alone: the streamed-weights kernel, whose stage is a channel slab too
+        streamed = (self.op_name == "conv2d" and not resident
+                    and any(0 in idx for idx in self.packed_buffers.values()))
         _, tm = first_tile(row)
         _, tn = first_tile(col)
         kname, tk = first_tile(red)
@@ -231,7 +234,7 @@ class CudaNodeScheduler:
         if tn is not None:
             cfg["tile_n"] = snap(tn, LEGAL_TILE_N, "CTA tile columns")
         if tk is not None:
-            cfg["tile_k"] = (snap(tk, LEGAL_SLAB, "channels per stage") if resident
+            cfg["tile_k"] = (snap(tk, LEGAL_SLAB, "channels per stage") if resident or streamed
                              else snap(tk, LEGAL_TILE_K, "K per stage"))
         if kname is not None and kname in self.unrolling:
             u = self.unrolling[kname]
@@ -262,11 +265,14 @@ class CudaNodeScheduler:
             elif any(0 in idx for idx in self.packed_buffers.values()):
                 # pack_at(_, 0) too: the input window stays on chip from one tile to the next
                 cfg["variant"] = 4
-        elif self.op_name == "conv2d" and any(0 in idx for idx in self.packed_buffers.values()):
-            # pack_at(_, 0) alone: a tile's input window is packed on chip once per channel slab
-            # and read by every filter tap, the weights stream beside it (CTA pairs, 128 filters)
+        elif streamed:
+            # a tile's input window is packed on chip once per channel slab and read by every
+            # filter tap, the weights stream beside it (CTA pairs, 128 filters per work item)
+            slab = cfg.get("tile_k")
             cfg = {k: v for k, v in cfg.items() if k not in ("tile_m", "tile_n", "tile_k", "split_k", "epilogue")}
             cfg["variant"] = 5
+            if slab == 16:
+                cfg["tile_k"] = 16  # 16-channel slabs: twice as many, half as large stages
         return cfg
 
     def node_schedule(self, strict: bool = False) -> CudaNodeSchedule:

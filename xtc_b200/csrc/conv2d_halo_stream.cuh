@@ -16,7 +16,8 @@
 // Stage layout: [halo slab, rounded up to 1024 bytes][filter group 0: taps x 4 KB][group 1:
 // taps x 4 KB]; a tap's block is 32 k-rows of 32 filters, the MN-major operand layout of
 // conv2d_halo.cuh, and the two groups of a tap lie taps * 4096 bytes apart (the descriptor's
-// leading-dimension offset).
+// leading-dimension offset).  With 16-channel slabs (SLAB = 16) everything halves: pixel rows
+// of 64 bytes, tap blocks of 16 k-rows, and twice as many stages fit.
 //
 // Balance.  With whole work items dealt round-robin, 113 items on 74 CTA pairs are two rounds of
 // which the second is half empty.  Given a workspace, the kernel deals out (work item, channel
@@ -78,13 +79,16 @@ __device__ __forceinline__ long long stream_units_of(long long units, int num_pa
   return units / num_pairs + (pair < units % num_pairs ? 1 : 0);
 }
 
-template <bool DUAL>
+template <bool DUAL, int SLAB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HALO_THREADS, 1)
 conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
                           const __grid_constant__ CUtensorMap tmW, const ConvHaloParams p) {
   using namespace dev;
+  static_assert(SLAB == 16 || SLAB == 32, "slabs are 16 or 32 channels wide");
   constexpr int BN = STREAM_BN;
   constexpr int HALF = BN / 2;
+  constexpr int ROW = SLAB * 4;                   // bytes per pixel row of a stage
+  constexpr uint32_t TAP_BLOCK = SLAB * 128;      // one tap's weights for 32 filters: SLAB k rows of 128 B
   constexpr int NACC = DUAL ? 2 : 1;  // accumulators per tile, one per issuing thread
   constexpr uint32_t TMEM_COLS = 2 * NACC * BN;
   static_assert(TMEM_COLS <= 512, "accumulators do not fit in TMEM");
@@ -138,7 +142,7 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * 4096u;
+      const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * TAP_BLOCK;
       StreamSegments segs(p, pair, num_pairs);
       int tile, s0, s1;
       while (!failed && segs.next(tile, s0, s1)) {
@@ -161,10 +165,10 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
             mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(2 * (p.stage_tx + p.wts_tx)));
           uint8_t* dst = ring + static_cast<size_t>(stage) * p.stage_bytes;
           const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
-          tma_load_im2col_4d_pair(dst, &tmX, bar, slab * 32, iw, ih, img, 0, 0);
+          tma_load_im2col_4d_pair(dst, &tmX, bar, slab * SLAB, iw, ih, img, 0, 0);
 #pragma unroll
           for (int g = 0; g < HALF / 32; ++g)
-            tma_load_3d_pair(dst + p.wts_offset + g * group_bytes, &tmW, bar, f0 + g * 32, slab * 32, 0);
+            tma_load_3d_pair(dst + p.wts_offset + g * group_bytes, &tmW, bar, f0 + g * 32, slab * SLAB, 0);
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;
@@ -181,10 +185,13 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
       const int t0 = DUAL ? (w == 0 ? 0 : (p.taps + 1) / 2) : 0;
       const int t1 = DUAL ? (w == 0 ? (p.taps + 1) / 2 : p.taps) : p.taps;
       const int r0 = t0 / p.S, tap_s0 = t0 - r0 * p.S;
-      const uint32_t a_hi = umma_desc_hi(1024, static_cast<uint32_t>(UMMA_SWIZZLE_128B));
+      // A: K-major rows of ROW bytes, 8-row swizzle atoms
+      const uint32_t a_hi = umma_desc_hi(8 * ROW, static_cast<uint32_t>(SLAB == 32 ? UMMA_SWIZZLE_128B
+                                                                                  : UMMA_SWIZZLE_64B));
       const uint32_t b_hi = umma_desc_hi(512, static_cast<uint32_t>(UMMA_SWIZZLE_128B_BASE32B));
-      const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * 4096u;
-      const uint32_t row_step = static_cast<uint32_t>(p.Wp) * 8u;
+      const uint32_t group_bytes = static_cast<uint32_t>(p.taps) * TAP_BLOCK;
+      constexpr uint32_t PIX = ROW >> 4;                              // one pixel row, >> 4
+      const uint32_t row_step = static_cast<uint32_t>(p.Wp) * PIX;  // one image row down
       const uint32_t a_first = static_cast<uint32_t>(r0) * row_step;
       int stage = 0;
       uint32_t phase = 0;
@@ -210,17 +217,17 @@ conv2d_halo_stream_kernel(const __grid_constant__ CUtensorMap tmX,
           const uint32_t sA = smem_u32(ring + static_cast<size_t>(stage) * p.stage_bytes);
           uint32_t a_row = umma_desc_lo(sA, 16) + a_first;
           uint32_t b_lo = umma_desc_lo(sA + static_cast<uint32_t>(p.wts_offset) +
-                                           static_cast<uint32_t>(t0) * 4096u, group_bytes);
+                                           static_cast<uint32_t>(t0) * TAP_BLOCK, group_bytes);
           uint32_t first = slab == s0 ? 0u : 1u;  // a segment's first MMA overwrites its accumulator
           for (int tap = t0, s = tap_s0; tap < t1; ++tap) {
-            const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * 8u;
+            const uint32_t a_lo = a_row + static_cast<uint32_t>(s) * PIX;
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < SLAB / 8; ++kk) {
               umma_tf32_pair(d_tmem, umma_desc_pack(a_lo + kk * 2, a_hi),
                              umma_desc_pack(b_lo + kk * 64, b_hi), idesc, first | (kk != 0));
             }
             first = 1u;
-            b_lo += 4096u >> 4;
+            b_lo += TAP_BLOCK >> 4;
             if (++s == p.S) {
               s = 0;
               a_row += row_step;

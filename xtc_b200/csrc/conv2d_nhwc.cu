@@ -445,10 +445,11 @@ int launch_conv_slide(const ConvArgs& a, const SlidePlan& h) {
 // 32-channel halo slab + the weights of every tap for this CTA's 64 filters; at least two stages.
 struct StreamPlan {
   bool ok = false;
-  int P = 0, stages = 0, stage_bytes = 0, wts_offset = 0, wts_tx = 0, nslab = 0, smem = 0;
+  int P = 0, stages = 0, stage_bytes = 0, wts_offset = 0, wts_tx = 0, nslab = 0, smem = 0, slab = 32;
 };
-StreamPlan plan_stream(const ConvArgs& a) {
+StreamPlan plan_stream(const ConvArgs& a, int slab = 32) {
   StreamPlan s;
+  s.slab = slab;
   if (a.sh != 1 || a.sw != 1 || a.C % 4 != 0 || a.F % 4 != 0) return s;
   const int64_t taps = a.R * a.S;
   if (taps < 2 || taps > 32) return s;  // a single tap is a plain GEMM: nothing to share
@@ -456,14 +457,14 @@ StreamPlan plan_stream(const ConvArgs& a) {
   const int64_t P = BM + (a.R - 1) * Wp + (a.S - 1);
   if (P > 1024 || a.pl > 127 || a.pt > 127 || a.pr > 127 || a.pb > 127) return s;
   s.P = static_cast<int>(P);
-  s.wts_offset = static_cast<int>((P * 128 + 1023) / 1024 * 1024);
-  s.wts_tx = static_cast<int>(taps * (STREAM_BN / 2) * 128);
+  s.wts_offset = static_cast<int>((P * slab * 4 + 1023) / 1024 * 1024);
+  s.wts_tx = static_cast<int>(taps * (STREAM_BN / 2) * slab * 4);
   s.stage_bytes = s.wts_offset + s.wts_tx;
   const int64_t fixed = 1024 + 1024;  // alignment slack, barriers
   const int64_t stages = (232448 - fixed) / s.stage_bytes;
   if (stages < 2) return s;
-  s.stages = static_cast<int>(stages > 4 ? 4 : stages);
-  s.nslab = static_cast<int>((a.C + 31) / 32);
+  s.stages = static_cast<int>(stages > 6 ? 6 : stages);
+  s.nslab = static_cast<int>((a.C + slab - 1) / slab);
   s.smem = static_cast<int>(fixed + static_cast<int64_t>(s.stages) * s.stage_bytes);
   s.ok = true;
   return s;
@@ -505,8 +506,8 @@ static bool stream_is_default(const ConvArgs& a, const StreamPlan& sp) {
   return (items >= 40 || sp.nslab <= 2) && a.OH * a.OW * 10 >= grid_positions * 7;
 }
 
-int launch_conv_stream(const ConvArgs& a, const StreamPlan& h, void* workspace = nullptr,
-                       size_t workspace_bytes = 0) {
+template <int SLAB>
+int launch_conv_stream_slab(const ConvArgs& a, const StreamPlan& h, void* workspace, size_t workspace_bytes) {
   encode_im2col_fn enc = get_encode_im2col();
   encode_tiled_fn enc_tiled = get_encode_tiled();
   XTC_REQUIRE(enc != nullptr && enc_tiled != nullptr,
@@ -523,16 +524,16 @@ int launch_conv_stream(const ConvArgs& a, const StreamPlan& h, void* workspace =
   int upper[2] = {a.pr, a.pb};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.X), dims, strides,
-                   lower, upper, 32, static_cast<cuuint32_t>(h.P), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   lower, upper, SLAB, static_cast<cuuint32_t>(h.P), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   SLAB == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   XTC_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeIm2col (streamed halo) failed (%d)", static_cast<int>(r));
   // the filter as [tap][channel][filter]: one copy = every tap x 32 channels x 32 filters
   const int taps = static_cast<int>(a.R * a.S);
   cuuint64_t wdims[3] = {static_cast<cuuint64_t>(a.F), static_cast<cuuint64_t>(a.C),
                          static_cast<cuuint64_t>(taps)};
   cuuint64_t wstrides[2] = {static_cast<cuuint64_t>(a.F) * 4, static_cast<cuuint64_t>(a.C * a.F) * 4};
-  cuuint32_t wbox[3] = {32, 32, static_cast<cuuint32_t>(taps)};
+  cuuint32_t wbox[3] = {32, SLAB, static_cast<cuuint32_t>(taps)};
   r = enc_tiled(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(a.Wt), wdims, wstrides, wbox,
                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -561,13 +562,13 @@ int launch_conv_stream(const ConvArgs& a, const StreamPlan& h, void* workspace =
   p.pad_left = a.pl;
   p.pad_top = a.pt;
   p.stage_bytes = h.stage_bytes;
-  p.stage_tx = h.P * 128;
+  p.stage_tx = h.P * SLAB * 4;
   p.wts_offset = h.wts_offset;
   p.wts_tx = h.wts_tx;
   p.stages = a.stages >= 2 && a.stages < h.stages ? a.stages : h.stages;
   p.relu = a.relu;
   p.relu_threshold = a.thr;
-  auto kernel = conv2d_halo_stream_kernel<true>;  // plan_stream wants two taps or more
+  auto kernel = conv2d_halo_stream_kernel<true, SLAB>;  // plan_stream wants two taps or more
   static thread_local int configured_dev = -1;
   static thread_local int configured_smem = 0;
   if (configured_dev != dev || configured_smem < h.smem) {
@@ -587,6 +588,12 @@ int launch_conv_stream(const ConvArgs& a, const StreamPlan& h, void* workspace =
   }
   XTC_CUDA_CHECK(launch_overlapped(kernel, grid, HALO_THREADS, h.smem, a.stream, tmX, tmW, p));
   return XTC_CUDA_OK;
+}
+
+int launch_conv_stream(const ConvArgs& a, const StreamPlan& h, void* workspace = nullptr,
+                       size_t workspace_bytes = 0) {
+  return h.slab == 16 ? launch_conv_stream_slab<16>(a, h, workspace, workspace_bytes)
+                      : launch_conv_stream_slab<32>(a, h, workspace, workspace_bytes);
 }
 
 int dispatch_conv_halo(const ConvArgs& a, const HaloPlan& h, bool pair, bool taps = false) {
@@ -897,7 +904,7 @@ extern "C" int xtc_cuda_conv2d_nhwc_f32(const float* X, const float* Wt, float* 
   }
   XTC_REQUIRE(c.variant >= 0 && c.variant <= 5, "conv2d: unknown variant %d", c.variant);
   if (c.variant == 5) {
-    const StreamPlan sp = plan_stream(a);
+    const StreamPlan sp = plan_stream(a, c.tile_k == 16 ? 16 : 32);  // tile_k = 16: 16-channel slabs
     if (sp.ok) return launch_conv_stream(a, sp, workspace, workspace_bytes);
     set_error("conv2d: the streamed-weights variant (5) needs stride 1, channels and filters that are "
               "multiples of 4, 2 to 32 filter taps and two stages of one halo slab plus the taps' weights "

@@ -181,7 +181,8 @@ class StrategyCudaConv:
                  halo run of at most 256 positions); no other parameter applies
       variant 5  streamed weights beside halo tiles, for filter banks that do not fit in shared
                  memory: CTA pairs, 128 filters per tile, a stage = one 32-channel halo slab + every
-                 tap's weights (2 to 32 taps, two such stages must fit); only ``stages`` applies
+                 tap's weights (2 to 32 taps, two such stages must fit); ``tile_k`` = 16 halves the
+                 slabs, ``stages`` sets the depth
       variant 1  implicit GEMM, one im2col fetch per filter tap: the GEMM kernels' tile_m /
                  tile_n / tile_k / stages / epilogue, and split_k = 2 to 8 pieces of the
                  reduction in one thread-block cluster (one CTA per tile, tile_n <= 128)
@@ -230,17 +231,18 @@ class StrategyCudaConv:
         bank = self._r * self._s * -(-self._c // 32) * (64 if self._f <= 64 else 128) * 128
         return run <= 256 and bank + 5 * 16384 + 2048 <= SMEM_BUDGET + 2048
 
-    def streamed_stages(self) -> int:
-        """Stages of the streamed-weights kernel that fit (0 = it does not take this layer)."""
+    def streamed_stages(self, slab: int = 32) -> int:
+        """Stages of the streamed-weights kernel that fit with slabs of ``slab`` channels (0 = it
+        does not take this layer)."""
         taps = self._r * self._s
         if self._stride != (1, 1) or self._c % 4 or self._f % 4 or not 2 <= taps <= 32:
             return 0
         run = 128 + (self._r - 1) * self._in_w + self._s - 1
         if run > 1024:
             return 0
-        stage = -(-run * 128 // 1024) * 1024 + taps * 64 * 128
+        stage = -(-run * slab * 4 // 1024) * 1024 + taps * 64 * slab * 4
         fit = SMEM_BUDGET // stage
-        return min(fit, 4) if fit >= 2 else 0
+        return min(fit, 6) if fit >= 2 else 0
 
     def library_streams(self) -> bool:
         """Whether the library, with nothing named, runs this layer on the streamed-weights kernel
@@ -256,8 +258,8 @@ class StrategyCudaConv:
     def is_legal(self, sample: list[int]) -> bool:
         variant, tm, tn, tk, st, tma, split = sample
         if variant == 5:
-            fit = self.streamed_stages()
-            return (fit >= 2 and tm == 256 and tn == 128 and tk == 32 and tma == 0 and split == 1
+            fit = self.streamed_stages(tk) if tk in (16, 32) else 0
+            return (fit >= 2 and tm == 256 and tn == 128 and tma == 0 and split == 1
                     and (st == 0 or 2 <= st <= fit))
         if variant == 4:
             return (self.sliding_window_fits() and tm == 128 and tk == 32 and st == 0 and tma == 0
@@ -282,9 +284,9 @@ class StrategyCudaConv:
                 yield s
         if self.is_legal([4, 128, min(tn_res, 128), 32, 0, 0, 1]):
             yield [4, 128, min(tn_res, 128), 32, 0, 0, 1]
-        for st in (0, 2, 3):
-            if self.is_legal([5, 256, 128, 32, st, 0, 1]):
-                yield [5, 256, 128, 32, st, 0, 1]
+        for slab, st in itertools.product((32, 16), (0, 2, 3, 4)):
+            if self.is_legal([5, 256, 128, slab, st, 0, 1]):
+                yield [5, 256, 128, slab, st, 0, 1]
         for tm, tn, tk, st, tma, split in itertools.product(g.tile_m, g.tile_n, g.tile_k, g.stages,
                                                             (0, 1), StrategyCudaGemm.SPLITS):
             s = [1, tm, tn, tk, st, tma, split]
