@@ -289,8 +289,10 @@ int xtc_cuda_gemm_f32_3xtf32_noalloc(const float* A, const float* B, float* C, i
  * semantics src/xtc/graphs/xtc/operators.py:252-347 and, for the fused pad,
  * operators.py:350-433 with constant_value == 0.
  * `workspace` (size from xtc_cuda_conv2d_workspace_bytes for the same shape and
- * cfg; zeroed before its first use, may be reused by later calls) serves two
- * things: the partial sums of a split of K the library chose, and, for thin
+ * cfg; zeroed before its first use, may be reused by later calls) serves
+ * three things: the partial sums of a split of K the library chose, the
+ * partial sums and flags of the streamed-weights kernel's balanced form
+ * (cfg.variant 5, or the library's own choice of it), and, for thin
  * inputs (C not a multiple of 4, or at most 8 channels where the
  * resident-weights kernel does not apply, with nothing named in cfg), the
  * packed form of the layer: the S*C values a filter row needs per output
